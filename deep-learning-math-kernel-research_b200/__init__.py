@@ -1,0 +1,257 @@
+"""euler-b200: B200 (sm_100a) convolution kernels behind the Euler API.
+
+This package is the Python door to the C-ABI library ``lib/libeuler_b200.so`` (sources in
+``csrc/``, interface in ``include/euler_b200.h``).  It mirrors the reference's public surface
+(``include/euler.hpp``): an ``eld_conv_t`` descriptor with the same field names, ``setup()`` and
+``elx_conv(desc, output, input, weights, bias)``.
+
+There is no CPU implementation here.  Importing works without a GPU (the library loads and its
+symbols can be inspected), but every compute call needs an sm_100 device and fails loudly
+otherwise; a missing or stale shared library raises at import time.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+from types import SimpleNamespace
+
+PKG_DIR = Path(__file__).resolve().parent
+ROOT = PKG_DIR.parent
+LIB_PATH = PKG_DIR / "lib" / "libeuler_b200.so"
+HOST_LIB_PATH = PKG_DIR / "lib" / "libel.so"
+CSRC = PKG_DIR / "csrc"
+CU_SOURCES = ["elb_api.cu", "int8_conv.cu", "wino.cu", "misc.cu"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
+
+# ----------------------------------------------------------------------------- constants
+ELB_OK, ELB_UNIMPLEMENTED, ELB_GENERAL_ERROR = 0, 1, 2
+ELD_OK, ELD_UNIMPLEMENTED, ELD_GENERAL_ERROR = 0, 1, 2
+ELX_OK, ELX_UNIMPLEMENTED, ELX_GENERAL_ERROR = 0, 1, 2
+CONV_AUTO, CONV_DIRECT_1X1, CONV_DIRECT, CONV_DIRECT_VMG, CONV_WINOGRAD, DECONV_DIRECT = range(6)
+data_type_undef, f32, f16, u8, s8, s32 = range(6)
+(format_undef, nchw, nhwc, nChw16c, nChw8c, oihw, hwio, OIhw16i16o, OIhw8i8o, goihw, ghwio, gOIhw16i16o,
+ gOIhw8i8o) = range(13)
+forward_training, forward_inference, backward_data, backward_weights = range(4)
+FINE, COARSE, CALIBRATED = range(3)
+EL_NO_CALI = 3.4028234663852886e38
+KERNEL_NAMES = {0: "none", 1: "i8_gemm_umma", 2: "i8_conv_umma", 3: "i8_simt", 4: "wino_f32_umma",
+                5: "wino_i8_umma", 6: "i8_depthwise"}
+
+
+def build(verbose: bool = False) -> Path:
+    """Compile csrc/*.cu for sm_100a into lib/libeuler_b200.so (nvcc cross-compiles without a GPU)
+    and the C++ host library lib/libel.so that implements include/euler.hpp on top of it."""
+    LIB_PATH.parent.mkdir(exist_ok=True)
+    srcs = [str(CSRC / s) for s in CU_SOURCES]
+    deps = list(CSRC.glob("*")) + [ROOT / "include" / "euler_b200.h"]
+    if not LIB_PATH.exists() or any(p.stat().st_mtime > LIB_PATH.stat().st_mtime for p in deps):
+        cmd = ["nvcc"] + NVCC_FLAGS + ["-o", str(LIB_PATH)] + srcs
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
+    host_src = PKG_DIR / "host" / "euler_host.cpp"
+    hdeps = [host_src, ROOT / "include" / "euler.hpp", ROOT / "include" / "euler_reorder.hpp", LIB_PATH]
+    if host_src.exists() and (not HOST_LIB_PATH.exists()
+                              or any(p.stat().st_mtime > HOST_LIB_PATH.stat().st_mtime for p in hdeps)):
+        cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{ROOT / 'include'}",
+               "-o", str(HOST_LIB_PATH), str(host_src), f"-L{LIB_PATH.parent}", "-leuler_b200",
+               "-Wl,-rpath,$ORIGIN"]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
+    return LIB_PATH
+
+
+# ----------------------------------------------------------------------------- C structs
+class ElbConvDesc(C.Structure):
+    _fields_ = [(k, C.c_int32) for k in
+                ("n", "g", "ic", "oc", "ih", "iw", "oh", "ow", "kh", "kw", "pad_l", "pad_r", "pad_t", "pad_b",
+                 "stride_h", "stride_w", "dilation_h", "dilation_w", "dt_input", "dt_weights", "dt_output",
+                 "dt_bias", "fmt_input", "fmt_weights", "fmt_output", "prop_kind", "algorithm", "tile_size",
+                 "with_relu", "with_bias", "with_ip_sum", "with_op_sum", "with_argmax", "f16c_opt",
+                 "disable_autoparam")] + \
+               [("relu_lower", C.c_float), ("relu_upper", C.c_float), ("execution_mode", C.c_int32)] + \
+               [(k, C.c_float) for k in ("input_scale", "input_z", "tinput_scale", "tinput_z", "output_scale",
+                                         "output_z", "sum_scale", "sum_z")] + \
+               [("sampling_kind", C.c_int32), ("device", C.c_int32)]
+
+
+class ElbConvInfo(C.Structure):
+    _fields_ = [("algorithm", C.c_int32), ("tile_size", C.c_int32), ("kernel", C.c_int32), ("device", C.c_int32)] + \
+               [(k, C.c_uint64) for k in ("size_input", "size_weights", "size_output", "size_bias", "bytes_input",
+                                          "bytes_weights", "bytes_output", "bytes_bias", "workspace_bytes")] + \
+               [("launches_per_call", C.c_int32), ("reserved", C.c_int32)]
+
+
+def _load():
+    if not LIB_PATH.exists():
+        raise ImportError(f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                          "(there is no CPU fallback)")
+    lib = C.CDLL(str(LIB_PATH))
+    vp, i32, u64 = C.c_void_p, C.c_int32, C.c_uint64
+    sig = {
+        "elb_conv_sizes": (i32, [C.POINTER(ElbConvDesc), C.POINTER(ElbConvInfo)]),
+        "elb_conv_create": (i32, [C.POINTER(ElbConvDesc), C.POINTER(vp)]),
+        "elb_conv_info": (i32, [vp, C.POINTER(ElbConvInfo)]),
+        "elb_conv_execute": (i32, [vp, vp, vp, vp, vp]),
+        "elb_conv_enqueue": (i32, [vp, vp, vp, vp, vp, vp]),
+        "elb_conv_prepare": (i32, [vp, vp, vp]),
+        "elb_conv_set_accumulator_dump": (i32, [vp, vp]),
+        "elb_conv_device_status": (i32, [vp]),
+        "elb_conv_launch_count": (u64, [vp]),
+        "elb_conv_destroy": (None, [vp]),
+        "elb_last_error": (C.c_char_p, []),
+        "elb_device_supported": (i32, [i32]),
+        "elb_reorder_nchw_to_nChw16c": (i32, [vp, vp, i32, i32, i32, i32, i32, vp]),
+        "elb_reorder_nChw16c_to_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, vp]),
+        "elb_selftest_bounded_wait": (i32, [i32, C.c_ulonglong]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)          # AttributeError here = stale library
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+EXPORTED_SYMBOLS = ["elb_conv_sizes", "elb_conv_create", "elb_conv_info", "elb_conv_execute", "elb_conv_enqueue",
+                    "elb_conv_prepare", "elb_conv_set_accumulator_dump", "elb_conv_device_status",
+                    "elb_conv_launch_count", "elb_conv_destroy", "elb_last_error", "elb_device_supported",
+                    "elb_reorder_nchw_to_nChw16c", "elb_reorder_nChw16c_to_nchw"]
+
+
+def last_error() -> str:
+    return lib.elb_last_error().decode()
+
+
+def _ptr(x):
+    """Address of a torch tensor / numpy array / int / None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(f"cannot take the address of {type(x)}")
+
+
+class eld_conv_t:
+    """Python mirror of ``euler::eld_conv_t`` (include/euler.hpp:110-187): same field names, same
+    defaults (src/eld_conv.cpp:21-50), ``setup()`` returns ELD_* codes and fills ``sizes`` /
+    ``byte_sizes``; the plan (``xc``) is released by ``close()`` or garbage collection."""
+
+    def __init__(self):
+        self.dims = SimpleNamespace(n=0, g=1, ic=0, oc=0, ih=0, iw=0, oh=0, ow=0, kh=0, kw=0)
+        self.pads = SimpleNamespace(l=1, r=1, t=1, b=1)
+        self.strides = SimpleNamespace(h=1, w=1)
+        self.dilations = SimpleNamespace(h=1, w=1)
+        self.data_type = SimpleNamespace(input=f32, weights=f32, output=f32, bias=f32)
+        self.formats = SimpleNamespace(input=nChw16c, weights=OIhw16i16o, output=nChw16c)
+        self.prop_kind = forward_inference
+        self.algorithm = CONV_DIRECT
+        self.tile_size = 0
+        self.with_relu = self.with_bias = self.with_ip_sum = self.with_op_sum = self.with_argmax = False
+        self.f16c_opt = False
+        self.is_inference = True
+        self.use_scratch_pad = False
+        self.disable_autoparam = True
+        self.eager_mode = True
+        self.stream_sync = False
+        self.relu_bound = SimpleNamespace(lower=0.0, upper=EL_NO_CALI)
+        self.nthreads = 0
+        self.execution_mode = 0
+        self.flatting = SimpleNamespace(o=0, t=0)
+        self.blocking = SimpleNamespace(i=0, o=0)
+        self.partition = SimpleNamespace(i=1, o=1, g=1)
+        self.streaming_hint = SimpleNamespace(input=0, output=0)
+        self.input_quant = SimpleNamespace(scale=EL_NO_CALI, z=EL_NO_CALI)
+        self.wino_tinput_quant = SimpleNamespace(scale=EL_NO_CALI, z=EL_NO_CALI)
+        self.output_quant = SimpleNamespace(scale=EL_NO_CALI, z=EL_NO_CALI)
+        self.sum_quant = SimpleNamespace(scale=1.0, z=0.0)
+        self.sampling_kind = FINE
+        self.name = "ioi"
+        self.device = -1
+        self.sizes = SimpleNamespace(input=0, weights=0, output=0, bias=0)
+        self.byte_sizes = SimpleNamespace(input=0, weights=0, output=0, bias=0)
+        self.xc = None
+        self.info = None
+
+    def _c_desc(self) -> ElbConvDesc:
+        d, p = self.dims, self.pads
+        return ElbConvDesc(
+            d.n, d.g, d.ic, d.oc, d.ih, d.iw, d.oh, d.ow, d.kh, d.kw, p.l, p.r, p.t, p.b, self.strides.h,
+            self.strides.w, self.dilations.h, self.dilations.w, self.data_type.input, self.data_type.weights,
+            self.data_type.output, self.data_type.bias, self.formats.input, self.formats.weights,
+            self.formats.output, self.prop_kind, self.algorithm, self.tile_size, int(self.with_relu),
+            int(self.with_bias), int(self.with_ip_sum), int(self.with_op_sum), int(self.with_argmax),
+            int(self.f16c_opt), int(self.disable_autoparam), self.relu_bound.lower, self.relu_bound.upper,
+            self.execution_mode, self.input_quant.scale, self.input_quant.z, self.wino_tinput_quant.scale,
+            self.wino_tinput_quant.z, self.output_quant.scale, self.output_quant.z, self.sum_quant.scale,
+            self.sum_quant.z, int(self.sampling_kind), self.device)
+
+    def setup(self, fully_setup: bool = True) -> int:
+        desc = self._c_desc()
+        info = ElbConvInfo()
+        self.close()
+        if fully_setup:
+            plan = C.c_void_p()
+            rc = lib.elb_conv_create(C.byref(desc), C.byref(plan))
+            if rc != ELB_OK:
+                return rc
+            self.xc = plan
+            lib.elb_conv_info(self.xc, C.byref(info))
+        else:
+            rc = lib.elb_conv_sizes(C.byref(desc), C.byref(info))
+            if rc != ELB_OK:
+                return rc
+        self.info = info
+        self.algorithm, self.tile_size = info.algorithm, info.tile_size
+        self.sizes = SimpleNamespace(input=info.size_input, weights=info.size_weights, output=info.size_output,
+                                     bias=info.size_bias)
+        self.byte_sizes = SimpleNamespace(input=info.bytes_input, weights=info.bytes_weights,
+                                          output=info.bytes_output, bias=info.bytes_bias)
+        return ELD_OK
+
+    @property
+    def kernel(self) -> str:
+        return KERNEL_NAMES.get(self.info.kernel if self.info else 0, "?")
+
+    def prepare(self, weights, bias) -> int:
+        return lib.elb_conv_prepare(self.xc, _ptr(weights), _ptr(bias))
+
+    def enqueue(self, output, input, weights=None, bias=None, stream=None) -> int:
+        """Device pointers only; returns after the kernels are enqueued on ``stream``."""
+        return lib.elb_conv_enqueue(self.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias), stream)
+
+    def set_accumulator_dump(self, dev_int32) -> int:
+        return lib.elb_conv_set_accumulator_dump(self.xc, _ptr(dev_int32))
+
+    def device_status(self) -> int:
+        return lib.elb_conv_device_status(self.xc)
+
+    def launch_count(self) -> int:
+        return int(lib.elb_conv_launch_count(self.xc))
+
+    def close(self):
+        if self.xc is not None:
+            lib.elb_conv_destroy(self.xc)
+            self.xc = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def elx_conv(desc: eld_conv_t, output, input, weights, bias) -> int:
+    """``euler::elx_conv`` (include/euler.hpp:190): run the convolution and wait.  Arguments may be
+    torch tensors (CUDA or CPU), numpy arrays or raw addresses; output comes first."""
+    if desc.xc is None:
+        raise RuntimeError("elx_conv: descriptor is not set up")
+    return lib.elb_conv_execute(desc.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias))

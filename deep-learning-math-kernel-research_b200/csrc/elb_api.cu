@@ -1,0 +1,599 @@
+// C-ABI layer (include/euler_b200.h): descriptor validation and algorithm choice (the reference's
+// eld_conv_t::setup, src/eld_conv.cpp:59-316), the plan object that replaces `elx_conv_t *xc`,
+// first-call weight preparation (setup_workspace, src/elx_conv.hpp:130-145) and execution
+// (elx_conv, src/elx_conv.cpp:213-240).  There is deliberately no CPU path: when no CUDA device
+// is usable every compute entry point fails with ELB_GENERAL_ERROR.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/euler_b200.h"
+#include "elb_common.cuh"
+#include "host_prep.hpp"
+#include "wino.cuh"
+
+using namespace elb;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  const char *v = getenv("EULER_VERBOSE");
+  if (v && atoi(v) > 0) fprintf(stderr, "euler-b200: %s\n", buf);
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t e__ = (expr);                                                               \
+    if (e__ != cudaSuccess)                                                                 \
+      return fail(ELB_GENERAL_ERROR, "CUDA error %s at %s:%d (%s)", cudaGetErrorName(e__),  \
+                  __FILE__, __LINE__, cudaGetErrorString(e__));                             \
+  } while (0)
+
+size_t dt_size(int dt) {
+  switch (dt) {
+    case ELB_F32: return 4;
+    case ELB_F16: return 2;
+    case ELB_U8:
+    case ELB_S8: return 1;
+    default: return 0;
+  }
+}
+
+bool blocked_act(int f) { return f == ELB_NCHW16C || f == ELB_NCHW8C; }
+bool blocked_w(int f) {
+  return f == ELB_OIHW16I16O || f == ELB_OIHW8I8O || f == ELB_GOIHW16I16O || f == ELB_GOIHW8I8O;
+}
+
+// sizes exactly as src/eld_conv.cpp:99-126 computes them
+void compute_sizes(const elb_conv_desc_t &d, elb_conv_info_t &info) {
+  const int icg = d.ic / d.g, ocg = d.oc / d.g;
+  info.size_input = (uint64_t)d.n * d.ih * d.iw * (blocked_act(d.fmt_input) ? host::alignup(d.ic, V) : d.ic);
+  info.size_weights = (uint64_t)d.g * d.kh * d.kw *
+                          (blocked_w(d.fmt_weights) ? (uint64_t)host::alignup(icg, V) * host::alignup(ocg, V)
+                                                    : (uint64_t)ocg * icg) +
+                      4 * V;
+  info.size_output = (uint64_t)d.n * d.oh * d.ow * (blocked_act(d.fmt_output) ? host::alignup(d.oc, V) : d.oc);
+  info.size_bias = blocked_act(d.fmt_output) ? host::alignup(d.oc, V) : d.oc;
+  info.bytes_input = dt_size(d.dt_input) * info.size_input;
+  info.bytes_weights = dt_size(d.dt_weights) * info.size_weights;
+  info.bytes_output = dt_size(d.dt_output) * info.size_output;
+  info.bytes_bias = dt_size(d.dt_bias) * info.size_bias;
+}
+
+// CONV_AUTO and Winograd tile choice as in src/eld_conv.cpp:148-159, 231-236
+int resolve_algorithm(const elb_conv_desc_t &d, int &algorithm, int &tile) {
+  algorithm = d.algorithm;
+  tile = d.tile_size;
+  if (algorithm == ELB_CONV_AUTO) {
+    if (d.kh == 1 && d.kw == 1) algorithm = ELB_CONV_DIRECT_1X1;
+    else if (d.ic / d.g >= V && d.kh == 3 && d.kw == 3 && d.dilation_h == 1 && d.dilation_w == 1 &&
+             d.stride_h == 1 && d.stride_w == 1 && d.pad_l == 1 && d.pad_r == 1 && d.pad_t == 1 && d.pad_b == 1)
+      algorithm = ELB_CONV_WINOGRAD;
+    else algorithm = ELB_CONV_DIRECT;
+  }
+  if (algorithm == ELB_CONV_WINOGRAD && tile == 0) {
+    const int t = d.n * ((d.oh + 3) / 4) * ((d.ow + 3) / 4);
+    const float mac_per_read = (float)((double)t * host::alignup(d.oc, 16)) * 1.0f / (t + host::alignup(d.oc, V));
+    tile = mac_per_read > 25.0f ? 6 : 4;
+  }
+  return ELB_OK;
+}
+
+bool is_int8_user(const elb_conv_desc_t &d) {
+  return d.dt_input == ELB_U8 && d.dt_weights == ELB_F32 && d.dt_bias == ELB_F32 &&
+         (d.dt_output == ELB_U8 || d.dt_output == ELB_S8 || d.dt_output == ELB_F32);
+}
+bool is_fp32_user(const elb_conv_desc_t &d) {
+  return d.dt_input == ELB_F32 && d.dt_weights == ELB_F32 && d.dt_output == ELB_F32 && d.dt_bias == ELB_F32;
+}
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_encodeTiled>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+struct elb_conv {
+  elb_conv_desc_t d;
+  elb_conv_info_t info;
+  int device = 0;
+  int num_sms = 0;
+  bool prepared = false;
+  uint64_t launches = 0;
+  cudaStream_t stream = nullptr;        // used by elb_conv_execute
+  // device workspace
+  void *d_wpack = nullptr, *d_wplain = nullptr, *d_scale = nullptr, *d_shift = nullptr;
+  int *d_status = nullptr;
+  void *d_acc_dump = nullptr;           // caller memory
+  // staging for host-pointer callers
+  void *d_in_stage = nullptr, *d_out_stage = nullptr;
+  // int8 direct
+  I8ConvParams i8{};
+  I8UmmaConfig i8cfg{};
+  const void *tmap_for = nullptr;       // input pointer the tensor maps were encoded for
+  // winograd
+  WinoPlan wino{};
+
+  ~elb_conv() {
+    cudaSetDevice(device);
+    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, (void *)d_status, d_in_stage, d_out_stage})
+      if (p) cudaFree(p);
+    wino_release(wino);
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int validate_common(const elb_conv_desc_t &d) {
+  if (d.n <= 0 || d.g <= 0 || d.ic <= 0 || d.oc <= 0 || d.ih <= 0 || d.iw <= 0 || d.oh <= 0 || d.ow <= 0 ||
+      d.kh <= 0 || d.kw <= 0 || d.stride_h <= 0 || d.stride_w <= 0)
+    return fail(ELB_GENERAL_ERROR, "invalid dimensions");
+  if (d.ic % d.g || d.oc % d.g) return fail(ELB_GENERAL_ERROR, "ic/oc not divisible by groups");
+  if (d.prop_kind != ELB_FORWARD_INFERENCE)
+    return fail(ELB_GENERAL_ERROR, "Propagation kind error");     // src/eld_conv.cpp:143-146
+  return ELB_OK;
+}
+
+// Choose the kernel for a resolved algorithm; ELB_KERNEL_NONE = not implemented on this library.
+int choose_kernel(const elb_conv_desc_t &d, int algorithm, int tile, const char **why) {
+  *why = "";
+  const bool blocked = d.fmt_input == ELB_NCHW16C && d.fmt_output == ELB_NCHW16C;
+  if (!blocked) { *why = "only nChw16c activations are implemented"; return ELB_KERNEL_NONE; }
+  if (d.dilation_h != 1 || d.dilation_w != 1) { *why = "dilation"; return ELB_KERNEL_NONE; }
+  if (d.stride_h != d.stride_w) { *why = "anisotropic stride"; return ELB_KERNEL_NONE; }
+  const bool depthwise = d.g > 1 && d.g == d.ic && d.g == d.oc;
+  if (d.g != 1 && !depthwise) { *why = "grouped convolution"; return ELB_KERNEL_NONE; }
+  if (algorithm == ELB_CONV_WINOGRAD) {
+    if (d.stride_h != 1 || d.kh != 3 || d.kw != 3 || d.g != 1) { *why = "Winograd needs 3x3 stride 1"; return ELB_KERNEL_NONE; }
+    if (tile != 6) { *why = "only tile_size 6, F(4x4,3x3), is implemented"; return ELB_KERNEL_NONE; }
+    if (d.fmt_weights != ELB_OIHW16I16O) { *why = "weights must be OIhw16i16o"; return ELB_KERNEL_NONE; }
+    if (is_fp32_user(d)) return ELB_KERNEL_WINO_F32_UMMA;
+    if (is_int8_user(d)) return ELB_KERNEL_WINO_I8_UMMA;
+    *why = "unsupported data types for Winograd";
+    return ELB_KERNEL_NONE;
+  }
+  if (algorithm == ELB_CONV_DIRECT_1X1 || algorithm == ELB_CONV_DIRECT) {
+    if (!is_int8_user(d)) { *why = "direct convolution is implemented for u8 inputs only"; return ELB_KERNEL_NONE; }
+    if (algorithm == ELB_CONV_DIRECT_1X1 && (d.kh != 1 || d.kw != 1)) { *why = "1x1 algorithm on a non-1x1 filter"; return ELB_KERNEL_NONE; }
+    if (depthwise) {
+      if (d.kh != 3 || d.kw != 3 || d.dt_output == ELB_F32) { *why = "depthwise needs 3x3 and u8/s8 output"; return ELB_KERNEL_NONE; }
+      return ELB_KERNEL_I8_DEPTHWISE;
+    }
+    if (d.fmt_weights != ELB_OIHW16I16O) { *why = "weights must be OIhw16i16o"; return ELB_KERNEL_NONE; }
+    if (d.stride_h > 2) return ELB_KERNEL_I8_SIMT;
+    if (host::alignup(d.oc, V) > 2048) return ELB_KERNEL_I8_SIMT;
+    if (d.ih < d.stride_h || d.iw < d.stride_w) return ELB_KERNEL_I8_SIMT;
+    const char *force = getenv("ELB_FORCE_SIMT");
+    if (force && atoi(force) > 0) return ELB_KERNEL_I8_SIMT;
+    const bool flat = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.pad_t == 0 && d.pad_l == 0 &&
+                      d.oh == d.ih && d.ow == d.iw;
+    return flat ? ELB_KERNEL_I8_GEMM_UMMA : ELB_KERNEL_I8_CONV_UMMA;
+  }
+  *why = "algorithm not implemented";
+  return ELB_KERNEL_NONE;
+}
+
+// BOX-mode tile: BH x BW output pixels with BH*BW = 128, chosen to waste the fewest MMA rows.
+void choose_box(int oh, int ow, int &BW, int &BH) {
+  long best = -1;
+  for (int bw = 1; bw <= 128; bw *= 2) {
+    const int bh = 128 / bw;
+    const long cost = (long)((ow + bw - 1) / bw) * ((oh + bh - 1) / bh);
+    // prefer wide boxes on ties (longer contiguous runs per TMA row)
+    if (best < 0 || cost < best || (cost == best && bw > BW && bw <= 64)) { best = cost; BW = bw; BH = bh; }
+  }
+}
+
+int encode_i8_tmaps(elb_conv &pl, const void *input) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+  const elb_conv_desc_t &d = pl.d;
+  const int s = d.stride_h, CB = pl.i8.CB;
+  for (int ph = 0; ph < s; ++ph)
+    for (int pw = 0; pw < s; ++pw) {
+      const cuuint64_t Hp = (d.ih - ph + s - 1) / s, Wp = (d.iw - pw + s - 1) / s;
+      cuuint64_t dims[5] = {16, Wp, Hp, (cuuint64_t)CB, (cuuint64_t)d.n};
+      cuuint64_t strides[4] = {(cuuint64_t)s * 16, (cuuint64_t)s * d.iw * 16, (cuuint64_t)d.ih * d.iw * 16,
+                               (cuuint64_t)CB * d.ih * d.iw * 16};
+      cuuint32_t box[5] = {16, (cuuint32_t)pl.i8.BW, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8cfg.KC, 1};
+      cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+      void *base = (void *)((const uint8_t *)input + ((size_t)ph * d.iw + pw) * 16);
+      CUresult r = enc(&pl.i8.tmap[ph * s + pw], CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base, dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    }
+  pl.tmap_for = input;
+  return ELB_OK;
+}
+
+// ------------------------------------------------------------------------------ int8 direct
+int setup_i8_direct(elb_conv &pl) {
+  const elb_conv_desc_t &d = pl.d;
+  I8ConvParams &p = pl.i8;
+  if (d.sampling_kind != ELB_CALIBRATED)          // src/elx_int8_conv_direct.cpp:44-46, _1x1.cpp:225-226
+    return fail(ELB_UNIMPLEMENTED, "int8 direct: non-calibrated sampling_kind not supported");
+  if (d.input_z != 0.0f && (d.pad_t || d.pad_l || d.pad_b || d.pad_r))
+    return fail(ELB_UNIMPLEMENTED, "int8 direct: non-zero input zero-point with padding is not implemented");
+  p.N = d.n; p.IH = d.ih; p.IW = d.iw; p.OH = d.oh; p.OW = d.ow; p.KH = d.kh; p.KW = d.kw;
+  p.stride = d.stride_h; p.pad_t = d.pad_t; p.pad_l = d.pad_l;
+  p.CB = host::alignup(d.ic, V) / V;
+  p.OCB = host::alignup(d.oc, V) / V;
+  p.taps = d.kh * d.kw;
+  p.HW = d.oh * d.ow;
+  p.M = d.n * p.HW;
+  p.rq.out_type = d.dt_output == ELB_F32 ? OUT_F32 : d.dt_output == ELB_U8 ? OUT_U8 : OUT_S8;
+  p.rq.relu = d.with_relu;
+  p.rq.relu_lo = d.relu_lower;
+  p.rq.relu_hi = d.relu_upper;
+  // with_ip_sum: honoured by the 1x1 algorithm (src/kernel/elk_u8s8_gemm.hxx:221-237).  The KxK
+  // algorithm of the reference ignores the flag (src/elx_int8_conv_direct.cpp:121); this library
+  // applies the 1x1 semantics there as well, see DESIGN notes in the repository root.
+  p.rq.with_sum = d.with_ip_sum && d.dt_output != ELB_F32;
+  p.rq.sum_scale = d.sum_scale;
+  if (pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA || pl.info.kernel == ELB_KERNEL_I8_CONV_UMMA) {
+    const int mode = pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA ? I8_MODE_FLAT : I8_MODE_BOX;
+    pl.i8cfg = i8_umma_config(p.OCB, p.CB, p.taps, mode);
+    p.n_tiles = (p.OCB * V + pl.i8cfg.BN - 1) / pl.i8cfg.BN;
+    p.CBG = (p.CB + pl.i8cfg.KC - 1) / pl.i8cfg.KC;
+    p.k_stages = p.taps * p.CBG;
+    if (mode == I8_MODE_FLAT) {
+      p.m_tiles = (p.M + 127) / 128;
+    } else {
+      choose_box(d.oh, d.ow, p.BW, p.BH);
+      p.tiles_w = (d.ow + p.BW - 1) / p.BW;
+      p.tiles_h = (d.oh + p.BH - 1) / p.BH;
+      p.m_tiles = d.n * p.tiles_w * p.tiles_h;
+    }
+  }
+  pl.info.launches_per_call = 1;
+  return ELB_OK;
+}
+
+int prepare_i8_direct(elb_conv &pl, const void *weights, const void *bias) {
+  const elb_conv_desc_t &d = pl.d;
+  std::vector<float> hw(pl.info.size_weights), hb(pl.info.size_bias, 0.0f);
+  CUDA_TRY(cudaMemcpy(hw.data(), weights, pl.info.size_weights * 4, cudaMemcpyDefault));
+  if (d.with_bias) {
+    if (!bias) return fail(ELB_GENERAL_ERROR, "bias is null but with_bias is set");
+    CUDA_TRY(cudaMemcpy(hb.data(), bias, pl.info.size_bias * 4, cudaMemcpyDefault));
+  }
+  host::I8Weights wq = host::quantize_weights_i8(hw.data(), d.oc, d.ic, d.kh, d.kw);
+  std::vector<float> scale, shift;
+  host::fold_constants_i8(wq, hb.data(), d.with_bias != 0, d.dt_output == ELB_F32, d.input_scale, d.input_z,
+                          d.output_scale, d.output_z, pl.i8.rq.with_sum != 0, d.sum_scale, d.sum_z, scale, shift);
+  CUDA_TRY(cudaMalloc(&pl.d_scale, scale.size() * 4));
+  CUDA_TRY(cudaMalloc(&pl.d_shift, shift.size() * 4));
+  CUDA_TRY(cudaMemcpy(pl.d_scale, scale.data(), scale.size() * 4, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(pl.d_shift, shift.data(), shift.size() * 4, cudaMemcpyHostToDevice));
+  pl.info.workspace_bytes += scale.size() * 8;
+  if (pl.info.kernel == ELB_KERNEL_I8_SIMT) {
+    CUDA_TRY(cudaMalloc(&pl.d_wplain, wq.q.size()));
+    CUDA_TRY(cudaMemcpy(pl.d_wplain, wq.q.data(), wq.q.size(), cudaMemcpyHostToDevice));
+    pl.info.workspace_bytes += wq.q.size();
+  } else {
+    int n_tiles, CBG, k_stages;
+    std::vector<int8_t> pk = host::pack_b_i8(wq, pl.i8cfg.BN, pl.i8cfg.KC, n_tiles, CBG, k_stages);
+    if (n_tiles != pl.i8.n_tiles || CBG != pl.i8.CBG || k_stages != pl.i8.k_stages)
+      return fail(ELB_GENERAL_ERROR, "internal: weight packing geometry mismatch");
+    CUDA_TRY(cudaMalloc(&pl.d_wpack, pk.size()));
+    CUDA_TRY(cudaMemcpy(pl.d_wpack, pk.data(), pk.size(), cudaMemcpyHostToDevice));
+    pl.info.workspace_bytes += pk.size();
+  }
+  pl.i8.wpack = (const int8_t *)pl.d_wpack;
+  pl.i8.wplain = (const int8_t *)pl.d_wplain;
+  pl.i8.scale = (const float *)pl.d_scale;
+  pl.i8.shift = (const float *)pl.d_shift;
+  return ELB_OK;
+}
+
+int run_i8_direct(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
+  I8ConvParams &p = pl.i8;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(ELB_GENERAL_ERROR, "input/output tensors must be 16-byte aligned");
+  p.in = (const uint8_t *)in;
+  p.out = out;
+  p.acc_dump = (int32_t *)pl.d_acc_dump;
+  p.status = pl.d_status;
+  cudaError_t e;
+  if (pl.info.kernel == ELB_KERNEL_I8_SIMT) {
+    e = launch_i8_simt(p, s);
+  } else {
+    if (pl.info.kernel == ELB_KERNEL_I8_CONV_UMMA && pl.tmap_for != in) {
+      int rc = encode_i8_tmaps(pl, in);
+      if (rc != ELB_OK) return rc;
+    }
+    e = launch_i8_umma(p, pl.i8cfg, pl.num_sms, s);
+  }
+  pl.launches += 1;
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "kernel launch failed: %s", cudaGetErrorString(e));
+  return ELB_OK;
+}
+
+int check_status(elb_conv &pl) {
+  int st = 0;
+  CUDA_TRY(cudaMemcpy(&st, pl.d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(pl.d_status, 0, sizeof(int));
+    return fail(ELB_GENERAL_ERROR, "device kernel gave up waiting (status %d)", st);
+  }
+  return ELB_OK;
+}
+
+bool is_device_ptr(const void *p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
+  if (pl.prepared) return ELB_OK;
+  if (!weights) return fail(ELB_GENERAL_ERROR, "weights are null");
+  int rc;
+  switch (pl.info.kernel) {
+    case ELB_KERNEL_I8_GEMM_UMMA:
+    case ELB_KERNEL_I8_CONV_UMMA:
+    case ELB_KERNEL_I8_SIMT: rc = prepare_i8_direct(pl, weights, bias); break;
+    case ELB_KERNEL_WINO_F32_UMMA:
+    case ELB_KERNEL_WINO_I8_UMMA:
+    case ELB_KERNEL_I8_DEPTHWISE: {
+      std::string err;
+      rc = wino_prepare(pl.wino, pl.d, pl.info, weights, bias, err);
+      if (rc != ELB_OK) fail(rc, "%s", err.c_str());
+      break;
+    }
+    default: rc = fail(ELB_UNIMPLEMENTED, "no kernel");
+  }
+  if (rc == ELB_OK) pl.prepared = true;
+  return rc;
+}
+
+int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
+  switch (pl.info.kernel) {
+    case ELB_KERNEL_I8_GEMM_UMMA:
+    case ELB_KERNEL_I8_CONV_UMMA:
+    case ELB_KERNEL_I8_SIMT: return run_i8_direct(pl, out, in, s);
+    case ELB_KERNEL_WINO_F32_UMMA:
+    case ELB_KERNEL_WINO_I8_UMMA:
+    case ELB_KERNEL_I8_DEPTHWISE: {
+      std::string err;
+      int nl = 0;
+      int rc = wino_run(pl.wino, out, in, pl.d_acc_dump, pl.d_status, pl.num_sms, s, nl, err);
+      pl.launches += nl;
+      if (rc != ELB_OK) return fail(rc, "%s", err.c_str());
+      return rc;
+    }
+    default: return fail(ELB_UNIMPLEMENTED, "no kernel");
+  }
+}
+
+}  // namespace
+
+// =============================================================================== C ABI
+extern "C" {
+
+const char *elb_last_error(void) { return g_last_error.c_str(); }
+
+int elb_device_supported(int device) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(ELB_GENERAL_ERROR, "no CUDA device available");
+  }
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) return fail(ELB_GENERAL_ERROR, "cudaGetDevice failed");
+  if (device >= count) return fail(ELB_GENERAL_ERROR, "device %d out of range", device);
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return fail(ELB_UNIMPLEMENTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                                    device, prop.major, prop.minor);
+  return ELB_OK;
+}
+
+int elb_conv_sizes(const elb_conv_desc_t *desc, elb_conv_info_t *info) {
+  if (!desc || !info) return fail(ELB_GENERAL_ERROR, "null argument");
+  int rc = validate_common(*desc);
+  if (rc != ELB_OK) return rc;
+  memset(info, 0, sizeof(*info));
+  compute_sizes(*desc, *info);
+  resolve_algorithm(*desc, info->algorithm, info->tile_size);
+  const char *why;
+  info->kernel = choose_kernel(*desc, info->algorithm, info->tile_size, &why);
+  info->device = desc->device;
+  return ELB_OK;
+}
+
+int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
+  if (!desc || !plan) return fail(ELB_GENERAL_ERROR, "null argument");
+  *plan = nullptr;
+  int rc = validate_common(*desc);
+  if (rc != ELB_OK) return rc;
+  elb_conv_desc_t d = *desc;
+  // bottom/right padding follow from the output size, as the reference does with a warning
+  // (src/eld_conv.cpp:128-139, src/elx_conv.cpp:36-37)
+  {
+    const int need_b = (d.oh - 1) * d.stride_h + d.kh - d.ih - d.pad_t;
+    const int need_r = (d.ow - 1) * d.stride_w + d.kw - d.iw - d.pad_l;
+    d.pad_b = need_b > 0 ? need_b : 0;
+    d.pad_r = need_r > 0 ? need_r : 0;
+  }
+  elb_conv_info_t info;
+  memset(&info, 0, sizeof(info));
+  compute_sizes(d, info);
+  // algorithm choice uses the caller's pads, like the reference
+  resolve_algorithm(*desc, info.algorithm, info.tile_size);
+  const char *why;
+  info.kernel = choose_kernel(d, info.algorithm, info.tile_size, &why);
+  if (info.kernel == ELB_KERNEL_NONE) return fail(ELB_UNIMPLEMENTED, "not implemented on the GPU: %s", why);
+
+  rc = elb_device_supported(d.device);
+  if (rc != ELB_OK) return rc;
+  int dev = d.device;
+  if (dev < 0) cudaGetDevice(&dev);
+  info.device = dev;
+  DeviceGuard guard(dev);
+  if (!guard.ok) return fail(ELB_GENERAL_ERROR, "cannot select device %d", dev);
+
+  elb_conv *pl = new elb_conv();
+  pl->d = d;
+  pl->info = info;
+  pl->device = dev;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { delete pl; return fail(ELB_GENERAL_ERROR, "device query failed"); }
+  pl->num_sms = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&pl->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(&pl->d_status, sizeof(int)) != cudaSuccess ||
+      cudaMemset(pl->d_status, 0, sizeof(int)) != cudaSuccess) {
+    delete pl;
+    return fail(ELB_GENERAL_ERROR, "device allocation failed");
+  }
+  switch (info.kernel) {
+    case ELB_KERNEL_I8_GEMM_UMMA:
+    case ELB_KERNEL_I8_CONV_UMMA:
+    case ELB_KERNEL_I8_SIMT: rc = setup_i8_direct(*pl); break;
+    default: {
+      std::string err;
+      rc = wino_setup(pl->wino, pl->d, pl->info, err);
+      if (rc != ELB_OK) fail(rc, "%s", err.c_str());
+    }
+  }
+  if (rc != ELB_OK) { delete pl; return rc; }
+  *plan = pl;
+  return ELB_OK;
+}
+
+int elb_conv_info(const elb_conv_t *plan, elb_conv_info_t *info) {
+  if (!plan || !info) return fail(ELB_GENERAL_ERROR, "null argument");
+  *info = plan->info;
+  return ELB_OK;
+}
+
+int elb_conv_prepare(elb_conv_t *plan, const void *weights, const void *bias) {
+  if (!plan) return fail(ELB_GENERAL_ERROR, "null plan");
+  DeviceGuard guard(plan->device);
+  return do_prepare(*plan, weights, bias);
+}
+
+int elb_conv_enqueue(elb_conv_t *plan, void *output, const void *input, const void *weights, const void *bias,
+                     void *cuda_stream) {
+  if (!plan || !output || !input) return fail(ELB_GENERAL_ERROR, "null argument");   // src/elx_conv.cpp:218-222
+  DeviceGuard guard(plan->device);
+  int rc = do_prepare(*plan, weights, bias);
+  if (rc != ELB_OK) return rc;
+  return do_enqueue(*plan, output, input, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const void *weights, const void *bias) {
+  if (!plan || !output || !input) return fail(ELB_GENERAL_ERROR, "null argument");
+  elb_conv &pl = *plan;
+  DeviceGuard guard(pl.device);
+  int rc = do_prepare(pl, weights, bias);
+  if (rc != ELB_OK) return rc;
+  const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+  const void *din = input;
+  void *dout = output;
+  if (!in_dev) {
+    if (!pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.info.bytes_input));
+    CUDA_TRY(cudaMemcpyAsync(pl.d_in_stage, input, pl.info.bytes_input, cudaMemcpyHostToDevice, pl.stream));
+    din = pl.d_in_stage;
+  }
+  if (!out_dev) {
+    if (!pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.info.bytes_output));
+    if (pl.d.with_ip_sum)
+      CUDA_TRY(cudaMemcpyAsync(pl.d_out_stage, output, pl.info.bytes_output, cudaMemcpyHostToDevice, pl.stream));
+    dout = pl.d_out_stage;
+  }
+  rc = do_enqueue(pl, dout, din, pl.stream);
+  if (rc != ELB_OK) return rc;
+  if (!out_dev)
+    CUDA_TRY(cudaMemcpyAsync(output, pl.d_out_stage, pl.info.bytes_output, cudaMemcpyDeviceToHost, pl.stream));
+  CUDA_TRY(cudaStreamSynchronize(pl.stream));
+  return check_status(pl);
+}
+
+int elb_conv_set_accumulator_dump(elb_conv_t *plan, void *device_int32) {
+  if (!plan) return fail(ELB_GENERAL_ERROR, "null plan");
+  plan->d_acc_dump = device_int32;
+  return ELB_OK;
+}
+
+int elb_conv_device_status(elb_conv_t *plan) {
+  if (!plan) return -1;
+  DeviceGuard guard(plan->device);
+  int st = -1;
+  if (cudaMemcpy(&st, plan->d_status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return st;
+}
+
+uint64_t elb_conv_launch_count(const elb_conv_t *plan) { return plan ? plan->launches : 0; }
+
+void elb_conv_destroy(elb_conv_t *plan) { delete plan; }
+
+int elb_reorder_nchw_to_nChw16c(void *dst, const void *src, int n, int c, int h, int w, int elem_bytes,
+                                void *cuda_stream) {
+  if (!dst || !src || (elem_bytes != 1 && elem_bytes != 4)) return fail(ELB_GENERAL_ERROR, "bad reorder argument");
+  cudaError_t e = launch_reorder_to_blocked(dst, src, n, c, h, w, elem_bytes, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "reorder launch failed: %s", cudaGetErrorString(e));
+  return ELB_OK;
+}
+
+int elb_reorder_nChw16c_to_nchw(void *dst, const void *src, int n, int c, int h, int w, int elem_bytes,
+                                void *cuda_stream) {
+  if (!dst || !src || (elem_bytes != 1 && elem_bytes != 4)) return fail(ELB_GENERAL_ERROR, "bad reorder argument");
+  cudaError_t e = launch_reorder_from_blocked(dst, src, n, c, h, w, elem_bytes, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "reorder launch failed: %s", cudaGetErrorString(e));
+  return ELB_OK;
+}
+
+// Test hook (not part of the reference surface): runs the bounded-wait self test and returns the
+// status word the kernel wrote (ST_WAIT_TIMEOUT_TEST = 104 when the wait gave up as designed).
+ELB_API int elb_selftest_bounded_wait(int device, unsigned long long limit_ns) {
+  int rc = elb_device_supported(device);
+  if (rc != ELB_OK) return -rc;
+  DeviceGuard guard(device < 0 ? 0 : device);
+  int *st = nullptr, h = -1;
+  if (cudaMalloc(&st, sizeof(int)) != cudaSuccess) return -1;
+  cudaMemset(st, 0, sizeof(int));
+  cudaError_t e = launch_wait_selftest(st, limit_ns, nullptr);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) cudaMemcpy(&h, st, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(st);
+  return e == cudaSuccess ? h : -1;
+}
+
+}  // extern "C"

@@ -1,0 +1,132 @@
+// Shared declarations of the CUDA translation units: kernel parameter blocks, the fused
+// requantisation epilogue, status codes and the launcher prototypes the C-ABI layer calls.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace elb {
+
+constexpr int V = 16;   // channel block of nChw16c / OIhw16i16o
+
+// device status word values (0 = ok)
+enum : int {
+  ST_OK = 0,
+  ST_WAIT_TIMEOUT_PRODUCER = 101,   // producer waited too long for a free shared-memory stage
+  ST_WAIT_TIMEOUT_MMA = 102,        // MMA issuer waited too long for operands or a free accumulator
+  ST_WAIT_TIMEOUT_EPILOGUE = 103,   // epilogue waited too long for an accumulator
+  ST_WAIT_TIMEOUT_TEST = 104        // the deliberate give-up of the wait self-test
+};
+
+enum : int { OUT_F32 = 0, OUT_U8 = 1, OUT_S8 = 2 };
+
+// ---------------------------------------------------------------------------------------------
+// Requantisation of 16 consecutive output channels of one pixel.
+// Arithmetic of the reference's int8 epilogues (src/kernel/elk_u8s8_gemm.hxx:200-256,
+// src/kernel/elk_u8s8_conv.hxx:218-243), in its order:
+//   f = fma((float)acc, scale, shift)            (one fused multiply-add in the reference build)
+//   f = fma((float)prev, sum_scale, f)           if in-place sum (u8/s8 outputs only)
+//   f = min(max(f, relu_lo), relu_hi)            if ReLU
+//   q = round-to-nearest-even(f); u8: values outside [0,255] -> 255 (unsigned saturation of the
+//       int32 bit pattern, so negatives become 255); s8: clamp to [-128,127]
+// ---------------------------------------------------------------------------------------------
+struct Requant {
+  int out_type;
+  int relu;
+  int with_sum;
+  float relu_lo, relu_hi, sum_scale;
+};
+
+__device__ __forceinline__ float requant_one(int acc, float sc, float sh) {
+  return __fmaf_rn(__int2float_rn(acc), sc, sh);
+}
+
+// acc: 16 int32 accumulators; sc/sh: 16 per-channel constants; out/prev: address of the 16-channel
+// group in the output tensor (prev == out for the in-place sum).
+__device__ __forceinline__ void requant_store16(const int (&acc)[16], const float *__restrict__ sc,
+                                                const float *__restrict__ sh, void *out, const Requant &rq) {
+  float f[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) f[i] = requant_one(acc[i], sc[i], sh[i]);
+  if (rq.out_type == OUT_F32) {
+    if (rq.relu) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
+    }
+    float4 *o = reinterpret_cast<float4 *>(out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+    return;
+  }
+  if (rq.with_sum) {
+    const uint4 pv = *reinterpret_cast<const uint4 *>(out);
+    const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+      const float p = rq.out_type == OUT_U8 ? static_cast<float>(b)
+                                            : static_cast<float>(static_cast<int>(static_cast<int8_t>(b)));
+      f[i] = __fmaf_rn(p, rq.sum_scale, f[i]);
+    }
+  }
+  if (rq.relu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
+  }
+  uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    int r = __float2int_rn(f[i]);
+    uint32_t b;
+    if (rq.out_type == OUT_U8) b = (static_cast<uint32_t>(r) > 255u) ? 255u : static_cast<uint32_t>(r);
+    else b = static_cast<uint32_t>(max(-128, min(127, r))) & 0xFFu;
+    w[i >> 2] |= b << (8 * (i & 3));
+  }
+  *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// INT8 direct convolution (1x1 and KxK) parameter block, shared by the tcgen05 kernels and the
+// CUDA-core kernel.
+// ---------------------------------------------------------------------------------------------
+struct I8ConvParams {
+  alignas(64) CUtensorMap tmap[4];   // BOX mode: one map per (row parity, column parity) input plane
+  const uint8_t *in;                 // nChw16c u8
+  const int8_t *wpack;               // UMMA operand image [n_tile][k_stage][KC][BN][16]
+  const int8_t *wplain;              // [OCpad][taps][ICpad] (CUDA-core kernel)
+  const float *scale;                // [OCpad] folded iS*Sw(/oS)
+  const float *shift;                // [OCpad] folded bias/oS + oz - ...
+  void *out;                         // nChw16c u8 / s8 / f32
+  int32_t *acc_dump;                 // optional raw accumulators, nChw16c int32
+  int *status;
+  Requant rq;
+  int N, IH, IW, OH, OW, KH, KW, stride, pad_t, pad_l;
+  int CB, OCB;                       // channel blocks of 16 (input / output)
+  int M, HW;                         // FLAT mode: M = N*OH*OW rows, HW = OH*OW
+  int taps, CBG, k_stages;           // K loop: stage = (tap, group of KC channel blocks)
+  int n_tiles, m_tiles;
+  int BW, BH, tiles_w, tiles_h;      // BOX mode tile = BH x BW output pixels (BH*BW = 128)
+};
+
+enum : int { I8_MODE_FLAT = 0, I8_MODE_BOX = 1 };
+
+// geometry the host needs to pack weights / size grids for the tcgen05 kernels
+struct I8UmmaConfig {
+  int BN, KC, STAGES, mode;
+  size_t smem_bytes;
+};
+I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode);
+cudaError_t launch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s);
+cudaError_t launch_i8_simt(const I8ConvParams &p, cudaStream_t s);
+
+// Bounded-wait self test: one CTA waits on an mbarrier nobody arrives at, gives up after
+// `limit_ns`, writes ST_WAIT_TIMEOUT_TEST to *status and returns normally.
+cudaError_t launch_wait_selftest(int *status, unsigned long long limit_ns, cudaStream_t s);
+
+// layout converters
+cudaError_t launch_reorder_to_blocked(void *dst, const void *src, int n, int c, int h, int w, int eb,
+                                      cudaStream_t s);
+cudaError_t launch_reorder_from_blocked(void *dst, const void *src, int n, int c, int h, int w, int eb,
+                                        cudaStream_t s);
+
+}  // namespace elb

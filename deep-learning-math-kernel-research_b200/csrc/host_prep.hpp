@@ -1,0 +1,129 @@
+// Host-side, one-time weight preparation: quantisation and constant folding in exactly the
+// reference's fp32 association order, and packing into the operand images the kernels copy with
+// single bulk TMA transfers.  Plain scalar C++ on purpose: these few thousand operations define
+// bit-exactness of every later output, so nothing here may be re-associated or fused except where
+// the reference build itself fuses (written as an explicit fmaf).
+#pragma once
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+namespace elb {
+namespace host {
+
+inline int alignup(int x, int a) { return (x + a - 1) / a * a; }
+
+// OIhw16i16o index: [O/16][I/16][kh][kw][16 i][16 o]   (reference: src/elx_conv.hpp:10-12)
+inline size_t w_index(int I2, int KH, int KW, int o, int i, int kh, int kw) {
+  return (((((size_t)(o / 16) * I2 + i / 16) * KH + kh) * KW + kw) * 16 + i % 16) * 16 + o % 16;
+}
+
+struct I8Weights {
+  int OCP = 0, ICP = 0, taps = 0;
+  std::vector<int8_t> q;        // [OCP][taps][ICP]
+  std::vector<float> absmax;    // [OCP]
+  std::vector<int32_t> qsum;    // [OCP] sum of q over all taps and channels
+};
+
+// Per output channel: absmax over the real input channels and all taps; q = rne((w*127)/absmax)
+// (multiply, then divide), padded lanes 0.
+// Reference: src/elx_int8_conv_direct_1x1.cpp:239-295, src/elx_int8_conv_direct.cpp:430-475.
+inline I8Weights quantize_weights_i8(const float *w, int oc, int ic, int kh, int kw) {
+  I8Weights r;
+  r.OCP = alignup(oc, 16);
+  r.ICP = alignup(ic, 16);
+  r.taps = kh * kw;
+  const int I2 = r.ICP / 16;
+  r.q.assign((size_t)r.OCP * r.taps * r.ICP, 0);
+  r.absmax.assign(r.OCP, 0.0f);
+  r.qsum.assign(r.OCP, 0);
+  for (int o = 0; o < r.OCP; ++o) {
+    float m = 0.0f;
+    for (int i = 0; i < ic; ++i)
+      for (int a = 0; a < kh; ++a)
+        for (int b = 0; b < kw; ++b) {
+          const float v = std::fabs(w[w_index(I2, kh, kw, o, i, a, b)]);
+          if (v > m) m = v;
+        }
+    r.absmax[o] = m;
+    if (m == 0.0f) continue;
+    int32_t s = 0;
+    for (int a = 0; a < kh; ++a)
+      for (int b = 0; b < kw; ++b)
+        for (int i = 0; i < ic; ++i) {
+          volatile float t = w[w_index(I2, kh, kw, o, i, a, b)] * 127.0f;   // volatile: keep the two
+          volatile float u = t / m;                                        // roundings separate
+          const int8_t qv = (int8_t)std::nearbyintf(u);
+          r.q[((size_t)o * r.taps + a * kw + b) * r.ICP + i] = qv;
+          s += qv;
+        }
+    r.qsum[o] = s;
+  }
+  return r;
+}
+
+// scale / shift of the requantising epilogue.
+// Reference: src/elx_int8_conv_direct_1x1.cpp:316-353, src/elx_int8_conv_direct.cpp:357-419.
+//   u8/s8 out: scale = (iS*Sw)*(1/oS); shift = fma(bias, 1/oS, oz) - (iz*Sq)*scale [- sum_z*sum_S]
+//   f32  out: scale =  iS*Sw;         shift = bias - (iz*Sq)*scale
+inline void fold_constants_i8(const I8Weights &wq, const float *bias, bool with_bias, bool out_f32,
+                              float iS, float iz, float oS, float oz, bool with_sum, float sum_S,
+                              float sum_z, std::vector<float> &scale, std::vector<float> &shift) {
+  scale.assign(wq.OCP, 0.0f);
+  shift.assign(wq.OCP, 0.0f);
+  volatile float orepS = 1.0f / oS;
+  for (int o = 0; o < wq.OCP; ++o) {
+    volatile float Sw = wq.absmax[o] / 127.0f;
+    const float b = (with_bias && bias) ? bias[o] : 0.0f;
+    volatile float sc, sh;
+    if (out_f32) {
+      sc = iS * Sw;
+      sh = b;
+    } else {
+      volatile float t = iS * Sw;
+      sc = t * orepS;
+      sh = std::fmaf(b, orepS, oz);
+    }
+    if (iz != 0.0f) {
+      volatile float zq = iz * (float)wq.qsum[o];
+      volatile float zs = zq * sc;
+      sh = sh - zs;
+    }
+    if (with_sum && !out_f32) {
+      volatile float ss = sum_z * sum_S;
+      sh = sh - ss;
+    }
+    scale[o] = sc;
+    shift[o] = sh;
+  }
+}
+
+// Operand image of B for the tcgen05 kernels: [n_tile][k_stage][KC chunks][BN rows][16 bytes],
+// k_stage = tap*CBG + g, chunk j of a stage = channel block g*KC + j, zero where out of range.
+inline std::vector<int8_t> pack_b_i8(const I8Weights &wq, int BN, int KC, int &n_tiles, int &CBG,
+                                     int &k_stages) {
+  const int CB = wq.ICP / 16;
+  n_tiles = (wq.OCP + BN - 1) / BN;
+  CBG = (CB + KC - 1) / KC;
+  k_stages = wq.taps * CBG;
+  std::vector<int8_t> out((size_t)n_tiles * k_stages * KC * BN * 16, 0);
+  for (int nt = 0; nt < n_tiles; ++nt)
+    for (int ks = 0; ks < k_stages; ++ks) {
+      const int tap = ks / CBG, g = ks % CBG;
+      for (int j = 0; j < KC; ++j) {
+        const int cb = g * KC + j;
+        if (cb >= CB) continue;
+        for (int r = 0; r < BN; ++r) {
+          const int o = nt * BN + r;
+          if (o >= wq.OCP) continue;
+          int8_t *dst = &out[((((size_t)nt * k_stages + ks) * KC + j) * BN + r) * 16];
+          std::memcpy(dst, &wq.q[((size_t)o * wq.taps + tap) * wq.ICP + cb * 16], 16);
+        }
+      }
+    }
+  return out;
+}
+
+}  // namespace host
+}  // namespace elb

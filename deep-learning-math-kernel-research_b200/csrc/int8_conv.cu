@@ -1,0 +1,383 @@
+// INT8 (u8 activations x s8 weights -> s32) direct convolution for sm_100a.
+//
+// Replaces the reference's elx_int8_conv_direct_1x1_t (src/elx_int8_conv_direct_1x1.cpp:409-480,
+// src/elx_int8_conv_direct_1x1_xopt.hpp:20-101), elx_int8_conv_direct_t
+// (src/elx_int8_conv_direct.cpp:502-571, src/elx_int8_conv_direct_xopt.hpp:20-110) and the
+// micro-kernels under them (src/kernel/elk_u8s8_gemm.hxx:269-406, src/kernel/elk_u8s8_conv.hxx:254-677).
+//
+// i8_umma_kernel: implicit GEMM  D[pixel][oc] = sum_k A[pixel][k] * B[oc][k]  on tcgen05 tensor
+// cores.  One CTA = 6 warps with fixed roles:
+//   warp 0      producer: TMA copies global -> shared, STAGES-deep ring, mbarrier complete_tx
+//   warp 1      allocates TMEM; lane 0 issues tcgen05.mma (kind::i8, M=128, N=BN, K=32 per
+//               instruction) and commits to the ring's "empty" barriers / the accumulator barrier
+//   warps 2..5  epilogue: tcgen05.ld the s32 accumulators (one pixel per thread), fused
+//               scale/shift/sum/ReLU/requantise, 16-byte stores into nChw16c
+// Two TMEM accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1.  The grid
+// is persistent: min(#tiles, #SMs) CTAs walk the tile list with stride gridDim.x.
+//
+// Operand layout in shared memory (both K-major, no swizzle): [K chunk of 16 B][row][16 B], i.e.
+// 8 rows x 16 B core matrices; rows of A are output pixels, rows of B are output channels.  The
+// nChw16c activation layout already IS that layout: 16 channels of one pixel are 16 contiguous
+// bytes and consecutive pixels are consecutive 16-byte groups, so
+//   FLAT mode (1x1, stride 1, no padding): a K chunk of a 128-pixel tile is one or two contiguous
+//        runs of global memory -> plain bulk copies;
+//   BOX mode (KxK, padding, stride 1|2): the tile is a BH x BW rectangle of output pixels and a K
+//        chunk is a (16 B, BW, BH) box of the input plane shifted by the filter tap -> one tiled
+//        TMA copy per stage, out-of-image taps arrive as zeros from the TMA unit.  Stride 2 is
+//        handled by four tensor maps, one per (row, column) parity plane of the input.
+// Weights are packed once on the host into exactly the shared-memory image of each
+// (oc tile, K stage), so a stage of B is a single contiguous bulk copy.
+#include "elb_common.cuh"
+#include "umma.cuh"
+
+namespace elb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_OC_SMEM = 2048;    // per-channel constants cached in shared memory
+
+__device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
+  return d;
+}
+
+template <int BN, int KC, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = KC * BM * 16;
+  static constexpr int B_BYTES = KC * BN * 16;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = RING_BYTES;                       // full[S], empty[S], tfull[2], tempty[2]
+  static constexpr int MISC_OFF = BAR_OFF + (2 * STAGES + 4) * 8;  // tmem slot, abort flag
+  static constexpr int CONST_OFF = (MISC_OFF + 16 + 15) / 16 * 16; // scale[MAX_OC_SMEM], shift[MAX_OC_SMEM]
+  static constexpr int TOTAL = CONST_OFF + 2 * MAX_OC_SMEM * 4 + 128;   // +128: manual alignment slack
+};
+
+template <int BN, int KC, int STAGES, int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_constant__ I8ConvParams p) {
+  using L = SmemLayout<BN, KC, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+  uint64_t *empty = full + STAGES;
+  uint64_t *tfull = empty + STAGES;
+  uint64_t *tempty = tfull + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::MISC_OFF);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFF + 4);
+  float *s_scale = reinterpret_cast<float *>(smem + L::CONST_OFF);
+  float *s_shift = s_scale + MAX_OC_SMEM;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulator buffers (power of two >= 32)
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 4 * 32);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  for (int i = threadIdx.x; i < p.OCB * V; i += NUM_THREADS) {
+    s_scale[i] = p.scale[i];
+    s_shift[i] = p.shift[i];
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  int fail_code = 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (MODE == I8_MODE_BOX && lane == 0) {
+      for (int i = 0; i < p.stride * p.stride; ++i) tma_prefetch_desc(&p.tmap[i]);
+    }
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+      // tile geometry
+      int n0 = 0, p0 = 0, rows = BM, oh0 = 0, ow0 = 0;
+      if (MODE == I8_MODE_FLAT) {
+        const int m0 = mt * BM;
+        rows = min(BM, p.M - m0);
+        n0 = m0 / p.HW;
+        p0 = m0 - n0 * p.HW;
+      } else {
+        const int per_img = p.tiles_h * p.tiles_w;
+        n0 = mt / per_img;
+        const int r = mt - n0 * per_img;
+        oh0 = (r / p.tiles_w) * p.BH;
+        ow0 = (r % p.tiles_w) * p.BW;
+      }
+      for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+        uint8_t *a_dst = smem + s * L::STAGE_BYTES;
+        uint8_t *b_dst = a_dst + L::A_BYTES;
+        const int tap = ks / p.CBG, g = ks - tap * p.CBG;
+        const int cb0 = g * KC;
+        const int8_t *b_src = p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES;
+        if (MODE == I8_MODE_FLAT) {
+          const int nchunks = min(KC, p.CB - cb0);
+          if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(nchunks * rows * 16 + L::B_BYTES));
+          __syncwarp();
+          if (lane < nchunks) {
+            // rows [0, rows) of the tile = pixels p0.. of image n0, continuing into the next images
+            int done = 0, n = n0, pp = p0;
+            while (done < rows) {
+              const int len = min(rows - done, p.HW - pp);
+              const uint8_t *src = p.in + ((static_cast<size_t>(n) * p.CB + cb0 + lane) * p.HW + pp) * 16;
+              tma_bulk_g2s(a_dst + lane * (BM * 16) + done * 16, src, static_cast<uint32_t>(len * 16), &full[s]);
+              done += len;
+              pp = 0;
+              ++n;
+            }
+          } else if (lane == KC) {
+            tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
+          }
+        } else {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(L::A_BYTES + L::B_BYTES));
+            // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
+            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            const int eh = kh - p.pad_t, ew = kw - p.pad_l;
+            const int dh = (eh >= 0) ? eh / p.stride : -((-eh + p.stride - 1) / p.stride);
+            const int dw = (ew >= 0) ? ew / p.stride : -((-ew + p.stride - 1) / p.stride);
+            const int par_h = eh - dh * p.stride, par_w = ew - dw * p.stride;
+            const CUtensorMap *tm = &p.tmap[par_h * p.stride + par_w];
+            tma_tile_5d(a_dst, tm, 0, ow0 + dw, oh0 + dh, cb0, n0, &full[s]);
+            tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC = umma_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b s8*/ 1, BM, BN);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
+        if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + b * BN;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+          for (int k2 = 0; k2 < KC / 2; ++k2) {
+            const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 2 * (BM * 16), BM * 16, 128);
+            const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * (BN * 16), BN * 16, 128);
+            umma_i8(d_tmem, ad, bd, IDESC, (ks | k2) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&tfull[b]);  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter ..
+    const int row = quarter * 32 + lane;
+    const int elt = p.rq.out_type == OUT_F32 ? 4 : 1;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+      const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
+      // where does this thread's pixel live?
+      bool valid;
+      size_t pix_off;      // element offset of channel-block 0 of this pixel, in units of 16 channels
+      size_t blk_stride;   // distance between channel blocks, same units
+      if (MODE == I8_MODE_FLAT) {
+        const int m = mt * BM + row;
+        valid = m < p.M;
+        const int n = m / p.HW, pp = m - n * p.HW;
+        pix_off = static_cast<size_t>(n) * p.OCB * p.HW + pp;
+        blk_stride = p.HW;
+      } else {
+        const int per_img = p.tiles_h * p.tiles_w;
+        const int n = mt / per_img;
+        const int r = mt - n * per_img;
+        const int oh = (r / p.tiles_w) * p.BH + row / p.BW;
+        const int ow = (r % p.tiles_w) * p.BW + row % p.BW;
+        valid = oh < p.OH && ow < p.OW;
+        pix_off = (static_cast<size_t>(n) * p.OCB * p.OH + oh) * p.OW + ow;
+        blk_stride = static_cast<size_t>(p.OH) * p.OW;
+      }
+      if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * BN;
+#pragma unroll 1
+      for (int ob = 0; ob < BN / 16; ++ob) {
+        uint32_t r[16];
+        tmem_ld16(t_addr + ob * 16, r);
+        tmem_ld_wait();
+        const int ocb = nt * (BN / 16) + ob;
+        if (valid && ocb < p.OCB) {
+          int acc[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = static_cast<int>(r[i]);
+          const size_t off = (pix_off + ocb * blk_stride) * 16;
+          if (p.acc_dump) {
+            int4 *d = reinterpret_cast<int4 *>(p.acc_dump + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d[i] = make_int4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+          }
+          requant_store16(acc, s_scale + ocb * 16, s_shift + ocb * 16,
+                          static_cast<uint8_t *>(p.out) + off * elt, p.rq);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty[b]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (fail_code != 0) atomicCAS(p.status, 0, fail_code);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CUDA-core kernel: one thread = one output pixel x 16 output channels, dp4a over the K loop.
+// Serves shapes the tensor-core kernels do not take (few channels, odd geometry) and is the
+// on-device cross-check of the tcgen05 path in the tests.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) i8_simt_kernel(const __grid_constant__ I8ConvParams p) {
+  const long long total = static_cast<long long>(p.N) * p.OH * p.OW;
+  const long long m = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int ocb = blockIdx.y;
+  if (m >= total) return;
+  const int n = static_cast<int>(m / (p.OH * p.OW));
+  const int rem = static_cast<int>(m - static_cast<long long>(n) * p.OH * p.OW);
+  const int oh = rem / p.OW, ow = rem - oh * p.OW;
+  const int ICP = p.CB * 16;
+  int acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0;
+  for (int kh = 0; kh < p.KH; ++kh) {
+    const int ih = oh * p.stride - p.pad_t + kh;
+    if (ih < 0 || ih >= p.IH) continue;
+    for (int kw = 0; kw < p.KW; ++kw) {
+      const int iw = ow * p.stride - p.pad_l + kw;
+      if (iw < 0 || iw >= p.IW) continue;
+      const int tap = kh * p.KW + kw;
+      for (int cb = 0; cb < p.CB; ++cb) {
+        const uint4 a = *reinterpret_cast<const uint4 *>(
+            p.in + (((static_cast<size_t>(n) * p.CB + cb) * p.IH + ih) * p.IW + iw) * 16);
+#pragma unroll
+        for (int o = 0; o < 16; ++o) {
+          const uint4 w = __ldg(reinterpret_cast<const uint4 *>(
+              p.wplain + (static_cast<size_t>(ocb * 16 + o) * p.taps + tap) * ICP + cb * 16));
+          int c = acc[o];
+          c = dp4a_us(a.x, w.x, c);
+          c = dp4a_us(a.y, w.y, c);
+          c = dp4a_us(a.z, w.z, c);
+          c = dp4a_us(a.w, w.w, c);
+          acc[o] = c;
+        }
+      }
+    }
+  }
+  const size_t off = (((static_cast<size_t>(n) * p.OCB + ocb) * p.OH + oh) * p.OW + ow) * 16;
+  if (p.acc_dump) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) p.acc_dump[off + i] = acc[i];
+  }
+  const int elt = p.rq.out_type == OUT_F32 ? 4 : 1;
+  requant_store16(acc, p.scale + ocb * 16, p.shift + ocb * 16, static_cast<uint8_t *>(p.out) + off * elt, p.rq);
+}
+
+__global__ void wait_selftest_kernel(int *status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+    const unsigned long long t0 = global_timer_ns();
+    bool done = false;
+    while (!done) {
+      if (mbar_try_wait(&bar, 0)) break;               // never true: nobody arrives
+      if (global_timer_ns() - t0 > limit_ns) done = true;
+    }
+    if (done) *status = ST_WAIT_TIMEOUT_TEST;
+    mbar_inval(&bar);
+  }
+}
+
+template <int BN, int KC, int STAGES, int MODE>
+cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s) {
+  using L = SmemLayout<BN, KC, STAGES>;
+  auto kern = i8_umma_kernel<BN, KC, STAGES, MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  if (e != cudaSuccess) return e;
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// Tile configuration: BN = 128 output channels per tile when OC allows it (two N tiles give the
+// persistent grid more tiles to balance), 8 K-chunks (128 bytes of K) per stage.
+I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
+  I8UmmaConfig c;
+  c.mode = mode;
+  c.BN = (ocb * 16 >= 128) ? 128 : 64;
+  c.KC = 8;
+  c.STAGES = 6;
+  (void)cb; (void)taps;
+  c.smem_bytes = c.BN == 128 ? SmemLayout<128, 8, 6>::TOTAL : SmemLayout<64, 8, 6>::TOTAL;
+  return c;
+}
+
+cudaError_t launch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s) {
+  if (p.OCB * V > MAX_OC_SMEM) return cudaErrorInvalidValue;
+  if (cfg.mode == I8_MODE_FLAT) {
+    if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_FLAT>(p, num_sms, s);
+    return launch_cfg<64, 8, 6, I8_MODE_FLAT>(p, num_sms, s);
+  }
+  if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_BOX>(p, num_sms, s);
+  return launch_cfg<64, 8, 6, I8_MODE_BOX>(p, num_sms, s);
+}
+
+cudaError_t launch_i8_simt(const I8ConvParams &p, cudaStream_t s) {
+  const long long total = static_cast<long long>(p.N) * p.OH * p.OW;
+  dim3 grid(static_cast<unsigned>((total + 127) / 128), static_cast<unsigned>(p.OCB));
+  i8_simt_kernel<<<grid, 128, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_selftest(int *status, unsigned long long limit_ns, cudaStream_t s) {
+  wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_ns);
+  return cudaGetLastError();
+}
+
+}  // namespace elb

@@ -1,0 +1,162 @@
+/*
+ * euler_b200.h -- C ABI of the B200 (sm_100a) convolution library.
+ *
+ * This is the boundary a host-language binding (C++, ctypes, cgo, JNI ...) talks to.  It carries
+ * the same information as the reference's C++ descriptor `euler::eld_conv_t` and the same two-step
+ * protocol (describe + set up once, then execute many times), but with plain C types only: no
+ * std::string, no C++ classes, no torch types.  `include/euler.hpp` in this repository implements
+ * the reference's C++ surface (eld_conv_t::setup / elx_conv) on top of these functions.
+ *
+ * Each entry point names the reference interface it replaces (file:line in the reference project).
+ *
+ * Pointers passed to elb_conv_execute may be host or device memory (detected per call); pointers
+ * passed to elb_conv_enqueue must be device memory of the plan's device.  Tensor layouts are the
+ * reference's blocked layouts: nChw16c activations, OIhw16i16o weights (goihw for depthwise),
+ * fp32 bias of ALIGNUP(oc,16) elements.
+ */
+#ifndef EULER_B200_H_
+#define EULER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ELB_API __attribute__((visibility("default")))
+
+/* Return codes: numerically equal to ELD_OK/ELD_UNIMPLEMENTED/ELD_GENERAL_ERROR and
+ * ELX_OK/ELX_UNIMPLEMENTED/ELX_GENERAL_ERROR (include/euler.hpp:45-56). */
+enum { ELB_OK = 0, ELB_UNIMPLEMENTED = 1, ELB_GENERAL_ERROR = 2 };
+
+/* Algorithms (include/euler.hpp:35-42). */
+enum {
+  ELB_CONV_AUTO = 0, ELB_CONV_DIRECT_1X1 = 1, ELB_CONV_DIRECT = 2, ELB_CONV_DIRECT_VMG = 3,
+  ELB_CONV_WINOGRAD = 4, ELB_DECONV_DIRECT = 5
+};
+/* Element types (include/euler.hpp:66-73). */
+enum { ELB_DT_UNDEF = 0, ELB_F32 = 1, ELB_F16 = 2, ELB_U8 = 3, ELB_S8 = 4, ELB_S32 = 5 };
+/* Tensor formats (include/euler.hpp:75-89). */
+enum {
+  ELB_FMT_UNDEF = 0, ELB_NCHW, ELB_NHWC, ELB_NCHW16C, ELB_NCHW8C, ELB_OIHW, ELB_HWIO, ELB_OIHW16I16O,
+  ELB_OIHW8I8O, ELB_GOIHW, ELB_GHWIO, ELB_GOIHW16I16O, ELB_GOIHW8I8O
+};
+/* Propagation kinds (include/euler.hpp:92-97); only forward_inference is implemented. */
+enum { ELB_FORWARD_TRAINING = 0, ELB_FORWARD_INFERENCE = 1, ELB_BACKWARD_DATA = 2, ELB_BACKWARD_WEIGHTS = 3 };
+/* Quantisation sampling kinds (include/euler.hpp:99-103). */
+enum { ELB_FINE = 0, ELB_COARSE = 1, ELB_CALIBRATED = 2 };
+
+/* Plain-C mirror of euler::eld_conv_t (include/euler.hpp:110-187).  Tuning knobs of the CPU
+ * implementation (flatting / blocking / partition / nthreads / streaming_hint) have no meaning on
+ * the GPU and are not part of this struct; execution_mode is carried only to be validated. */
+typedef struct elb_conv_desc {
+  int32_t n, g, ic, oc, ih, iw, oh, ow, kh, kw;        /* dims                      :113-115 */
+  int32_t pad_l, pad_r, pad_t, pad_b;                  /* pads                      :116     */
+  int32_t stride_h, stride_w;                          /* strides                   :117     */
+  int32_t dilation_h, dilation_w;                      /* dilations                 :118     */
+  int32_t dt_input, dt_weights, dt_output, dt_bias;    /* data_type                 :121-126 */
+  int32_t fmt_input, fmt_weights, fmt_output;          /* formats                   :131     */
+  int32_t prop_kind;                                   /*                           :134     */
+  int32_t algorithm, tile_size;                        /*                           :137-138 */
+  int32_t with_relu, with_bias, with_ip_sum, with_op_sum, with_argmax;   /*         :140-144 */
+  int32_t f16c_opt, disable_autoparam;                 /*                           :145,148 */
+  float relu_lower, relu_upper;                        /* relu_bound                :150     */
+  int32_t execution_mode;                              /*                           :156     */
+  float input_scale, input_z;                          /* input_quant               :168     */
+  float tinput_scale, tinput_z;                        /* wino_tinput_quant         :168     */
+  float output_scale, output_z;                        /* output_quant              :168     */
+  float sum_scale, sum_z;                              /* sum_quant                 :168     */
+  int32_t sampling_kind;                               /*                           :169     */
+  int32_t device;                                      /* CUDA device ordinal; -1 = current device */
+} elb_conv_desc_t;
+
+/* What setup() computes (include/euler.hpp:181-183 byte_sizes / sizes) plus what it chose. */
+typedef struct elb_conv_info {
+  int32_t algorithm;          /* resolved from ELB_CONV_AUTO                    src/eld_conv.cpp:148-159 */
+  int32_t tile_size;          /* resolved Winograd tile (6 = F(4x4,3x3))        src/eld_conv.cpp:231-236 */
+  int32_t kernel;             /* ELB_KERNEL_* below                                                   */
+  int32_t device;
+  uint64_t size_input, size_weights, size_output, size_bias;           /* elements, src/eld_conv.cpp:99-112 */
+  uint64_t bytes_input, bytes_weights, bytes_output, bytes_bias;       /* bytes,    src/eld_conv.cpp:123-126 */
+  uint64_t workspace_bytes;   /* device memory the plan holds (packed weights, constants, t-buffers) */
+  int32_t launches_per_call;  /* kernels one steady-state execute launches */
+  int32_t reserved;
+} elb_conv_info_t;
+
+enum {
+  ELB_KERNEL_NONE = 0,
+  ELB_KERNEL_I8_GEMM_UMMA = 1,      /* int8 1x1: tcgen05 kind::i8, TMEM s32 accumulators            */
+  ELB_KERNEL_I8_CONV_UMMA = 2,      /* int8 KxK implicit GEMM: TMA-tiled operand fetch + tcgen05     */
+  ELB_KERNEL_I8_SIMT = 3,           /* int8 any shape: dp4a CUDA-core kernel (small / odd shapes)    */
+  ELB_KERNEL_WINO_F32_UMMA = 4,     /* fp32 F(4x4,3x3): transforms + 3xTF32 tcgen05 batched GEMM     */
+  ELB_KERNEL_WINO_I8_UMMA = 5,      /* int8 F(4x4,3x3): quantising transforms + tcgen05 kind::i8     */
+  ELB_KERNEL_I8_DEPTHWISE = 6       /* int8 depthwise 3x3: bandwidth-bound dp4a kernel               */
+};
+
+typedef struct elb_conv elb_conv_t;      /* the plan; replaces `elx_conv_t *xc` (include/euler.hpp:186) */
+
+/* Sizes and algorithm choice only -- replaces eld_conv_t::setup(false) (src/eld_conv.cpp:59-163). */
+ELB_API int elb_conv_sizes(const elb_conv_desc_t *desc, elb_conv_info_t *info);
+
+/* Validate, choose the kernel and build the plan -- replaces eld_conv_t::setup(true)
+ * (src/eld_conv.cpp:59-316) and the elx_*_t constructors it calls.  Unsupported descriptors return
+ * ELB_UNIMPLEMENTED (there is no CPU fallback); the reference would abort() through el_error. */
+ELB_API int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan);
+
+ELB_API int elb_conv_info(const elb_conv_t *plan, elb_conv_info_t *info);
+
+/* Run the convolution and wait for it -- replaces elx_conv(desc, output, input, weights, bias)
+ * (include/euler.hpp:190, src/elx_conv.cpp:213-240) with eager_mode = true.  As in the reference,
+ * weights and bias are read on the FIRST call only (quantised / transformed / packed into the
+ * plan's workspace); later calls ignore them.  `output` is also read when with_ip_sum is set.
+ * Host pointers are staged through the plan's device buffers inside this call. */
+ELB_API int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const void *weights,
+                             const void *bias);
+
+/* Same work, device pointers only, enqueued on `cuda_stream` (a cudaStream_t; NULL = default
+ * stream) without waiting -- the eager_mode = false path (src/elx_conv.cpp:228-236,
+ * src/elx_stream.cpp:54-62).  The first-call weight preparation is still done synchronously. */
+ELB_API int elb_conv_enqueue(elb_conv_t *plan, void *output, const void *input, const void *weights,
+                             const void *bias, void *cuda_stream);
+
+/* Do the first-call weight preparation now -- the `setup_workspace` step of the reference
+ * (src/elx_conv.hpp:130-145) made explicit so that callers can keep it out of a timed region. */
+ELB_API int elb_conv_prepare(elb_conv_t *plan, const void *weights, const void *bias);
+
+/* Parity hook: when set (device pointer to int32, output-tensor shape nChw16c, or [36][tiles][OC]
+ * for Winograd), integer kernels also store their raw int32 accumulators there.  NULL switches it
+ * off.  The reference keeps the same values in its `toutput` scratch (src/kernel/elk_u8s8_gemm.hxx:146-166). */
+ELB_API int elb_conv_set_accumulator_dump(elb_conv_t *plan, void *device_int32);
+
+/* Device-side status word of the last launch: 0 = ok, otherwise the code of the bounded wait that
+ * gave up (see csrc/elb_common.cuh).  Also returned as ELB_GENERAL_ERROR by execute. */
+ELB_API int elb_conv_device_status(elb_conv_t *plan);
+
+/* Number of kernels this plan has launched since it was created. */
+ELB_API uint64_t elb_conv_launch_count(const elb_conv_t *plan);
+
+/* Release the plan and its device memory -- replaces ~eld_conv_t / ~elx_conv_t
+ * (src/eld_conv.cpp:52-57, src/elx_conv.cpp:168-188). */
+ELB_API void elb_conv_destroy(elb_conv_t *plan);
+
+/* Message of the last failure on the calling thread ("" if none); the text the reference would
+ * have printed through el_error / el_warn (src/common/el_log.cpp:7-25). */
+ELB_API const char *elb_last_error(void);
+
+/* Library / device probe -- replaces the AVX-512 check in setup (src/eld_conv.cpp:62-72,
+ * src/common/el_isa.hpp:31-70): returns ELB_OK when `device` is an sm_100 GPU. */
+ELB_API int elb_device_supported(int device);
+
+/* Layout converters on the device -- replace reorder<T, dst, src> (include/euler_reorder.hpp:9-64,
+ * src/elx_reorder.cpp:11-207) for the two conversions callers with plain tensors need.
+ * elem_bytes is 1 or 4.  Pointers are device pointers; stream may be NULL. */
+ELB_API int elb_reorder_nchw_to_nChw16c(void *dst, const void *src, int n, int c, int h, int w,
+                                        int elem_bytes, void *cuda_stream);
+ELB_API int elb_reorder_nChw16c_to_nchw(void *dst, const void *src, int n, int c, int h, int w,
+                                        int elem_bytes, void *cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EULER_B200_H_ */

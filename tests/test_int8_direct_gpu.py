@@ -1,0 +1,146 @@
+"""GPU parity of the INT8 direct convolution kernels (1x1 and KxK) against the CPU restatement.
+
+Everything here is bit-exact: u8/s8 outputs and raw int32 accumulators must equal the oracle's.
+The calls go through the C-ABI (elb_conv_create / elb_conv_execute) exactly as a host binding would.
+"""
+import dataclasses
+import os
+
+import numpy as np
+import pytest
+
+import refutil as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(name, n, ic, oc, ih, iw, **kw):
+    kw.setdefault("types", "u8f32u8f32")
+    kw.setdefault("relu", True)
+    kw.setdefault("bias", True)
+    return R.ConvCase(name, n, ic, oc, ih, iw, **kw)
+
+
+FLAT_CASES = [
+    _case("flat_c2_small", 2, 1024, 256, 14, 14, kh=1, kw=1, pad=0, algo="1x1"),
+    _case("flat_ragged_m", 3, 64, 64, 7, 7, kh=1, kw=1, pad=0, algo="1x1"),            # M=147, tiles span 3 images
+    _case("flat_partial_stage", 2, 48, 32, 9, 5, kh=1, kw=1, pad=0, algo="1x1"),        # CB=3 < KC, BN=64
+    _case("flat_pad_lanes", 2, 40, 24, 6, 6, kh=1, kw=1, pad=0, algo="1x1"),            # ic, oc not multiples of 16
+    _case("flat_oc192", 1, 160, 192, 12, 12, kh=1, kw=1, pad=0, algo="1x1"),            # OC not multiple of BN
+    _case("flat_s8_norelu", 2, 128, 64, 8, 8, kh=1, kw=1, pad=0, algo="1x1", types="u8f32s8f32", relu=False,
+          oscale=4.0),
+    _case("flat_u8_norelu_oz", 2, 128, 64, 8, 8, kh=1, kw=1, pad=0, algo="1x1", relu=False, oscale=4.0, oz=128.0),
+    _case("flat_f32_out", 2, 128, 64, 8, 8, kh=1, kw=1, pad=0, algo="1x1", types="u8f32f32f32"),
+    _case("flat_sum", 2, 256, 128, 10, 10, kh=1, kw=1, pad=0, algo="1x1", sum=True, sscale=0.5, oscale=0.5),
+    _case("flat_single_pixel", 1, 16, 16, 1, 1, kh=1, kw=1, pad=0, algo="1x1"),
+    _case("flat_many_tiles", 5, 32, 16, 56, 56, kh=1, kw=1, pad=0, algo="1x1"),         # 123 tiles: persistent loop
+]
+
+BOX_CASES = [
+    _case("box_3x3_s1", 2, 32, 64, 14, 14, algo="direct"),
+    _case("box_c3_small", 2, 128, 256, 56, 56, stride=2, algo="direct"),
+    _case("box_3x3_odd", 2, 16, 16, 13, 11, algo="direct"),
+    _case("box_3x3_s2_odd", 1, 48, 32, 15, 9, stride=2, algo="direct"),
+    _case("box_1x1_s2", 2, 64, 128, 14, 14, kh=1, kw=1, pad=0, stride=2, algo="direct"),
+    _case("box_3x3_pad0", 1, 32, 32, 10, 10, pad=0, algo="direct"),
+    _case("box_5x5", 1, 16, 32, 12, 12, kh=5, kw=5, pad=2, algo="direct"),
+    _case("box_3x3_s8", 1, 32, 32, 8, 8, algo="direct", types="u8f32s8f32", relu=False, oscale=8.0),
+    _case("box_3x3_224", 1, 16, 16, 224, 224, algo="direct"),                          # exact 32x4 tiling
+]
+
+
+def _check(case, kernel_expected=None, host_buffers=False):
+    import gpuutil as G
+    t = R.make_tensors(case)
+    want, want_acc = R.oracle_int8_conv(case, t, want_acc=True)
+    got, d, acc = G.run_gpu(case, t, want_acc=True, host_buffers=host_buffers)
+    try:
+        if kernel_expected:
+            assert d.kernel == kernel_expected, d.kernel
+        assert d.device_status() == 0
+        # padded output channels are written too (zero weights, zero bias): compare everything
+        assert np.array_equal(acc, want_acc), f"{int((acc != want_acc).sum())} accumulators differ"
+        if case.out_dtype == np.float32:
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        else:
+            assert np.array_equal(got, want), f"{int((got != want).sum())} of {got.size} outputs differ"
+    finally:
+        d.close()
+
+
+@pytest.mark.parametrize("case", FLAT_CASES, ids=lambda c: c.name)
+def test_int8_1x1_umma_matches_oracle(pkg, case):
+    _check(case, "i8_gemm_umma")
+
+
+@pytest.mark.parametrize("case", BOX_CASES, ids=lambda c: c.name)
+def test_int8_kxk_umma_matches_oracle(pkg, case):
+    _check(case, "i8_conv_umma")
+
+
+@pytest.mark.parametrize("case", [FLAT_CASES[1], FLAT_CASES[3], BOX_CASES[0], BOX_CASES[3]], ids=lambda c: c.name)
+def test_int8_simt_matches_oracle(pkg, case, monkeypatch):
+    monkeypatch.setenv("ELB_FORCE_SIMT", "1")
+    _check(case, "i8_simt")
+
+
+def test_int8_host_buffers(pkg):
+    """The drop-in call with HOST pointers (staged through the plan's device buffers)."""
+    _check(FLAT_CASES[0], "i8_gemm_umma", host_buffers=True)
+    _check(dataclasses.replace(FLAT_CASES[8], name="flat_sum_host"), host_buffers=True)
+
+
+def test_weights_read_on_first_call_only(pkg):
+    """Reference contract: weights/bias are consumed on the first execute, later calls ignore them
+    (src/elx_conv_wino_xopt.hpp:34-38, src/elx_int8_conv_direct_1x1_xopt.hpp first-run guard)."""
+    import torch
+    import gpuutil as G
+    E = G.package()
+    case = FLAT_CASES[1]
+    t = R.make_tensors(case)
+    want = R.oracle_int8_conv(case, t)
+    d = G.make_desc(case)
+    assert d.setup() == E.ELD_OK
+    x = torch.from_numpy(t["input"]).cuda()
+    o = torch.zeros(R.out_shape(case), dtype=torch.uint8, device="cuda")
+    assert E.elx_conv(d, o, x, torch.from_numpy(t["weights"]).cuda(), torch.from_numpy(t["bias"]).cuda()) == 0
+    garbage = torch.full((t["weights"].size,), 7.0, device="cuda")
+    o2 = torch.zeros_like(o)
+    assert E.elx_conv(d, o2, x, garbage, None) == 0
+    assert np.array_equal(o2.cpu().numpy(), want) and np.array_equal(o.cpu().numpy(), want)
+    d.close()
+
+
+def test_idempotent_and_deterministic(pkg):
+    """Same input twice -> identical bytes (persistent tile walk has no order dependence)."""
+    import gpuutil as G
+    case = FLAT_CASES[10]
+    t = R.make_tensors(case)
+    a, d1 = G.run_gpu(case, t, repeat=2)
+    b, d2 = G.run_gpu(case, t)
+    assert np.array_equal(a, b)
+    d1.close(); d2.close()
+
+
+def test_unsupported_descriptors_return_codes(pkg):
+    import gpuutil as G
+    E = G.package()
+    d = G.make_desc(_case("bad_group", 1, 32, 32, 8, 8, algo="direct", g=2))
+    assert d.setup() == E.ELD_UNIMPLEMENTED and "group" in E.last_error()
+    d = G.make_desc(_case("bad_prop", 1, 32, 32, 8, 8, algo="direct"))
+    d.prop_kind = E.forward_training
+    assert d.setup() == E.ELD_GENERAL_ERROR
+    d = G.make_desc(_case("null_in", 1, 16, 16, 4, 4, kh=1, kw=1, pad=0, algo="1x1"))
+    assert d.setup() == E.ELD_OK
+    assert E.elx_conv(d, None, None, None, None) == E.ELX_GENERAL_ERROR
+    d.close()
+
+
+def test_bounded_wait_gives_up(pkg):
+    """A wait nobody satisfies returns a status instead of hanging: one CTA waits 20 ms on an
+    mbarrier with no arrivals, writes its status word and exits normally."""
+    import gpuutil as G
+    E = G.package()
+    assert E.lib.elb_selftest_bounded_wait(0, 20_000_000) == 104
+    # the context is still usable afterwards
+    _check(FLAT_CASES[9], "i8_gemm_umma")
