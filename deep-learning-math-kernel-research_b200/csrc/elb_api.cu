@@ -281,6 +281,7 @@ int setup_i8_direct(elb_conv &pl) {
       p.tiles_h = (d.oh + p.BH - 1) / p.BH;
       p.m_tiles = d.n * p.tiles_w * p.tiles_h;
     }
+    CUDA_TRY(init_i8_umma(pl.i8cfg));
   }
   pl.info.launches_per_call = 1;
   return ELB_OK;

@@ -116,6 +116,7 @@ struct I8UmmaConfig {
   size_t smem_bytes;
 };
 I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode);
+cudaError_t init_i8_umma(const I8UmmaConfig &cfg);   // per-device kernel attributes, call once per plan
 cudaError_t launch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s);
 cudaError_t launch_i8_simt(const I8ConvParams &p, cudaStream_t s);
 

@@ -332,11 +332,11 @@ __global__ void wait_selftest_kernel(int *status, unsigned long long limit_ns) {
 }
 
 template <int BN, int KC, int STAGES, int MODE>
-cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s) {
+cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool attr_only) {
   using L = SmemLayout<BN, KC, STAGES>;
   auto kern = i8_umma_kernel<BN, KC, STAGES, MODE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-  if (e != cudaSuccess) return e;
+  if (attr_only)   // once per plan and device, outside any stream capture
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
@@ -358,14 +358,24 @@ I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
   return c;
 }
 
+static cudaError_t dispatch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s,
+                                    bool attr_only) {
+  if (cfg.mode == I8_MODE_FLAT) {
+    if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);
+    return launch_cfg<64, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);
+  }
+  if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_BOX>(p, num_sms, s, attr_only);
+  return launch_cfg<64, 8, 6, I8_MODE_BOX>(p, num_sms, s, attr_only);
+}
+
+cudaError_t init_i8_umma(const I8UmmaConfig &cfg) {
+  I8ConvParams dummy{};
+  return dispatch_i8_umma(dummy, cfg, 1, nullptr, true);
+}
+
 cudaError_t launch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s) {
   if (p.OCB * V > MAX_OC_SMEM) return cudaErrorInvalidValue;
-  if (cfg.mode == I8_MODE_FLAT) {
-    if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_FLAT>(p, num_sms, s);
-    return launch_cfg<64, 8, 6, I8_MODE_FLAT>(p, num_sms, s);
-  }
-  if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_BOX>(p, num_sms, s);
-  return launch_cfg<64, 8, 6, I8_MODE_BOX>(p, num_sms, s);
+  return dispatch_i8_umma(p, cfg, num_sms, s, false);
 }
 
 cudaError_t launch_i8_simt(const I8ConvParams &p, cudaStream_t s) {
