@@ -130,6 +130,7 @@ struct elb_conv {
   void *d_wpack = nullptr, *d_wplain = nullptr, *d_scale = nullptr, *d_shift = nullptr;
   int *d_status = nullptr;
   void *d_acc_dump = nullptr;           // caller memory
+  void *d_trace = nullptr;              // caller memory (debug timeline)
   // staging for host-pointer callers
   void *d_in_stage = nullptr, *d_out_stage = nullptr;
   // int8 direct
@@ -223,17 +224,17 @@ void choose_box(int oh, int ow, int &BW, int &BH) {
 int encode_i8_tmaps(elb_conv &pl, const void *input) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
-  const elb_conv_desc_t &d = pl.d;
-  const int s = d.stride_h, CB = pl.i8.CB;
+  // IH/IW are the plan's view of the input plane (a 1x1 stride-1 convolution sees it as one row)
+  const int s = pl.i8.stride, CB = pl.i8.CB, IH = pl.i8.IH, IW = pl.i8.IW;
   for (int ph = 0; ph < s; ++ph)
     for (int pw = 0; pw < s; ++pw) {
-      const cuuint64_t Hp = (d.ih - ph + s - 1) / s, Wp = (d.iw - pw + s - 1) / s;
-      cuuint64_t dims[5] = {16, Wp, Hp, (cuuint64_t)CB, (cuuint64_t)d.n};
-      cuuint64_t strides[4] = {(cuuint64_t)s * 16, (cuuint64_t)s * d.iw * 16, (cuuint64_t)d.ih * d.iw * 16,
-                               (cuuint64_t)CB * d.ih * d.iw * 16};
+      const cuuint64_t Hp = (IH - ph + s - 1) / s, Wp = (IW - pw + s - 1) / s;
+      cuuint64_t dims[5] = {16, Wp, Hp, (cuuint64_t)CB, (cuuint64_t)pl.i8.N};
+      cuuint64_t strides[4] = {(cuuint64_t)s * 16, (cuuint64_t)s * IW * 16, (cuuint64_t)IH * IW * 16,
+                               (cuuint64_t)CB * IH * IW * 16};
       cuuint32_t box[5] = {16, (cuuint32_t)pl.i8.BW, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8cfg.KC, 1};
       cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-      void *base = (void *)((const uint8_t *)input + ((size_t)ph * d.iw + pw) * 16);
+      void *base = (void *)((const uint8_t *)input + ((size_t)ph * IW + pw) * 16);
       CUresult r = enc(&pl.i8.tmap[ph * s + pw], CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base, dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -268,7 +269,16 @@ int setup_i8_direct(elb_conv &pl) {
   p.rq.with_sum = d.with_ip_sum && d.dt_output != ELB_F32;
   p.rq.sum_scale = d.sum_scale;
   if (pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA || pl.info.kernel == ELB_KERNEL_I8_CONV_UMMA) {
-    const int mode = pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA ? I8_MODE_FLAT : I8_MODE_BOX;
+    // A 1x1 stride-1 convolution has no halo, so its image plane is viewed as ONE row of oh*ow
+    // pixels: the tile becomes 128 consecutive pixels of one image and a whole K stage of A is a
+    // single tiled TMA copy.  (ELB_I8_FLAT=1 selects the variant that tiles across images with
+    // per-run bulk copies instead; it issues many more, smaller copies.)
+    int mode = I8_MODE_BOX;
+    if (pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA) {
+      const char *flat = getenv("ELB_I8_FLAT");
+      if (flat && atoi(flat) > 0) mode = I8_MODE_FLAT;
+      else { p.IH = 1; p.IW = d.ih * d.iw; p.OH = 1; p.OW = d.oh * d.ow; }
+    }
     pl.i8cfg = i8_umma_config(p.OCB, p.CB, p.taps, mode);
     p.n_tiles = (p.OCB * V + pl.i8cfg.BN - 1) / pl.i8cfg.BN;
     p.CBG = (p.CB + pl.i8cfg.KC - 1) / pl.i8cfg.KC;
@@ -276,9 +286,9 @@ int setup_i8_direct(elb_conv &pl) {
     if (mode == I8_MODE_FLAT) {
       p.m_tiles = (p.M + 127) / 128;
     } else {
-      choose_box(d.oh, d.ow, p.BW, p.BH);
-      p.tiles_w = (d.ow + p.BW - 1) / p.BW;
-      p.tiles_h = (d.oh + p.BH - 1) / p.BH;
+      choose_box(p.OH, p.OW, p.BW, p.BH);
+      p.tiles_w = (p.OW + p.BW - 1) / p.BW;
+      p.tiles_h = (p.OH + p.BH - 1) / p.BH;
       p.m_tiles = d.n * p.tiles_w * p.tiles_h;
     }
     CUDA_TRY(init_i8_umma(pl.i8cfg));
@@ -332,11 +342,12 @@ int run_i8_direct(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
   p.out = out;
   p.acc_dump = (int32_t *)pl.d_acc_dump;
   p.status = pl.d_status;
+  p.trace = (long long *)pl.d_trace;
   cudaError_t e;
   if (pl.info.kernel == ELB_KERNEL_I8_SIMT) {
     e = launch_i8_simt(p, s);
   } else {
-    if (pl.info.kernel == ELB_KERNEL_I8_CONV_UMMA && pl.tmap_for != in) {
+    if (pl.i8cfg.mode == I8_MODE_BOX && pl.tmap_for != in) {
       int rc = encode_i8_tmaps(pl, in);
       if (rc != ELB_OK) return rc;
     }
@@ -550,6 +561,14 @@ int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const vo
 int elb_conv_set_accumulator_dump(elb_conv_t *plan, void *device_int32) {
   if (!plan) return fail(ELB_GENERAL_ERROR, "null plan");
   plan->d_acc_dump = device_int32;
+  return ELB_OK;
+}
+
+// Debug hook (not part of the reference surface): per-CTA timeline of the tcgen05 kernels, 64
+// int64 slots per CTA in caller device memory; NULL switches it off.
+ELB_API int elb_conv_set_trace(elb_conv_t *plan, void *device_int64) {
+  if (!plan) return ELB_GENERAL_ERROR;
+  plan->d_trace = device_int64;
   return ELB_OK;
 }
 

@@ -73,14 +73,35 @@ __device__ __forceinline__ void requant_store16(const int (&acc)[16], const floa
 #pragma unroll
     for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
   }
-  uint32_t w[4] = {0, 0, 0, 0};
+  uint32_t w[4];
+  // Packing with saturation.  s8: signed saturation is what the reference does.  u8: the reference
+  // saturates the int32 bit pattern as UNSIGNED (negatives -> 255); when ReLU with a non-negative
+  // lower bound is on no negative value can reach this point and the plain saturating pack is
+  // identical, otherwise the unsigned rule is applied explicitly.
+  if (rq.out_type == OUT_S8 || (rq.relu && rq.relu_lo >= 0.0f)) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    int r = __float2int_rn(f[i]);
-    uint32_t b;
-    if (rq.out_type == OUT_U8) b = (static_cast<uint32_t>(r) > 255u) ? 255u : static_cast<uint32_t>(r);
-    else b = static_cast<uint32_t>(max(-128, min(127, r))) & 0xFFu;
-    w[i >> 2] |= b << (8 * (i & 3));
+    for (int i = 0; i < 4; ++i) {
+      const int r0 = __float2int_rn(f[4 * i]), r1 = __float2int_rn(f[4 * i + 1]);
+      const int r2 = __float2int_rn(f[4 * i + 2]), r3 = __float2int_rn(f[4 * i + 3]);
+      uint32_t hi, lo;
+      if (rq.out_type == OUT_S8) {
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r3), "r"(r2));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"(r1), "r"(r0), "r"(hi));
+      } else {
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r3), "r"(r2));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"(r1), "r"(r0), "r"(hi));
+      }
+      w[i] = lo;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int r = __float2int_rn(f[i]);
+      const uint32_t b = (static_cast<uint32_t>(r) > 255u) ? 255u : static_cast<uint32_t>(r);
+      w[i >> 2] |= b << (8 * (i & 3));
+    }
   }
   *reinterpret_cast<uint4 *>(out) = make_uint4(w[0], w[1], w[2], w[3]);
 }
@@ -99,6 +120,7 @@ struct I8ConvParams {
   void *out;                         // nChw16c u8 / s8 / f32
   int32_t *acc_dump;                 // optional raw accumulators, nChw16c int32
   int *status;
+  long long *trace;                  // optional timeline, 64 slots per CTA (debug)
   Requant rq;
   int N, IH, IW, OH, OW, KH, KW, stride, pad_t, pad_l;
   int CB, OCB;                       // channel blocks of 16 (input / output)

@@ -6,11 +6,11 @@
 // micro-kernels under them (src/kernel/elk_u8s8_gemm.hxx:269-406, src/kernel/elk_u8s8_conv.hxx:254-677).
 //
 // i8_umma_kernel: implicit GEMM  D[pixel][oc] = sum_k A[pixel][k] * B[oc][k]  on tcgen05 tensor
-// cores.  One CTA = 6 warps with fixed roles:
+// cores.  One CTA = 10 warps with fixed roles:
 //   warp 0      producer: TMA copies global -> shared, STAGES-deep ring, mbarrier complete_tx
 //   warp 1      allocates TMEM; lane 0 issues tcgen05.mma (kind::i8, M=128, N=BN, K=32 per
 //               instruction) and commits to the ring's "empty" barriers / the accumulator barrier
-//   warps 2..5  epilogue: tcgen05.ld the s32 accumulators (one pixel per thread), fused
+//   warps 2..9  epilogue: tcgen05.ld the s32 accumulators (one pixel per thread), fused
 //               scale/shift/sum/ReLU/requantise, 16-byte stores into nChw16c
 // Two TMEM accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1.  The grid
 // is persistent: min(#tiles, #SMs) CTAs walk the tile list with stride gridDim.x.
@@ -29,13 +29,15 @@
 // (oc tile, K stage), so a stage of B is a single contiguous bulk copy.
 #include "elb_common.cuh"
 #include "umma.cuh"
+#include <cstdlib>
 
 namespace elb {
 
 namespace {
 
 constexpr int BM = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_WARPS = 8;     // two warps per TMEM lane quarter, alternating 16-channel blocks
+constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32;
 constexpr int MAX_OC_SMEM = 2048;    // per-channel constants cached in shared memory
 
 __device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
@@ -55,6 +57,9 @@ struct SmemLayout {
   static constexpr int CONST_OFF = (MISC_OFF + 16 + 15) / 16 * 16; // scale[MAX_OC_SMEM], shift[MAX_OC_SMEM]
   static constexpr int TOTAL = CONST_OFF + 2 * MAX_OC_SMEM * 4 + 128;   // +128: manual alignment slack
 };
+
+// optional per-CTA timeline (SM cycle counter), 64 slots per CTA; used by the profiling notes
+#define ELB_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
 template <int BN, int KC, int STAGES, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_constant__ I8ConvParams p) {
@@ -76,13 +81,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   const int total_tiles = p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
+    ELB_TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 4 * 32);
+      mbar_init(&tempty[b], NUM_EPI_WARPS * 32);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -97,6 +103,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) ELB_TRACE(1);
   int fail_code = 0;
 
   if (warp == 0) {
@@ -164,6 +171,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           }
           __syncwarp();
         }
+        if (lane == 0 && it < 16) ELB_TRACE(2 + it);
       }
     }
   } else if (warp == 1) {
@@ -182,6 +190,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           tc_fence_after_sync();
+          if (it < 16) ELB_TRACE(20 + it);
           const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t b_addr = a_addr + L::A_BYTES;
 #pragma unroll
@@ -193,12 +202,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
         }
         if (ok) umma_commit(&tfull[b]);  // accumulator complete
+        if (tcount == 0) ELB_TRACE(40);
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter ..
+    const int half = (warp - 2) >> 2;              // which of the two warps of this quarter
     const int row = quarter * 32 + lane;
     const int elt = p.rq.out_type == OUT_F32 ? 4 : 1;
     uint32_t tcount = 0;
@@ -228,9 +239,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
       }
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
       tc_fence_after_sync();
+      if (tcount == 0 && threadIdx.x == 64) ELB_TRACE(41);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * BN;
 #pragma unroll 1
-      for (int ob = 0; ob < BN / 16; ++ob) {
+      for (int ob = half; ob < BN / 16; ob += 2) {
         uint32_t r[16];
         tmem_ld16(t_addr + ob * 16, r);
         tmem_ld_wait();
@@ -251,11 +263,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
       }
       tc_fence_before_sync();
       mbar_arrive(&tempty[b]);
+      if (tcount == 0 && threadIdx.x == 64) ELB_TRACE(42);
     }
   }
 
   // ------------------------------------------------------------------ teardown
   if (fail_code != 0) atomicCAS(p.status, 0, fail_code);
+  if (threadIdx.x == 0) ELB_TRACE(43);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -338,32 +352,44 @@ cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool 
   if (attr_only)   // once per plan and device, outside any stream capture
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
   const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < num_sms ? tiles : num_sms;
+  int grid = tiles < num_sms ? tiles : num_sms;
+  if (const char *e = getenv("ELB_MAX_CTAS")) {   // tuning experiments only
+    const int v = atoi(e);
+    if (v > 0 && v < grid) grid = v;
+  }
   kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
-// Tile configuration: BN = 128 output channels per tile when OC allows it (two N tiles give the
-// persistent grid more tiles to balance), 8 K-chunks (128 bytes of K) per stage.
+// Tile configuration.  BN (output channels per tile) in {64, 128, 256}; 8 K-chunks (128 bytes of K)
+// per stage; as many stages as fit 227 KB.  ELB_I8_BN overrides the choice (tuning experiments).
 I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
   I8UmmaConfig c;
   c.mode = mode;
-  c.BN = (ocb * 16 >= 128) ? 128 : 64;
+  const int ocp = ocb * 16;
+  c.BN = ocp >= 128 ? 128 : 64;
+  if (const char *e = getenv("ELB_I8_BN")) {
+    const int v = atoi(e);
+    if (v == 64 || v == 128 || v == 256) c.BN = v;
+  }
   c.KC = 8;
-  c.STAGES = 6;
+  c.STAGES = c.BN == 256 ? 4 : 6;
   (void)cb; (void)taps;
-  c.smem_bytes = c.BN == 128 ? SmemLayout<128, 8, 6>::TOTAL : SmemLayout<64, 8, 6>::TOTAL;
+  c.smem_bytes = c.BN == 256 ? SmemLayout<256, 8, 4>::TOTAL
+               : c.BN == 128 ? SmemLayout<128, 8, 6>::TOTAL : SmemLayout<64, 8, 6>::TOTAL;
   return c;
 }
 
 static cudaError_t dispatch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s,
                                     bool attr_only) {
   if (cfg.mode == I8_MODE_FLAT) {
+    if (cfg.BN == 256) return launch_cfg<256, 8, 4, I8_MODE_FLAT>(p, num_sms, s, attr_only);
     if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);
     return launch_cfg<64, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);
   }
+  if (cfg.BN == 256) return launch_cfg<256, 8, 4, I8_MODE_BOX>(p, num_sms, s, attr_only);
   if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_BOX>(p, num_sms, s, attr_only);
   return launch_cfg<64, 8, 6, I8_MODE_BOX>(p, num_sms, s, attr_only);
 }

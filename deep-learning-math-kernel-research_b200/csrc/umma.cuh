@@ -2,7 +2,7 @@
 // mbarriers with BOUNDED waits, TMA bulk / tiled copies (no cluster-wide forms), tensor memory
 // (TMEM) allocation, tcgen05.mma / commit / ld and the proxy fences that order them.
 //
-// Every wait in here gives up after a wall-clock limit (WAIT_LIMIT_NS) and reports failure to the
+// Every wait in here gives up after a limit counted in SM cycles (WAIT_LIMIT_CYCLES, about two seconds) and reports failure to the
 // caller instead of spinning for ever; kernels turn that into a status word the host reads.
 #pragma once
 #include <cstdint>
@@ -10,7 +10,7 @@
 
 namespace elb {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about 2 s of SM clock per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -72,14 +72,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // a shared-memory word every role of the CTA polls) if the wait ran out of time or another role
 // already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  // The limit is counted on the SM's own cycle counter: it is a register read, whereas the global
+  // nanosecond timer costs a microsecond-scale round trip that would sit on the critical path of
+  // every pipeline stage.
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
         *abort_flag = 1;
         return false;
       }
