@@ -1,7 +1,753 @@
+// Winograd F(4x4,3x3) convolution (the reference's tile_size = 6) for sm_100a, fp32 and int8.
+//
+// Replaces elx_conv_wino_t / elx_int8_conv_wino_t (src/elx_conv_wino.cpp, src/elx_int8_conv_wino.cpp,
+// their *_xopt.hpp execution modes) and the stages under them:
+//   input transform   src/elx_conv_wino_trans_input.cpp + src/kernel/elk_conv_wino_4x4_3x3_input.hxx
+//   weights transform src/elx_conv_wino_trans_weights.cpp + src/kernel/elk_conv_wino_4x4_3x3_weights.hxx
+//   batched GEMM      src/elx_conv_wino_gemm.cpp, src/elx_int8_conv_wino_gemm.cpp,
+//                     src/kernel/elk_gemm.hxx, src/kernel/elk_u8s8_gemm.hxx
+//   output transform  src/elx_conv_wino_trans_output.cpp + src/kernel/elk_conv_wino_4x4_3x3_output.hxx
+//
+// Data flow on the device (three kernels per call, the weights are transformed once per plan):
+//   1. wino_input_kernel: reads nChw16c, computes V = B^T d B for every 6x6 tile and writes it
+//      DIRECTLY in the operand image of the GEMM: for each of the 36 positions a, each 128-tile
+//      row block and each K stage, [K chunk of 16 B][128 rows][16 B] -- so one GEMM stage of A is
+//      one contiguous bulk TMA copy.  fp32: two planes, hi = tf32(V) and lo = V - hi (3xTF32
+//      split); int8: V is quantised to u8 here (sat(rne(fma(V, iS/tS, tz)))).
+//   2. wino_gemm_kernel: 36 independent GEMMs M[a] = V[a] * U[a]^T on tcgen05 tensor cores with
+//      TMEM accumulators.  fp32: three kind::tf32 MMAs per K step (lo*hi + hi*lo + hi*hi), fp32
+//      accumulation.  int8: kind::i8 with s32 accumulation and the fp32 de-scale
+//      fma(acc, scale[a][oc], shift[a][oc]) in the epilogue.  Same warp roles, ring of
+//      shared-memory stages and bounded waits as the direct-convolution kernel.
+//   3. wino_output_kernel: Y = A^T M A, + bias, (requantise), + in-place sum, ReLU, clipped store
+//      into nChw16c.
+// Batches whose transform-domain buffers would exceed the workspace budget are processed in
+// chunks of whole images.
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "elb_common.cuh"
+#include "host_prep.hpp"
+#include "umma.cuh"
 #include "wino.cuh"
+
 namespace elb {
-int wino_setup(WinoPlan &, const elb_conv_desc_t &, elb_conv_info_t &, std::string &err) { err = "Winograd path not built yet"; return ELB_UNIMPLEMENTED; }
-int wino_prepare(WinoPlan &, const elb_conv_desc_t &, elb_conv_info_t &, const void *, const void *, std::string &err) { err = "not built"; return ELB_UNIMPLEMENTED; }
-int wino_run(WinoPlan &, void *, const void *, void *, int *, int, cudaStream_t, int &, std::string &err) { err = "not built"; return ELB_UNIMPLEMENTED; }
-void wino_release(WinoPlan &) {}
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int GEMM_STAGES = 4;
+constexpr int A_STAGE_BYTES = 16384;          // fp32: 2 planes x 4 chunks x 2 KB; int8: 8 chunks x 2 KB
+constexpr int MAX_BN = 256;
+constexpr int B_STAGE_MAX = 128 * MAX_BN;     // fp32: 2 x 4 x BN x 16; int8: 8 x BN x 16  (= 128*BN)
+constexpr int GEMM_EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32;
+constexpr size_t WORKSPACE_BUDGET = size_t(6) << 30;   // transform-domain buffers per chunk
+
+enum : int { KIND_F32 = 0, KIND_I8 = 1 };
+
+// ------------------------------------------------------------------------------ 1-D transforms
+// B^T with the reference's constants and evaluation order; every a*b+c is ONE fused multiply-add
+// there (src/kernel/elk_conv_wino_4x4_3x3_input.hxx:89-94, 133-145).
+__device__ __forceinline__ void bt6(const float (&f)[6], float (&o)[6]) {
+  const float z0 = -2.25f, z1 = -0.390625f, z2 = 0.87890625f, z3 = -2.640625f, z4 = 0.625f, z5 = 1.5f;
+  const float t0 = __fmaf_rn(f[2], z0, f[4]);
+  const float t1 = __fmaf_rn(f[1], z0, f[3]);
+  const float t2 = __fmaf_rn(f[2], z1, f[4]);
+  const float t3 = __fmaf_rn(f[1], z1, f[3]);
+  const float t4 = __fmaf_rn(f[0], z2, f[4]);
+  const float t5 = __fmaf_rn(f[1], z2, f[5]);
+  o[0] = __fmaf_rn(f[2], z3, t4);
+  o[1] = __fmaf_rn(t1, z4, t0);
+  o[2] = __fmaf_rn(-t1, z4, t0);
+  o[3] = __fmaf_rn(t3, z5, t2);
+  o[4] = __fmaf_rn(-t3, z5, t2);
+  o[5] = __fmaf_rn(f[3], z3, t5);
 }
+
+// A^T (src/kernel/elk_conv_wino_4x4_3x3_output.hxx:115-157)
+__device__ __forceinline__ void at6(const float (&f)[6], float (&p)[4]) {
+  const float z0 = 1.5f, z1 = 2.25f, z2 = 3.375f, z3 = 0.625f, z4 = 0.390625f, z5 = 0.244140625f;
+  const float t0 = __fadd_rn(f[1], f[2]);
+  const float t1 = __fadd_rn(f[3], f[4]);
+  const float t2 = __fsub_rn(f[1], f[2]);
+  const float t3 = __fsub_rn(f[3], f[4]);
+  p[0] = __fadd_rn(__fadd_rn(t0, t1), f[0]);
+  p[1] = __fmaf_rn(t2, z3, __fmul_rn(t3, z0));
+  p[2] = __fmaf_rn(t0, z4, __fmul_rn(t1, z1));
+  p[3] = __fadd_rn(__fmaf_rn(t2, z5, __fmul_rn(t3, z2)), f[5]);
+}
+
+struct WinoGeom {
+  int N, CB, OCB, IH, IW, OH, OW, ht, wt, pad_t, pad_l;
+  int T;          // tiles in this chunk = images * ht * wt
+  int m_tiles;    // ceil(T / 128)
+  int Tpad;       // m_tiles * 128
+  int k_stages;   // fp32: CB (16 channels per stage); int8: ceil(CB / 8) (128 channels per stage)
+};
+
+// ------------------------------------------------------------------------------ input transform
+// One thread = one tile x 4 consecutive channels.  A warp covers 8 consecutive tiles x the 16
+// channels of one block, so its stores are 128 contiguous bytes per K chunk (8 rows x 16 B).
+struct WinoInParams {
+  const void *in;      // nChw16c fp32 or u8, first image of the chunk
+  void *a_img;         // operand image
+  WinoGeom g;
+  float mrepS, tz;     // int8: u8 = sat(rne(fma(V, mrepS, tz)))
+};
+
+template <bool IN_U8>
+__global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__ WinoInParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * 64 + (threadIdx.x >> 2);
+  const int cb = blockIdx.y;
+  if (t >= g.Tpad) return;
+  const int mt = t >> 7, row = t & 127;
+
+  float m[6][6][4];   // after the pass along h: m[i][w][channel]
+  const bool live = t < g.T;
+  int n = 0, th = 0, tw = 0;
+  if (live) {
+    n = t / (g.ht * g.wt);
+    const int r = t - n * g.ht * g.wt;
+    th = r / g.wt;
+    tw = r - th * g.wt;
+  }
+  const int ih0 = 4 * th - g.pad_t, iw0 = 4 * tw - g.pad_l;
+#pragma unroll
+  for (int w = 0; w < 6; ++w) {
+    float col[6][4];
+    const int iw = iw0 + w;
+#pragma unroll
+    for (int h = 0; h < 6; ++h) {
+      const int ih = ih0 + h;
+      const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+      const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
+      if (IN_U8) {
+        uchar4 v = make_uchar4(0, 0, 0, 0);
+        if (ok) v = *reinterpret_cast<const uchar4 *>(static_cast<const uint8_t *>(p.in) + pix * 16 + quad * 4);
+        col[h][0] = static_cast<float>(v.x); col[h][1] = static_cast<float>(v.y);
+        col[h][2] = static_cast<float>(v.z); col[h][3] = static_cast<float>(v.w);
+      } else {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ok) v = *reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16 + quad * 4);
+        col[h][0] = v.x; col[h][1] = v.y; col[h][2] = v.z; col[h][3] = v.w;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float f[6] = {col[0][c], col[1][c], col[2][c], col[3][c], col[4][c], col[5][c]};
+      float o[6];
+      bt6(f, o);
+#pragma unroll
+      for (int i = 0; i < 6; ++i) m[i][w][c] = o[i];
+    }
+  }
+  // pass along w, one transformed row at a time, stored as soon as it is ready
+#pragma unroll
+  for (int i = 0; i < 6; ++i) {
+    float v[6][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float f[6] = {m[i][0][c], m[i][1][c], m[i][2][c], m[i][3][c], m[i][4][c], m[i][5][c]};
+      float o[6];
+      bt6(f, o);
+#pragma unroll
+      for (int j = 0; j < 6; ++j) v[j][c] = o[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+      const int a = i * 6 + j;
+      if (IN_U8) {
+        // stage = 8 channel blocks; chunk = cb % 8; 4 bytes per thread
+        uint32_t w = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float q = rintf(__fmaf_rn(v[j][c], p.mrepS, p.tz));
+          // a value that rounds below zero saturates to 255 in the reference (unsigned convert)
+          const uint32_t b = (q < 0.0f || q > 255.0f) ? 255u : static_cast<uint32_t>(q);
+          w |= b << (8 * c);
+        }
+        const size_t off = ((((static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4;
+        *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) + off) = live ? w : 0u;
+      } else {
+        // stage = this channel block; planes hi / lo; chunk = quad
+        float4 hi, lo;
+        float *hp = &hi.x, *lp = &lo.x;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t hb;
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v[j][c]));
+          const float h = __uint_as_float(hb);
+          hp[c] = h;
+          lp[c] = __fsub_rn(v[j][c], h);
+        }
+        const size_t stage = (static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + cb;
+        float *base = static_cast<float *>(p.a_img) + stage * (A_STAGE_BYTES / 4);
+        *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = hi;
+        *reinterpret_cast<float4 *>(base + ((4 + quad) * BM + row) * 4) = lo;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ batched GEMM
+struct WinoGemmParams {
+  const uint8_t *a_img;     // [36][m_tiles][k_stages][A_STAGE_BYTES]
+  const uint8_t *b_img;     // [36][n_tiles][k_stages][128*BN bytes]
+  float *m_out;             // [36][OCB][Tpad][16] fp32
+  const float *scale;       // int8: [36][OCP]
+  const float *shift;       // int8: [36][OCP]
+  int32_t *acc_dump;        // int8, optional: [36][T][OCP]
+  int *status;
+  int m_tiles, m_pitch, n_tiles, k_stages, BN, OCB, Tpad, T, kind;
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid_constant__ WinoGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_MAX;
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + GEMM_STAGES * STAGE_BYTES);
+  uint64_t *empty = full + GEMM_STAGES;
+  uint64_t *tfull = empty + GEMM_STAGES;
+  uint64_t *tempty = tfull + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN = p.BN;
+  const uint32_t b_stage_bytes = 128u * BN;
+  const int tiles_per_a = p.m_tiles * p.n_tiles;
+  const int total_tiles = 36 * tiles_per_a;
+  constexpr uint32_t TMEM_COLS = 512;     // two accumulator buffers of up to 256 columns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GEMM_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], GEMM_EPI_WARPS * 32);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  int fail_code = 0;
+
+  if (warp == 0) {
+    // -------- producer: two contiguous bulk copies per stage
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int a = tile / tiles_per_a;
+      const int r = tile - a * tiles_per_a;
+      const int nt = r / p.m_tiles, mt = r - nt * p.m_tiles;
+      const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + mt) * p.k_stages * A_STAGE_BYTES;
+      const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * b_stage_bytes;
+      for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+        const int s = it % GEMM_STAGES;
+        const uint32_t ph = (it / GEMM_STAGES) & 1u;
+        if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+        if (lane == 0) {
+          uint8_t *a_dst = smem + s * STAGE_BYTES;
+          mbar_arrive_expect_tx(&full[s], A_STAGE_BYTES + b_stage_bytes);
+          tma_bulk_g2s(a_dst, a_src + static_cast<size_t>(ks) * A_STAGE_BYTES, A_STAGE_BYTES, &full[s]);
+          tma_bulk_g2s(a_dst + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_stage_bytes, b_stage_bytes, &full[s]);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    // -------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = p.kind == KIND_F32 ? umma_idesc(1, 2, 2, BM, BN) : umma_idesc(2, 0, 1, BM, BN);
+      const uint32_t b_lbo = 16u * BN;
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
+        if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + b * MAX_BN;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = it % GEMM_STAGES;
+          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+          if (p.kind == KIND_F32) {
+            // planes: A hi at +0, lo at +8 KB; B hi at +0, lo at +4 chunks.  K step = 2 chunks.
+#pragma unroll
+            for (int k2 = 0; k2 < 2; ++k2) {
+              const uint64_t ahi = umma_desc_kmajor(a_addr + k2 * 4096, 2048, 128);
+              const uint64_t alo = umma_desc_kmajor(a_addr + 8192 + k2 * 4096, 2048, 128);
+              const uint64_t bhi = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
+              const uint64_t blo = umma_desc_kmajor(b_addr + 4 * b_lbo + k2 * 2 * b_lbo, b_lbo, 128);
+              umma_tf32(d_tmem, alo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
+              umma_tf32(d_tmem, ahi, blo, idesc, 1u);
+              umma_tf32(d_tmem, ahi, bhi, idesc, 1u);
+            }
+          } else {
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) {
+              const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 4096, 2048, 128);
+              const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
+              umma_i8(d_tmem, ad, bd, idesc, (ks | k2) != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tfull[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // -------- epilogue: one tile row (= one Winograd tile) per thread, 16 channels at a time
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    const int OCP = p.OCB * 16;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int a = tile / tiles_per_a;
+      const int r = tile - a * tiles_per_a;
+      const int nt = r / p.m_tiles, mt = r - nt * p.m_tiles;
+      const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
+      const int t = mt * BM + row;
+      if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * MAX_BN;
+#pragma unroll 1
+      for (int ob = half; ob < BN / 16; ob += 2) {
+        uint32_t rr[16];
+        tmem_ld16(t_addr + ob * 16, rr);
+        tmem_ld_wait();
+        const int ocb = nt * (BN / 16) + ob;
+        if (ocb < p.OCB) {
+          float f[16];
+          if (p.kind == KIND_F32) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(rr[i]);
+          } else {
+            const float *sc = p.scale + static_cast<size_t>(a) * OCP + ocb * 16;
+            const float *sh = p.shift + static_cast<size_t>(a) * OCP + ocb * 16;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              f[i] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[i])), __ldg(sc + i), __ldg(sh + i));
+            if (p.acc_dump && t < p.T) {
+              int32_t *d = p.acc_dump + (static_cast<size_t>(a) * p.T + t) * OCP + ocb * 16;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) d[i] = static_cast<int>(rr[i]);
+            }
+          }
+          float4 *o = reinterpret_cast<float4 *>(p.m_out + ((static_cast<size_t>(a) * p.OCB + ocb) * p.Tpad + t) * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty[b]);
+    }
+  }
+
+  if (fail_code != 0) atomicCAS(p.status, 0, fail_code);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * (A_STAGE_BYTES + B_STAGE_MAX) + (2 * GEMM_STAGES + 4) * 8 + 16 + 128;
+
+// ------------------------------------------------------------------------------ output transform
+struct WinoOutParams {
+  const float *m_in;    // [36][OCB][Tpad][16]
+  const float *bias;    // [OCP] or null
+  void *out;            // nChw16c f32 / u8 / s8, first image of the chunk
+  WinoGeom g;
+  int out_type, with_bias, with_relu, with_sum;
+  float orepS, oz;
+};
+
+__global__ void __launch_bounds__(256) wino_output_kernel(const __grid_constant__ WinoOutParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * 64 + (threadIdx.x >> 2);
+  const int ocb = blockIdx.y;
+  if (t >= g.T) return;
+  const int n = t / (g.ht * g.wt);
+  const int r = t - n * g.ht * g.wt;
+  const int th = r / g.wt, tw = r - th * g.wt;
+
+  float m[4][6][4];   // after the pass along h: m[i][j][channel]
+#pragma unroll
+  for (int j = 0; j < 6; ++j) {
+    float col[6][4];
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+      const float4 v = *reinterpret_cast<const float4 *>(
+          p.m_in + ((static_cast<size_t>(i * 6 + j) * g.OCB + ocb) * g.Tpad + t) * 16 + quad * 4);
+      col[i][0] = v.x; col[i][1] = v.y; col[i][2] = v.z; col[i][3] = v.w;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float f[6] = {col[0][c], col[1][c], col[2][c], col[3][c], col[4][c], col[5][c]};
+      float q[4];
+      at6(f, q);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m[i][j][c] = q[i];
+    }
+  }
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.with_bias && p.bias) bias4 = *reinterpret_cast<const float4 *>(p.bias + ocb * 16 + quad * 4);
+  const float bb[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
+  const int elt = p.out_type == OUT_F32 ? 4 : 1;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int oh = 4 * th + i;
+    float y[4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float f[6] = {m[i][0][c], m[i][1][c], m[i][2][c], m[i][3][c], m[i][4][c], m[i][5][c]};
+      float q[4];
+      at6(f, q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y[j][c] = q[j];
+    }
+    if (oh >= g.OH) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int ow = 4 * tw + j;
+      if (ow >= g.OW) continue;
+      const size_t pix = ((static_cast<size_t>(n) * g.OCB + ocb) * g.OH + oh) * g.OW + ow;
+      uint8_t *dst = static_cast<uint8_t *>(p.out) + (pix * 16 + quad * 4) * elt;
+      float f[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        f[c] = y[j][c];
+        if (p.with_bias) f[c] = __fadd_rn(f[c], bb[c]);
+        if (p.out_type != OUT_F32) f[c] = __fmaf_rn(f[c], p.orepS, p.oz);
+      }
+      if (p.with_sum) {
+        if (p.out_type == OUT_F32) {
+          const float4 pv = *reinterpret_cast<const float4 *>(dst);
+          f[0] = __fadd_rn(f[0], pv.x); f[1] = __fadd_rn(f[1], pv.y);
+          f[2] = __fadd_rn(f[2], pv.z); f[3] = __fadd_rn(f[3], pv.w);
+        } else {
+          const uint32_t pv = *reinterpret_cast<const uint32_t *>(dst);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t b = (pv >> (8 * c)) & 0xFFu;
+            f[c] = __fadd_rn(f[c], p.out_type == OUT_U8 ? static_cast<float>(b)
+                                                        : static_cast<float>(static_cast<int>(static_cast<int8_t>(b))));
+          }
+        }
+      }
+      if (p.with_relu) {          // literal zero: relu_bound is not used on this path in the reference
+#pragma unroll
+        for (int c = 0; c < 4; ++c) f[c] = fmaxf(f[c], 0.0f);
+      }
+      if (p.out_type == OUT_F32) {
+        *reinterpret_cast<float4 *>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+      } else {
+        uint32_t w = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float q = rintf(f[c]);
+          uint32_t b;
+          if (p.out_type == OUT_U8) b = (q < 0.0f || q > 255.0f) ? 255u : static_cast<uint32_t>(q);
+          else b = static_cast<uint32_t>(static_cast<int>(fminf(fmaxf(q, -128.0f), 127.0f))) & 0xFFu;
+          w |= b << (8 * c);
+        }
+        *reinterpret_cast<uint32_t *>(dst) = w;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+inline float tf32_rna(float x) {            // what cvt.rna.tf32.f32 returns for finite x
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  u = (u + 0x1000u) & 0xFFFFE000u;
+  float r;
+  std::memcpy(&r, &u, 4);
+  return r;
+}
+
+// G with the reference's constants and order (src/kernel/elk_conv_wino_4x4_3x3_weights.hxx:25-58)
+inline void g3(float f0, float f1, float f2, float o[6]) {
+  const float z0 = 0.26890756302521f, z1 = -0.688403361344538f, z2 = 0.119514472455649f,
+              z3 = 1.13777777777778f, z4 = 0.430252100840336f, z5 = 0.179271708683473f;
+  volatile float t0 = z0 * f2;
+  const float t1 = std::fmaf(z1, f0, -t0);
+  const float t2 = std::fmaf(z2, f0, t0);
+  volatile float o0 = z3 * f0;
+  o[0] = o0;
+  o[1] = std::fmaf(-z4, f1, t1);
+  o[2] = std::fmaf(z4, f1, t1);
+  o[3] = std::fmaf(z5, f1, t2);
+  o[4] = std::fmaf(-z5, f1, t2);
+  o[5] = f2;
+}
+
+// U[a][oc][ic] = G g G^T, kh direction first (the reference's order), zero for padded channels.
+std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, int ICP) {
+  std::vector<float> u(static_cast<size_t>(36) * OCP * ICP, 0.0f);
+  const int I2 = ICP / 16;
+  for (int o = 0; o < oc; ++o)
+    for (int i = 0; i < ic; ++i) {
+      float g[3][3], m[6][3], r[6];
+      for (int kh = 0; kh < 3; ++kh)
+        for (int kw = 0; kw < 3; ++kw) g[kh][kw] = w[host::w_index(I2, 3, 3, o, i, kh, kw)];
+      for (int kw = 0; kw < 3; ++kw) {
+        g3(g[0][kw], g[1][kw], g[2][kw], r);
+        for (int a = 0; a < 6; ++a) m[a][kw] = r[a];
+      }
+      for (int a = 0; a < 6; ++a) {
+        g3(m[a][0], m[a][1], m[a][2], r);
+        for (int b = 0; b < 6; ++b) u[(static_cast<size_t>(a * 6 + b) * OCP + o) * ICP + i] = r[b];
+      }
+    }
+  return u;
+}
+
+}  // namespace
+
+struct WinoImpl {
+  int kind = KIND_F32;
+  WinoGeom g{};            // geometry of a full chunk
+  int N = 0, imgs_per_chunk = 0;
+  int ICP = 0, OCP = 0, BN = 0, n_tiles = 0;
+  int out_type = OUT_F32, with_bias = 0, with_relu = 0, with_sum = 0;
+  float orepS = 1.f, oz = 0.f, mrepS = 1.f, tz = 0.f;
+  size_t in_img_bytes = 0, out_img_bytes = 0;
+  size_t a_bytes = 0, b_bytes = 0, m_bytes = 0;
+  void *d_a = nullptr, *d_b = nullptr, *d_m = nullptr, *d_bias = nullptr, *d_scale = nullptr, *d_shift = nullptr;
+};
+
+int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, std::string &err) {
+  if (info.kernel == ELB_KERNEL_I8_DEPTHWISE) { err = "int8 depthwise is not implemented yet"; return ELB_UNIMPLEMENTED; }
+  if (d.pad_t != 1 || d.pad_l != 1) { err = "Winograd needs pad 1"; return ELB_UNIMPLEMENTED; }
+  WinoImpl *w = new WinoImpl();
+  pl.impl = w;
+  w->kind = info.kernel == ELB_KERNEL_WINO_I8_UMMA ? KIND_I8 : KIND_F32;
+  if (w->kind == KIND_I8) {
+    if (d.sampling_kind != ELB_CALIBRATED) { err = "int8 Winograd: only CALIBRATED sampling is implemented"; return ELB_UNIMPLEMENTED; }
+    if (d.input_z != 0.0f) { err = "Support abs-max scaling for input only in Conv Winograd"; return ELB_UNIMPLEMENTED; }  // src/eld_conv.cpp:224-229
+  }
+  w->N = d.n;
+  w->ICP = host::alignup(d.ic, V);
+  w->OCP = host::alignup(d.oc, V);
+  WinoGeom &g = w->g;
+  g.CB = w->ICP / V; g.OCB = w->OCP / V;
+  g.IH = d.ih; g.IW = d.iw; g.OH = d.oh; g.OW = d.ow;
+  g.ht = (d.oh + 3) / 4; g.wt = (d.ow + 3) / 4;
+  g.pad_t = d.pad_t; g.pad_l = d.pad_l;
+  g.k_stages = w->kind == KIND_F32 ? g.CB : (g.CB + 7) / 8;
+  w->n_tiles = (w->OCP + MAX_BN - 1) / MAX_BN;
+  w->BN = host::alignup((w->OCP + w->n_tiles - 1) / w->n_tiles, 16);
+  // chunk of whole images whose transform-domain buffers fit the budget
+  const size_t tiles_img = static_cast<size_t>(g.ht) * g.wt;
+  const size_t per_tile = static_cast<size_t>(36) * (static_cast<size_t>(g.k_stages) * A_STAGE_BYTES / BM + static_cast<size_t>(w->OCP) * 4);
+  size_t imgs = WORKSPACE_BUDGET / (per_tile * tiles_img);
+  if (imgs < 1) imgs = 1;
+  if (imgs > static_cast<size_t>(d.n)) imgs = d.n;
+  w->imgs_per_chunk = static_cast<int>(imgs);
+  g.N = w->imgs_per_chunk;
+  g.T = static_cast<int>(imgs * tiles_img);
+  g.m_tiles = (g.T + BM - 1) / BM;
+  g.Tpad = g.m_tiles * BM;
+  w->a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * A_STAGE_BYTES;
+  w->b_bytes = static_cast<size_t>(36) * w->n_tiles * g.k_stages * 128 * w->BN;
+  w->m_bytes = static_cast<size_t>(36) * g.OCB * g.Tpad * 16 * 4;
+  w->in_img_bytes = static_cast<size_t>(w->ICP) * d.ih * d.iw * (d.dt_input == ELB_F32 ? 4 : 1);
+  w->out_type = d.dt_output == ELB_F32 ? OUT_F32 : d.dt_output == ELB_U8 ? OUT_U8 : OUT_S8;
+  w->out_img_bytes = static_cast<size_t>(w->OCP) * d.oh * d.ow * (w->out_type == OUT_F32 ? 4 : 1);
+  w->with_bias = d.with_bias; w->with_relu = d.with_relu; w->with_sum = d.with_ip_sum;
+  if (w->out_type != OUT_F32) {
+    w->orepS = 1.0f / d.output_scale;
+    w->oz = w->kind == KIND_I8 ? std::ceil(d.output_z) : d.output_z;      // src/elx_int8_conv_wino.cpp:276
+  }
+  if (w->kind == KIND_I8) {
+    w->tz = std::ceil(d.tinput_z);                                       // src/elx_int8_conv_wino.cpp:274
+    volatile float rep = 1.0f / d.tinput_scale;
+    w->mrepS = d.input_scale * rep;                                      // src/elx_conv_wino_trans_input.cpp:617
+  }
+  cudaError_t e = cudaFuncSetAttribute(wino_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return ELB_GENERAL_ERROR; }
+  info.launches_per_call = 3 * ((d.n + w->imgs_per_chunk - 1) / w->imgs_per_chunk);
+  return ELB_OK;
+}
+
+#define W_TRY(expr)                                                                   \
+  do {                                                                                \
+    cudaError_t e__ = (expr);                                                         \
+    if (e__ != cudaSuccess) { err = std::string(#expr) + ": " + cudaGetErrorString(e__); return ELB_GENERAL_ERROR; } \
+  } while (0)
+
+int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, const void *weights,
+                 const void *bias, std::string &err) {
+  WinoImpl *w = pl.impl;
+  if (!w) { err = "plan not set up"; return ELB_GENERAL_ERROR; }
+  const WinoGeom &g = w->g;
+  std::vector<float> hw(info.size_weights), hb(w->OCP, 0.0f);
+  W_TRY(cudaMemcpy(hw.data(), weights, info.size_weights * 4, cudaMemcpyDefault));
+  if (d.with_bias) {
+    if (!bias) { err = "bias is null but with_bias is set"; return ELB_GENERAL_ERROR; }
+    W_TRY(cudaMemcpy(hb.data(), bias, static_cast<size_t>(w->OCP) * 4, cudaMemcpyDefault));
+  }
+  std::vector<float> u = transform_weights(hw.data(), d.oc, d.ic, w->OCP, w->ICP);
+  const int BN = w->BN, KS = g.k_stages;
+  std::vector<uint8_t> img(w->b_bytes, 0);
+  if (w->kind == KIND_F32) {
+    // [a][nt][ks = channel block][plane][chunk j = 4 channels][BN rows][4 floats]
+    float *dst = reinterpret_cast<float *>(img.data());
+    for (int a = 0; a < 36; ++a)
+      for (int nt = 0; nt < w->n_tiles; ++nt)
+        for (int ks = 0; ks < KS; ++ks)
+          for (int r = 0; r < BN; ++r) {
+            const int o = nt * BN + r;
+            if (o >= w->OCP) continue;
+            const float *src = &u[(static_cast<size_t>(a) * w->OCP + o) * w->ICP + ks * 16];
+            float *stage = dst + ((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * (32 * BN);
+            for (int c = 0; c < 16; ++c) {
+              const float hi = tf32_rna(src[c]);
+              volatile float lo = src[c] - hi;
+              const int j = c >> 2, e = c & 3;
+              stage[(static_cast<size_t>(j) * BN + r) * 4 + e] = hi;
+              stage[(static_cast<size_t>(4 + j) * BN + r) * 4 + e] = lo;
+            }
+          }
+  } else {
+    // per (a, oc): abs-max over ic, q = rne((U*127)/absmax), scale = (absmax/127)*tS,
+    // shift = -(sum q * scale) * ceil(tz)      (src/elx_conv_wino_trans_weights.cpp:437-535)
+    std::vector<float> scale(static_cast<size_t>(36) * w->OCP, 0.0f), shift(scale.size(), 0.0f);
+    for (int a = 0; a < 36; ++a)
+      for (int o = 0; o < w->OCP; ++o) {
+        const float *src = &u[(static_cast<size_t>(a) * w->OCP + o) * w->ICP];
+        float m = 0.0f;
+        for (int i = 0; i < w->ICP; ++i) m = std::fmax(m, std::fabs(src[i]));
+        float sq = 0.0f;
+        const int nt = o / BN, r = o % BN;
+        for (int i = 0; i < w->ICP; ++i) {
+          int8_t q = 0;
+          if (m != 0.0f) {
+            volatile float t = src[i] * 127.0f;
+            volatile float v = t / m;
+            q = static_cast<int8_t>(std::nearbyintf(v));
+          }
+          sq += static_cast<float>(q);
+          const int cb = i >> 4, ks = cb >> 3, j = cb & 7;
+          img[(((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * 8 + j) * (16 * BN) + r * 16 + (i & 15)] =
+              static_cast<uint8_t>(q);
+        }
+        volatile float sw = m / 127.0f;
+        volatile float sc = sw * d.tinput_scale;
+        volatile float z1 = -sq * sc;
+        volatile float zw = z1 * w->tz;
+        scale[static_cast<size_t>(a) * w->OCP + o] = sc;
+        shift[static_cast<size_t>(a) * w->OCP + o] = zw;
+      }
+    W_TRY(cudaMalloc(&w->d_scale, scale.size() * 4));
+    W_TRY(cudaMalloc(&w->d_shift, shift.size() * 4));
+    W_TRY(cudaMemcpy(w->d_scale, scale.data(), scale.size() * 4, cudaMemcpyHostToDevice));
+    W_TRY(cudaMemcpy(w->d_shift, shift.data(), shift.size() * 4, cudaMemcpyHostToDevice));
+  }
+  W_TRY(cudaMalloc(&w->d_b, w->b_bytes));
+  W_TRY(cudaMemcpy(w->d_b, img.data(), w->b_bytes, cudaMemcpyHostToDevice));
+  W_TRY(cudaMalloc(&w->d_bias, static_cast<size_t>(w->OCP) * 4));
+  W_TRY(cudaMemcpy(w->d_bias, hb.data(), static_cast<size_t>(w->OCP) * 4, cudaMemcpyHostToDevice));
+  W_TRY(cudaMalloc(&w->d_a, w->a_bytes));
+  W_TRY(cudaMemset(w->d_a, 0, w->a_bytes));          // K padding chunks stay zero for ever
+  W_TRY(cudaMalloc(&w->d_m, w->m_bytes));
+  info.workspace_bytes += w->a_bytes + w->b_bytes + w->m_bytes + static_cast<size_t>(w->OCP) * 4;
+  return ELB_OK;
+}
+
+int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *status, int num_sms,
+             cudaStream_t s, int &launches, std::string &err) {
+  WinoImpl *w = pl.impl;
+  launches = 0;
+  if (!w) { err = "plan not set up"; return ELB_GENERAL_ERROR; }
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) {
+    err = "input/output tensors must be 16-byte aligned";
+    return ELB_GENERAL_ERROR;
+  }
+  for (int n0 = 0; n0 < w->N; n0 += w->imgs_per_chunk) {
+    WinoGeom g = w->g;
+    const int imgs = std::min(w->imgs_per_chunk, w->N - n0);
+    g.N = imgs;
+    g.T = imgs * g.ht * g.wt;
+    g.m_tiles = (g.T + BM - 1) / BM;
+    g.Tpad = w->g.Tpad;                   // buffers keep the full-chunk pitch
+    const int m_tiles_run = g.m_tiles;
+    g.m_tiles = w->g.m_tiles;             // operand image pitch
+    // 1. input transform (covers every row of the m-tiles that will be multiplied)
+    WinoInParams ip{};
+    ip.in = static_cast<const uint8_t *>(in) + static_cast<size_t>(n0) * w->in_img_bytes;
+    ip.a_img = w->d_a;
+    ip.g = g;
+    ip.g.Tpad = m_tiles_run * BM;
+    ip.mrepS = w->mrepS; ip.tz = w->tz;
+    dim3 gi((m_tiles_run * BM + 63) / 64, g.CB);
+    if (w->kind == KIND_I8) wino_input_kernel<true><<<gi, 256, 0, s>>>(ip);
+    else wino_input_kernel<false><<<gi, 256, 0, s>>>(ip);
+    W_TRY(cudaGetLastError());
+    // 2. batched GEMM
+    WinoGemmParams gp{};
+    gp.a_img = static_cast<const uint8_t *>(w->d_a);
+    gp.b_img = static_cast<const uint8_t *>(w->d_b);
+    gp.m_out = static_cast<float *>(w->d_m);
+    gp.scale = static_cast<const float *>(w->d_scale);
+    gp.shift = static_cast<const float *>(w->d_shift);
+    gp.acc_dump = (w->kind == KIND_I8 && acc_dump && n0 == 0 && imgs == w->N) ? static_cast<int32_t *>(acc_dump) : nullptr;
+    gp.status = status;
+    gp.m_tiles = m_tiles_run;            // tiles multiplied in this chunk
+    gp.m_pitch = w->g.m_tiles;           // pitch of the operand image (full chunk)
+    gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
+    gp.OCB = g.OCB; gp.Tpad = w->g.Tpad; gp.T = g.T; gp.kind = w->kind;
+    const int total = 36 * gp.m_tiles * gp.n_tiles;
+    wino_gemm_kernel<<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    W_TRY(cudaGetLastError());
+    // 3. output transform
+    WinoOutParams op{};
+    op.m_in = static_cast<const float *>(w->d_m);
+    op.bias = static_cast<const float *>(w->d_bias);
+    op.out = static_cast<uint8_t *>(out) + static_cast<size_t>(n0) * w->out_img_bytes;
+    op.g = g;
+    op.g.Tpad = w->g.Tpad;
+    op.out_type = w->out_type; op.with_bias = w->with_bias; op.with_relu = w->with_relu; op.with_sum = w->with_sum;
+    op.orepS = w->orepS; op.oz = w->oz;
+    dim3 go((g.T + 63) / 64, g.OCB);
+    wino_output_kernel<<<go, 256, 0, s>>>(op);
+    W_TRY(cudaGetLastError());
+    launches += 3;
+  }
+  return ELB_OK;
+}
+
+void wino_release(WinoPlan &pl) {
+  WinoImpl *w = pl.impl;
+  if (!w) return;
+  for (void *p : {w->d_a, w->d_b, w->d_m, w->d_bias, w->d_scale, w->d_shift})
+    if (p) cudaFree(p);
+  delete w;
+  pl.impl = nullptr;
+}
+
+}  // namespace elb

@@ -267,6 +267,8 @@ static void wino_weights_tile(float g[3][3], float u[6][6]) {
  * t2*z3 + t3*z0 as fma(t2, z3, t3*z0) (left product folded into the add of the right product is
  * equally possible; the difference is below the fp32 parity tolerance and only matters for the
  * staged int8 checks, which compare against the reference's own output). */
+static int g_at6_variant = 0;
+void orc_set_at6_variant(int v) { g_at6_variant = v; }
 static inline void wino_at6(const float f[6], float p[4]) {
   const float z0 = 1.5f, z1 = 2.25f, z2 = 3.375f, z3 = 0.625f, z4 = 0.390625f, z5 = 0.244140625f;
   float t0 = f[1] + f[2];
@@ -274,9 +276,19 @@ static inline void wino_at6(const float f[6], float p[4]) {
   float t2 = f[1] - f[2];
   float t3 = f[3] - f[4];
   p[0] = t0 + t1 + f[0];
-  p[1] = fmaf(t2, z3, t3 * z0);
-  p[2] = fmaf(t0, z4, t1 * z1);
-  p[3] = fmaf(t2, z5, t3 * z2) + f[5];
+  if (g_at6_variant == 0) {
+    p[1] = fmaf(t2, z3, t3 * z0);
+    p[2] = fmaf(t0, z4, t1 * z1);
+    p[3] = fmaf(t2, z5, t3 * z2) + f[5];
+  } else if (g_at6_variant == 1) {
+    p[1] = fmaf(t3, z0, t2 * z3);
+    p[2] = fmaf(t1, z1, t0 * z4);
+    p[3] = fmaf(t3, z2, t2 * z5) + f[5];
+  } else {
+    p[1] = t2 * z3 + t3 * z0;
+    p[2] = t0 * z4 + t1 * z1;
+    p[3] = t2 * z5 + t3 * z2 + f[5];
+  }
 }
 
 /* tweights out: [36][OC][IC] fp32 (a = hA*6 + wA).  Padded channels are zero. */
@@ -464,8 +476,10 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
   orc_wino_trans_input(p, in, 1, tinf);
 #pragma omp parallel for schedule(static)
   for (size_t k = 0; k < (size_t)36 * T * IC; ++k) {
+    /* cvt_roundps_epu32 + cvtusepi32_epi8: a value that rounds below zero converts to 0xFFFFFFFF
+     * and therefore saturates to 255, not to 0 (src/elx_conv_wino_trans_input.cpp:643-648) */
     float f = rne(fmaf(tinf[k], mrepS, tz));
-    tin[k] = (uint8_t)(f < 0.0f ? 0.0f : f > 255.0f ? 255.0f : f);
+    tin[k] = (uint8_t)(f < 0.0f ? 255.0f : f > 255.0f ? 255.0f : f);
   }
 
 #pragma omp parallel for collapse(2) schedule(static)
@@ -484,7 +498,9 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
   if (dump_tin) memcpy(dump_tin, tin, (size_t)36 * T * IC);
   if (dump_tw) memcpy(dump_tw, tw, (size_t)36 * OC * IC);
   if (dump_tout) memcpy(dump_tout, tout, sizeof(float) * 36 * T * OC);
-  orc_wino_trans_output(p, tout, bias, out, prev);
+  orc_conv_t po = *p;
+  po.out_z = ceilf(p->out_z);        /* src/elx_int8_conv_wino.cpp:276 */
+  orc_wino_trans_output(&po, tout, bias, out, prev);
   free(twf); free(tinf); free(tin); free(tw); free(scale); free(shift); free(tout);
   return 0;
 }

@@ -1,0 +1,109 @@
+"""GPU parity of the Winograd F(4x4,3x3) path (fp32 with the 3xTF32 tensor-core GEMM, and int8)
+against the CPU restatement, through the C-ABI.
+
+fp32 tolerance: relative L2 error <= 1e-5 against the restated fp32 Winograd result (the bar the
+benchmark definition sets), and additionally against an fp64 direct convolution.
+int8: the raw int32 accumulators of the 36 transform-domain GEMMs are compared bit for bit, the
+final fp32 output by relative L2 (only the fp32 output transform's summation order differs).
+"""
+import dataclasses
+
+import numpy as np
+import pytest
+
+import refutil as R
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+
+
+def _f32(name, n, ic, oc, ih, iw, **kw):
+    kw.setdefault("relu", True)
+    kw.setdefault("bias", True)
+    return R.ConvCase(name, n, ic, oc, ih, iw, types="fp32", algo="wino", tile=6, **kw)
+
+
+F32_CASES = [
+    _f32("wino_small", 2, 32, 32, 14, 14),
+    _f32("wino_partial_tiles", 1, 16, 48, 13, 11),              # oh, ow not multiples of 4
+    _f32("wino_c1_small", 2, 256, 256, 56, 56),                 # the benchmark layer at n=2
+    _f32("wino_plain", 3, 64, 32, 8, 8, relu=False, bias=False),
+    _f32("wino_sum", 2, 32, 64, 12, 12, sum=True),
+    _f32("wino_pad_lanes", 1, 24, 40, 9, 9),                    # channels not multiples of 16
+    _f32("wino_oc512", 1, 64, 512, 8, 8),                       # two N tiles of 256
+    _f32("wino_oc320", 1, 32, 320, 8, 8),                       # N tiles of 160
+    _f32("wino_tiny", 1, 16, 16, 4, 4),
+]
+
+
+@pytest.mark.parametrize("case", F32_CASES, ids=lambda c: c.name)
+def test_fp32_winograd_matches_oracle(pkg, case):
+    import gpuutil as G
+    t = R.make_tensors(case)
+    want = R.oracle_wino_f32(case, t)
+    got, d = G.run_gpu(case, t)
+    try:
+        assert d.kernel == "wino_f32_umma"
+        assert d.device_status() == 0
+        err = R.rel_l2(got, want)
+        assert err <= F32_TOL, f"rel-L2 vs restated Winograd {err:.3e}"
+        if not case.sum:
+            exact = R.oracle_direct_f64(case, t)
+            oc = case.oc
+            g2 = R.from_nChw16c(got, oc)
+            e2 = R.from_nChw16c(exact, oc)
+            assert R.rel_l2(g2, e2) <= 2e-5
+        # padded output channels carry bias-free zeros (relu(0 + 0))
+        if case.oc % 16:
+            assert np.all(R.from_nChw16c(got, R.alignup(case.oc))[:, case.oc:] == 0)
+    finally:
+        d.close()
+
+
+def test_fp32_winograd_host_buffers_and_repeat(pkg):
+    import gpuutil as G
+    case = F32_CASES[0]
+    t = R.make_tensors(case)
+    want = R.oracle_wino_f32(case, t)
+    got, d = G.run_gpu(case, t, host_buffers=True, repeat=2)
+    assert R.rel_l2(got, want) <= F32_TOL
+    d.close()
+
+
+def _i8(name, n, ic, oc, ih, iw, **kw):
+    kw.setdefault("types", "u8f32f32f32")
+    return R.ConvCase(name, n, ic, oc, ih, iw, algo="wino", tile=6, **kw)
+
+
+I8_CASES = [
+    _i8("i8wino_small", 2, 32, 32, 12, 12),
+    _i8("i8wino_c4_small", 2, 512, 512, 28, 28),
+    _i8("i8wino_partial", 1, 48, 16, 7, 10, relu=True, bias=True),
+    _i8("i8wino_k_tail", 1, 144, 32, 8, 8),                      # 9 channel blocks: partial K stage
+    _i8("i8wino_u8out", 2, 64, 64, 8, 8, types="u8f32u8f32", relu=True, bias=True, oscale=2.0),
+]
+
+
+@pytest.mark.parametrize("case", I8_CASES, ids=lambda c: c.name)
+def test_int8_winograd_matches_oracle(pkg, case):
+    import gpuutil as G
+    t = R.make_tensors(case)
+    case = R.calibrate_tinput(case, t)
+    want, dumps = R.oracle_int8_wino(case, t, dumps=True)
+    T, OCP = R.wino_tiles(case), R.alignup(case.oc)
+    got, d, acc = G.run_gpu(case, t, want_acc=True, acc_shape=(36, T, OCP))
+    try:
+        assert d.kernel == "wino_i8_umma"
+        assert d.device_status() == 0
+        bad = int((acc != dumps["acc"]).sum())
+        assert bad == 0, f"{bad} of {acc.size} transform-domain accumulators differ"
+        if case.out_dtype == np.float32:
+            assert R.rel_l2(got, want) <= 1e-5
+        else:
+            # requantised output: the fp32 output transform may differ in the last bit, which can
+            # flip a rounding; allow 1 LSB on a tiny fraction
+            diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
+            assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+    finally:
+        d.close()
