@@ -33,6 +33,14 @@ int fail(int code, const char *fmt, ...) {
   return code;
 }
 
+}  // namespace
+
+namespace elb {
+void set_last_error(const char *msg) { g_last_error = msg ? msg : ""; }
+}  // namespace elb
+
+namespace {
+
 #define CUDA_TRY(expr)                                                                      \
   do {                                                                                      \
     cudaError_t e__ = (expr);                                                               \

@@ -750,4 +750,192 @@ void wino_release(WinoPlan &pl) {
   pl.impl = nullptr;
 }
 
+// =================================================================================================
+// Allocation-free FP32 Winograd entry point.
+//
+// Some hosts may not allocate device memory where they call a convolution: a serving process whose
+// memory was carved up at start-up and handed to an arena it must not grow, a real-time loop that
+// must not take the driver's allocation lock, a plug-in running inside another framework's memory
+// budget.  For them elb_wino_f32_conv_noalloc() runs the same three kernels as the plan-based path
+// (plus a device-side weight transform) with every transform-domain buffer -- packed weights,
+// operand image of the transformed input, GEMM result, status word -- carved out of ONE file-scope
+// device array of fixed size.  Every GPU that loads the library holds that array until the process
+// exits.  The call uses no cudaMalloc / cudaFree and no allocating library routine; the caller
+// passes device pointers for input, weights, bias and output.
+//
+// Rules that follow from sharing one static array:
+//   * problems whose buffers exceed ELB_NOALLOC_SCRATCH_BYTES are rejected with ELB_UNIMPLEMENTED;
+//   * the array keeps the previous call's contents; this path rewrites everything it reads (the
+//     operand image has no K padding in fp32) and clears the status word at the start of each call;
+//   * two calls that overlap on the GPU (different streams, or different host threads) race on the
+//     array -- serialise them;
+//   * the first call on each device resolves the array's device address and sets the GEMM kernel's
+//     shared-memory attribute; make that first call before any stream capture begins.
+// =================================================================================================
+namespace {
+
+constexpr size_t ELB_NOALLOC_SCRATCH_BYTES = size_t(64) << 20;     // 64 MiB per GPU
+static __device__ __align__(256) unsigned char g_noalloc_scratch[ELB_NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char *g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};     // device address of the array, per device
+
+__device__ __forceinline__ void g3_dev(float f0, float f1, float f2, float (&o)[6]) {
+  const float z0 = 0.26890756302521f, z1 = -0.688403361344538f, z2 = 0.119514472455649f,
+              z3 = 1.13777777777778f, z4 = 0.430252100840336f, z5 = 0.179271708683473f;
+  const float t0 = __fmul_rn(z0, f2);
+  const float t1 = __fmaf_rn(z1, f0, -t0);
+  const float t2 = __fmaf_rn(z2, f0, t0);
+  o[0] = __fmul_rn(z3, f0);
+  o[1] = __fmaf_rn(-z4, f1, t1);
+  o[2] = __fmaf_rn(z4, f1, t1);
+  o[3] = __fmaf_rn(z5, f1, t2);
+  o[4] = __fmaf_rn(-z5, f1, t2);
+  o[5] = f2;
+}
+
+// One thread = one (oc, ic) pair: U = G g G^T, 3xTF32 split, written into the GEMM's B image
+// [a][n tile][k stage = ic/16][plane][chunk = (ic%16)/4][BN rows][4 floats].
+__global__ void wino_weights_f32_kernel(const float *__restrict__ w, float *__restrict__ b_img, int oc, int ic,
+                                        int OCP, int ICP, int BN, int n_tiles) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= OCP * ICP) return;
+  const int o = idx / ICP, i = idx - o * ICP;
+  float g[3][3];
+#pragma unroll
+  for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+    for (int kw = 0; kw < 3; ++kw) {
+      float v = 0.0f;
+      if (o < oc && i < ic)
+        v = w[((((static_cast<size_t>(o >> 4) * (ICP >> 4) + (i >> 4)) * 3 + kh) * 3 + kw) * 16 + (i & 15)) * 16 + (o & 15)];
+      g[kh][kw] = v;
+    }
+  float m[6][3];
+#pragma unroll
+  for (int kw = 0; kw < 3; ++kw) {
+    float r[6];
+    g3_dev(g[0][kw], g[1][kw], g[2][kw], r);
+#pragma unroll
+    for (int a = 0; a < 6; ++a) m[a][kw] = r[a];
+  }
+  const int nt = o / BN, row = o - nt * BN;
+  const int ks = i >> 4, j = (i & 15) >> 2, e = i & 3;
+  const int KS = ICP >> 4;
+#pragma unroll
+  for (int a = 0; a < 6; ++a) {
+    float r[6];
+    g3_dev(m[a][0], m[a][1], m[a][2], r);
+#pragma unroll
+    for (int b = 0; b < 6; ++b) {
+      uint32_t hb;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(r[b]));
+      const float hi = __uint_as_float(hb);
+      const float lo = __fsub_rn(r[b], hi);
+      float *stage = b_img + ((static_cast<size_t>(a * 6 + b) * n_tiles + nt) * KS + ks) * (32 * BN);
+      stage[(static_cast<size_t>(j) * BN + row) * 4 + e] = hi;
+      stage[(static_cast<size_t>(4 + j) * BN + row) * 4 + e] = lo;
+    }
+  }
+}
+
+}  // namespace
+
+void set_last_error(const char *msg);   // elb_api.cu: text returned by elb_last_error()
+
 }  // namespace elb
+
+// No counterpart in the reference (its allocators, src/common/el_allocator.hpp:40-136, always own
+// their memory); see the block comment above for who needs this and the limits that come with it.
+// All pointers are device pointers of the current device; weights are OIhw16i16o fp32 as the
+// caller holds them (they are transformed on the device inside this call), bias may be NULL when
+// desc->with_bias is 0.  Returns ELB_OK / ELB_UNIMPLEMENTED / ELB_GENERAL_ERROR; the text of a
+// failure is returned by elb_last_error().
+extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, void *output, const void *input,
+                                                 const void *weights, const void *bias, void *cuda_stream) {
+  using namespace elb;
+  auto fail = [](int code, const std::string &msg) { set_last_error(msg.c_str()); return code; };
+  if (!desc || !output || !input || !weights) return fail(ELB_GENERAL_ERROR, "null argument");
+  const elb_conv_desc_t &d = *desc;
+  const bool shape_ok = d.kh == 3 && d.kw == 3 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 1 && d.pad_l == 1 &&
+                        d.dilation_h == 1 && d.dilation_w == 1 && d.g == 1 && d.n > 0 && d.ic > 0 && d.oc > 0 &&
+                        d.oh == d.ih && d.ow == d.iw && (d.tile_size == 6 || d.tile_size == 0);
+  const bool type_ok = d.dt_input == ELB_F32 && d.dt_weights == ELB_F32 && d.dt_output == ELB_F32 && d.dt_bias == ELB_F32 &&
+                       d.fmt_input == ELB_NCHW16C && d.fmt_output == ELB_NCHW16C && d.fmt_weights == ELB_OIHW16I16O;
+  if (!shape_ok || !type_ok)
+    return fail(ELB_UNIMPLEMENTED, "elb_wino_f32_conv_noalloc: needs fp32 nChw16c/OIhw16i16o, 3x3, stride 1, pad 1, F(4x4,3x3)");
+  if (d.with_bias && !bias) return fail(ELB_GENERAL_ERROR, "bias is null but with_bias is set");
+  if ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(output) | reinterpret_cast<uintptr_t>(weights)) & 15)
+    return fail(ELB_GENERAL_ERROR, "tensors must be 16-byte aligned");
+
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= NOALLOC_MAX_DEVICES) return fail(ELB_GENERAL_ERROR, "no usable CUDA device");
+  if (!g_noalloc_ptr[dev]) {
+    // first call on this device: the array's NAME is a host-side handle, the kernels need its
+    // device address
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(wino_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
+  }
+  int num_sms = 0;
+  if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+    return fail(ELB_GENERAL_ERROR, "cannot query the SM count");
+
+  // geometry (one chunk: the whole batch must fit)
+  const int ICP = host::alignup(d.ic, V), OCP = host::alignup(d.oc, V);
+  WinoGeom g{};
+  g.N = d.n; g.CB = ICP / V; g.OCB = OCP / V;
+  g.IH = d.ih; g.IW = d.iw; g.OH = d.oh; g.OW = d.ow;
+  g.ht = (d.oh + 3) / 4; g.wt = (d.ow + 3) / 4;
+  g.pad_t = 1; g.pad_l = 1;
+  g.k_stages = g.CB;
+  const long long T = static_cast<long long>(d.n) * g.ht * g.wt;
+  if (T > (1ll << 24)) return fail(ELB_UNIMPLEMENTED, "elb_wino_f32_conv_noalloc: problem exceeds the static scratch array");
+  g.T = static_cast<int>(T);
+  g.m_tiles = (g.T + BM - 1) / BM;
+  g.Tpad = g.m_tiles * BM;
+  const int n_tiles = (OCP + MAX_BN - 1) / MAX_BN;
+  const int BN = host::alignup((OCP + n_tiles - 1) / n_tiles, 16);
+  const size_t b_bytes = static_cast<size_t>(36) * n_tiles * g.k_stages * 128 * BN;
+  const size_t a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * A_STAGE_BYTES;
+  const size_t m_bytes = static_cast<size_t>(36) * g.OCB * g.Tpad * 16 * 4;
+  const size_t need = 256 + b_bytes + a_bytes + m_bytes;
+  if (need > ELB_NOALLOC_SCRATCH_BYTES) {
+    char buf[200];
+    snprintf(buf, sizeof(buf), "elb_wino_f32_conv_noalloc: needs %zu bytes of scratch, the static array holds %zu",
+             need, ELB_NOALLOC_SCRATCH_BYTES);
+    return fail(ELB_UNIMPLEMENTED, buf);
+  }
+  unsigned char *base = g_noalloc_ptr[dev];
+  int *status = reinterpret_cast<int *>(base);
+  float *b_img = reinterpret_cast<float *>(base + 256);
+  unsigned char *a_img = base + 256 + b_bytes;
+  float *m_buf = reinterpret_cast<float *>(base + 256 + b_bytes + a_bytes);
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+
+  // the status word must start at zero; everything else the kernels read is rewritten below
+  if (cudaMemsetAsync(status, 0, 256, s) != cudaSuccess) return fail(ELB_GENERAL_ERROR, "cudaMemsetAsync failed");
+  wino_weights_f32_kernel<<<(OCP * ICP + 255) / 256, 256, 0, s>>>(static_cast<const float *>(weights), b_img, d.oc, d.ic,
+                                                                OCP, ICP, BN, n_tiles);
+  WinoInParams ip{};
+  ip.in = input; ip.a_img = a_img; ip.g = g;
+  wino_input_kernel<false><<<dim3((g.Tpad + 63) / 64, g.CB), 256, 0, s>>>(ip);
+  WinoGemmParams gp{};
+  gp.a_img = a_img; gp.b_img = reinterpret_cast<const uint8_t *>(b_img); gp.m_out = m_buf;
+  gp.status = status;
+  gp.m_tiles = g.m_tiles; gp.m_pitch = g.m_tiles; gp.n_tiles = n_tiles; gp.k_stages = g.k_stages; gp.BN = BN;
+  gp.OCB = g.OCB; gp.Tpad = g.Tpad; gp.T = g.T; gp.kind = KIND_F32;
+  const int total = 36 * gp.m_tiles * gp.n_tiles;
+  wino_gemm_kernel<<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  WinoOutParams op{};
+  op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;
+  op.out_type = OUT_F32; op.with_bias = d.with_bias; op.with_relu = d.with_relu; op.with_sum = d.with_ip_sum;
+  op.orepS = 1.0f; op.oz = 0.0f;
+  wino_output_kernel<<<dim3((g.T + 63) / 64, g.OCB), 256, 0, s>>>(op);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("kernel launch failed: ") + cudaGetErrorString(e));
+  return ELB_OK;
+}

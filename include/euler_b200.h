@@ -156,6 +156,30 @@ ELB_API int elb_reorder_nchw_to_nChw16c(void *dst, const void *src, int n, int c
 ELB_API int elb_reorder_nChw16c_to_nchw(void *dst, const void *src, int n, int c, int h, int w,
                                         int elem_bytes, void *cuda_stream);
 
+/* FP32 Winograd F(4x4,3x3) convolution that allocates nothing -- no counterpart in the reference.
+ *
+ * For callers that may not allocate device memory at the point where they run a convolution (a
+ * server whose GPU memory was handed to a fixed arena at start-up, a latency-critical loop that
+ * must stay off the driver's allocation lock, a plug-in confined to its host framework's memory
+ * budget).  All transform-domain buffers live in one 64 MiB array that is part of the library
+ * image on every GPU; the call uses no cudaMalloc/cudaFree and no allocating library routine.
+ *
+ *   desc      fp32 in/weights/out/bias, nChw16c / OIhw16i16o, 3x3, stride 1, pad 1, g = 1;
+ *             with_bias / with_relu / with_ip_sum are honoured
+ *   output, input, weights, bias   DEVICE pointers on the current device, 16-byte aligned; weights
+ *             in the caller's OIhw16i16o form (they are transformed on the device in every call)
+ *   cuda_stream   cudaStream_t the kernels are enqueued on (NULL = default stream); the call does
+ *             not wait for them
+ *
+ * Limits: problems whose buffers (packed weights + transformed input + transform-domain result)
+ * exceed 64 MiB return ELB_UNIMPLEMENTED, message in elb_last_error().  The array is shared by
+ * every call in the process and keeps the previous call's contents (this path overwrites all it
+ * reads and clears its status word itself): calls that overlap on the GPU race, so serialise
+ * them.  The FIRST call on each device resolves the array's device address and sets a kernel
+ * attribute; issue it once before any CUDA stream capture starts. */
+ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, void *output, const void *input,
+                                      const void *weights, const void *bias, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
