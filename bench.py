@@ -103,6 +103,21 @@ class ClockSampler(threading.Thread):
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def max_over_ranks(values, dist, device="cuda"):
+    """Element-wise maximum of per-rank timings (the slowest rank defines the step time)."""
+    if dist is None:
+        return [float(v) for v in values]
+    import torch
+    tt = torch.tensor(list(values), device=device, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    return [float(v) for v in tt]
+
+
+def aggregate_throughput(ops, ms_per_step, world):
+    """Whole-job T(FL)OP/s: every rank processes the workload's full batch (weak scaling)."""
+    return world * ops / (ms_per_step * 1e-3) / 1e12
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -297,14 +312,11 @@ def main():
     assert rc == 0, E.last_error()
     sampler.stop()
 
-    if dist is not None:
-        tt = torch.tensor([ms_total, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms = float(tt[0]), float(tt[1])
+    ms_total, e2e_ms = max_over_ranks([ms_total, e2e_ms], dist, device="cuda")
 
     ms_step = ms_total / args.steps
-    value = world * ops / (ms_step * 1e-3) / 1e12
-    e2e_value = world * ops / (e2e_ms / e2e_steps * 1e-3) / 1e12
+    value = aggregate_throughput(ops, ms_step, world)
+    e2e_value = aggregate_throughput(ops, e2e_ms / e2e_steps, world)
 
     peaks, peak_kind = measured_peaks()
     traffic = None

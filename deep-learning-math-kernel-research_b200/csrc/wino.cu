@@ -117,6 +117,8 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__
     tw = r - th * g.wt;
   }
   const int ih0 = 4 * th - g.pad_t, iw0 = 4 * tw - g.pad_l;
+  // is_border of the reference's tile iterator (src/elx_conv_wino_trans_input.hpp:247-249)
+  const bool border = th == 0 || tw == 0 || th == g.ht - 1 || tw == g.wt - 1;
 #pragma unroll
   for (int w = 0; w < 6; ++w) {
     float col[6][4];
@@ -157,6 +159,15 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__
       bt6(f, o);
 #pragma unroll
       for (int j = 0; j < 6; ++j) v[j][c] = o[j];
+      // The reference compiles a separate kernel for tiles that touch the image border, and in it
+      // two corner results are not fully fused: V[0][5] is rounded products + rounded adds,
+      // V[5][0] keeps only its outer fma.  Reproduced so that the quantised u8 transform matches
+      // the reference bit for bit (found against its mode-a033 scratch dump).
+      if (border) {
+        const float z2 = 0.87890625f, z3 = -2.640625f;
+        if (i == 0) v[5][c] = __fadd_rn(__fmul_rn(f[3], z3), __fadd_rn(__fmul_rn(f[1], z2), f[5]));
+        if (i == 5) v[0][c] = __fmaf_rn(f[2], z3, __fadd_rn(__fmul_rn(f[0], z2), f[4]));
+      }
     }
 #pragma unroll
     for (int j = 0; j < 6; ++j) {
@@ -493,9 +504,14 @@ inline float tf32_rna(float x) {            // what cvt.rna.tf32.f32 returns for
 inline void g3(float f0, float f1, float f2, float o[6]) {
   const float z0 = 0.26890756302521f, z1 = -0.688403361344538f, z2 = 0.119514472455649f,
               z3 = 1.13777777777778f, z4 = 0.430252100840336f, z5 = 0.179271708683473f;
-  volatile float t0 = z0 * f2;
-  const float t1 = std::fmaf(z1, f0, -t0);
-  const float t2 = std::fmaf(z2, f0, t0);
+  // In the reference build the first product, z0*f2, is the one fused into both of its uses;
+  // z1*f0 and z2*f0 stay rounded products.  (Pinned against the reference's int8 Winograd
+  // output: with this structure the quantised weights agree everywhere, with the other one
+  // roughly one s8 code in 10^5 flips.)
+  volatile float p1 = z1 * f0;
+  volatile float p2 = z2 * f0;
+  const float t1 = std::fmaf(-z0, f2, p1);
+  const float t2 = std::fmaf(z0, f2, p2);
   volatile float o0 = z3 * f0;
   o[0] = o0;
   o[1] = std::fmaf(-z4, f1, t1);
@@ -783,9 +799,8 @@ unsigned char *g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};     // device address of
 __device__ __forceinline__ void g3_dev(float f0, float f1, float f2, float (&o)[6]) {
   const float z0 = 0.26890756302521f, z1 = -0.688403361344538f, z2 = 0.119514472455649f,
               z3 = 1.13777777777778f, z4 = 0.430252100840336f, z5 = 0.179271708683473f;
-  const float t0 = __fmul_rn(z0, f2);
-  const float t1 = __fmaf_rn(z1, f0, -t0);
-  const float t2 = __fmaf_rn(z2, f0, t0);
+  const float t1 = __fmaf_rn(-z0, f2, __fmul_rn(z1, f0));      // same fusion structure as the host path
+  const float t2 = __fmaf_rn(z0, f2, __fmul_rn(z2, f0));
   o[0] = __fmul_rn(z3, f0);
   o[1] = __fmaf_rn(-z4, f1, t1);
   o[2] = __fmaf_rn(z4, f1, t1);

@@ -227,7 +227,9 @@ static inline void wino_bt6(const float f[6], float o[6]) {
 
 /* V[hA][wA] = B^T d B for one 6x6 tile of one channel: h direction first, then w
  * (elk_conv_wino_4x4_3x3_input.hxx:133-352). */
-static void wino_input_tile(float d[6][6], float v[6][6]) {
+static int g_border_rule = 1;      /* probe switch, see orc_set_border_rule */
+void orc_set_border_rule(int v) { g_border_rule = v; }
+static void wino_input_tile(float d[6][6], float v[6][6], int border) {
   float m[6][6];
   for (int w = 0; w < 6; ++w) {
     float col[6], o[6];
@@ -236,15 +238,38 @@ static void wino_input_tile(float d[6][6], float v[6][6]) {
     for (int i = 0; i < 6; ++i) m[i][w] = o[i];
   }
   for (int i = 0; i < 6; ++i) wino_bt6(m[i], v[i]);
+  if (border && g_border_rule) {
+    /* The reference instantiates a separate kernel for tiles that touch the image border
+     * (is_border, src/elx_conv_wino_trans_input.hpp:247-249) and in THAT instantiation g++ leaves
+     * two corner results unfused: V[0][5] and V[5][0] are rounded products followed by rounded
+     * adds.  Found by comparing against the reference's transformed input (mode a033 scratch
+     * dump): with this rule 0 of 147456 values differ, without it 66 do, all in border tiles. */
+    const float z2 = 0.87890625f, z3 = -2.640625f;
+    float t5 = m[0][1] * z2;  t5 = t5 + m[0][5];
+    float p5 = m[0][3] * z3;  v[0][5] = p5 + t5;
+    float t4 = m[5][0] * z2;  t4 = t4 + m[5][4];     /* V[5][0]: only the inner sum is unfused */
+    v[5][0] = fmaf(m[5][2], z3, t4);
+  }
 }
 
 /* 1-D weight transform G (src/kernel/elk_conv_wino_4x4_3x3_weights.hxx:25-58) */
+static int g_g3_variant = 0;       /* probe switch */
+void orc_set_g3_variant(int v) { g_g3_variant = v; }
 static inline void wino_g3(float f0, float f1, float f2, float o[6]) {
   const float z0 = 0.26890756302521f, z1 = -0.688403361344538f, z2 = 0.119514472455649f,
               z3 = 1.13777777777778f, z4 = 0.430252100840336f, z5 = 0.179271708683473f;
-  float t0 = z0 * f2;
-  float t1 = fmaf(z1, f0, -t0);
-  float t2 = fmaf(z2, f0, t0);
+  float t1, t2;
+  if (g_g3_variant == 0) {
+    /* g++ fuses the FIRST product of the statement list, z0*f2, into both of its uses and leaves
+     * z1*f0 and z2*f0 as rounded products */
+    float p1 = z1 * f0, p2 = z2 * f0;
+    t1 = fmaf(-z0, f2, p1);
+    t2 = fmaf(z0, f2, p2);
+  } else {
+    float t0 = z0 * f2;
+    t1 = fmaf(z1, f0, -t0);
+    t2 = fmaf(z2, f0, t0);
+  }
   o[0] = z3 * f0;
   o[1] = fmaf(-z4, f1, t1);
   o[2] = fmaf(z4, f1, t1);
@@ -330,7 +355,9 @@ void orc_wino_trans_input(const orc_conv_t *p, const void *in, int in_is_u8, flo
               }
               d[h][w] = x;
             }
-          wino_input_tile(d, v);
+          /* is_border: first tile row/column (padding) or last (the tile overhangs the image) */
+          int border = th == 0 || tw == 0 || th == ht - 1 || tw == wt - 1;
+          wino_input_tile(d, v, border);
           size_t t = ((size_t)n * ht + th) * wt + tw;
           for (int a = 0; a < 36; ++a) tin[((size_t)a * T + t) * IC + c] = v[a / 6][a % 6];
         }

@@ -1,0 +1,69 @@
+"""Pin of the CPU restatement against the reference library itself (oracle/_ref), run where the
+host has AVX-512 VNNI and the reference build exists; skipped elsewhere (tests/golden/ carries the
+same pin as fixtures)."""
+import dataclasses
+
+import numpy as np
+import pytest
+
+import refutil as R
+
+pytestmark = pytest.mark.skipif(not R.reference_available(), reason="reference build or AVX-512 VNNI missing")
+
+BLK = lambda c: dict(blk_i=R.alignup(c.ic) // 16, blk_o=1, flt_o=1, flt_t=min(c.ow, 7))  # noqa: E731
+
+
+def _with_knobs(c):
+    return dataclasses.replace(c, knobs=BLK(c))
+
+
+@pytest.mark.parametrize("case", [
+    R.ConvCase("ovr_1x1", 2, 96, 48, 9, 9, kh=1, kw=1, pad=0, types="u8f32u8f32", algo="1x1", relu=True, bias=True),
+    R.ConvCase("ovr_1x1_s8", 2, 64, 32, 8, 8, kh=1, kw=1, pad=0, types="u8f32s8f32", algo="1x1", bias=True, oscale=4.0),
+    R.ConvCase("ovr_1x1_oz", 1, 64, 32, 8, 8, kh=1, kw=1, pad=0, types="u8f32u8f32", algo="1x1", bias=True, oscale=4.0,
+               oz=128.0),
+    R.ConvCase("ovr_1x1_sum", 1, 64, 32, 8, 8, kh=1, kw=1, pad=0, types="u8f32u8f32", algo="1x1", relu=True, bias=True,
+               sum=True, sscale=0.25, oscale=0.5),
+    R.ConvCase("ovr_3x3", 2, 48, 32, 11, 11, types="u8f32u8f32", algo="direct", relu=True, bias=True),
+    R.ConvCase("ovr_3x3_s2", 1, 32, 64, 14, 14, stride=2, types="u8f32u8f32", algo="direct", relu=True, bias=True),
+], ids=lambda c: c.name)
+def test_int8_direct_bit_exact(case):
+    case = _with_knobs(case)
+    t = R.make_tensors(case)
+    ref, _ = R.run_reference(case, t)
+    got = R.oracle_int8_conv(case, t)
+    assert np.array_equal(got.view(np.uint8), ref.view(np.uint8))
+
+
+def test_reference_ignores_sum_on_kxk():
+    """with_ip_sum has no effect on the reference's KxK int8 path (src/elx_int8_conv_direct.cpp:121)."""
+    base = _with_knobs(R.ConvCase("ovr_sum_kxk", 1, 32, 32, 8, 8, types="u8f32u8f32", algo="direct", relu=True,
+                                  bias=True))
+    t = R.make_tensors(dataclasses.replace(base, sum=True))
+    with_sum, _ = R.run_reference(dataclasses.replace(base, sum=True), t)
+    without, _ = R.run_reference(base, t)
+    assert np.array_equal(with_sum, without)
+
+
+def test_epilogue_is_fused_multiply_add():
+    """Large sample: the fused form must give zero mismatches against the reference build."""
+    case = dataclasses.replace(R.baseline_case("c2", 8), oscale=4.0, relu=False, types="u8f32s8f32")
+    t = R.make_tensors(case)
+    ref, _ = R.run_reference(case, t)
+    assert int((R.oracle_int8_conv(case, t, fused=True) != ref).sum()) == 0
+
+
+@pytest.mark.parametrize("dims", [(2, 32, 32, 14, 14), (1, 16, 48, 13, 11)])
+def test_fp32_winograd_close(dims):
+    case = R.ConvCase("ovr_wino", *dims, types="fp32", algo="wino", tile=6, relu=True, bias=True)
+    t = R.make_tensors(case)
+    ref, _ = R.run_reference(case, t)
+    assert R.rel_l2(R.oracle_wino_f32(case, t), ref) < 2e-6
+
+
+def test_int8_winograd_close():
+    case = R.ConvCase("ovr_i8wino", 2, 32, 32, 12, 12, types="u8f32f32f32", algo="wino", tile=6)
+    t = R.make_tensors(case)
+    case = R.calibrate_tinput(case, t)
+    ref, _ = R.run_reference(case, t)
+    assert R.rel_l2(R.oracle_int8_wino(case, t), ref) < 2e-6
