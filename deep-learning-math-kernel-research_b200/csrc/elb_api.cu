@@ -234,6 +234,20 @@ int encode_i8_tmaps(elb_conv &pl, const void *input) {
   if (!enc) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
   // IH/IW are the plan's view of the input plane (a 1x1 stride-1 convolution sees it as one row)
   const int s = pl.i8.stride, CB = pl.i8.CB, IH = pl.i8.IH, IW = pl.i8.IW;
+  if (pl.i8.merged_rows) {
+    // stride 1: a row of the box is BW*16 contiguous bytes; describe it as 2*BW 8-byte elements so
+    // the copy engine moves whole rows (4-D map: x in 8-byte units, h, channel block, image)
+    cuuint64_t dims[4] = {(cuuint64_t)IW * 2, (cuuint64_t)IH, (cuuint64_t)CB, (cuuint64_t)pl.i8.N};
+    cuuint64_t strides[3] = {(cuuint64_t)IW * 16, (cuuint64_t)IH * IW * 16, (cuuint64_t)CB * IH * IW * 16};
+    cuuint32_t box[4] = {(cuuint32_t)pl.i8.BW * 2, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8cfg.KC, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&pl.i8.tmap[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(input), dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    pl.tmap_for = input;
+    return ELB_OK;
+  }
   for (int ph = 0; ph < s; ++ph)
     for (int pw = 0; pw < s; ++pw) {
       const cuuint64_t Hp = (IH - ph + s - 1) / s, Wp = (IW - pw + s - 1) / s;
@@ -294,6 +308,8 @@ int setup_i8_direct(elb_conv &pl) {
     if (mode == I8_MODE_FLAT) {
       p.m_tiles = (p.M + 127) / 128;
     } else {
+      const char *nomerge = getenv("ELB_I8_NO_MERGED_ROWS");      // tuning experiments only
+      p.merged_rows = (p.stride == 1 && !(nomerge && atoi(nomerge) > 0)) ? 1 : 0;
       choose_box(p.OH, p.OW, p.BW, p.BH);
       p.tiles_w = (p.OW + p.BW - 1) / p.BW;
       p.tiles_h = (p.OH + p.BH - 1) / p.BH;

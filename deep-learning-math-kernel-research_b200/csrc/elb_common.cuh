@@ -128,6 +128,7 @@ struct I8ConvParams {
   int taps, CBG, k_stages;           // K loop: stage = (tap, group of KC channel blocks)
   int n_tiles, m_tiles;
   int BW, BH, tiles_w, tiles_h;      // BOX mode tile = BH x BW output pixels (BH*BW = 128)
+  int merged_rows;                   // BOX mode, stride 1: 4-D tensor map over 8-byte elements
 };
 
 enum : int { I8_MODE_FLAT = 0, I8_MODE_BOX = 1 };

@@ -121,6 +121,13 @@ __device__ __forceinline__ void tma_tile_3d(void *smem_dst, const void *tmap, in
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_tile_4d(void *smem_dst, const void *tmap, int c0, int c1, int c2,
+                                            int c3, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_tile_5d(void *smem_dst, const void *tmap, int c0, int c1, int c2,
                                             int c3, int c4, uint64_t *bar) {
   asm volatile(

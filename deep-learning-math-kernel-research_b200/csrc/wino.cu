@@ -12,10 +12,12 @@
 //   1. wino_input_kernel: reads nChw16c, computes V = B^T d B for every 6x6 tile and writes it
 //      DIRECTLY in the operand image of the GEMM: for each of the 36 positions a, each 128-tile
 //      row block and each K stage, [K chunk of 16 B][128 rows][16 B] -- so one GEMM stage of A is
-//      one contiguous bulk TMA copy.  fp32: two planes, hi = tf32(V) and lo = V - hi (3xTF32
-//      split); int8: V is quantised to u8 here (sat(rne(fma(V, iS/tS, tz)))).
+//      one contiguous bulk TMA copy.  fp32: V is stored as plain fp32; int8: V is quantised to u8
+//      here (sat(rne(fma(V, iS/tS, tz)))).
 //   2. wino_gemm_kernel: 36 independent GEMMs M[a] = V[a] * U[a]^T on tcgen05 tensor cores with
-//      TMEM accumulators.  fp32: three kind::tf32 MMAs per K step (lo*hi + hi*lo + hi*hi), fp32
+//      TMEM accumulators.  fp32: four splitter warps turn each landed fp32 stage of V into its
+//      tf32 planes hi = tf32(V), lo = V - hi in shared memory (the weights' planes are prepared
+//      once per plan), then three kind::tf32 MMAs per K step (lo*hi + hi*lo + hi*hi) with fp32
 //      accumulation.  int8: kind::i8 with s32 accumulation and the fp32 de-scale
 //      fma(acc, scale[a][oc], shift[a][oc]) in the epilogue.  Same warp roles, ring of
 //      shared-memory stages and bounded waits as the direct-convolution kernel.
@@ -39,11 +41,13 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int GEMM_STAGES = 4;
-constexpr int A_STAGE_BYTES = 16384;          // fp32: 2 planes x 4 chunks x 2 KB; int8: 8 chunks x 2 KB
+constexpr int A_STAGE_BYTES = 16384;          // in shared memory. fp32: hi + lo planes x 4 chunks x 2 KB; int8: 8 chunks x 2 KB
+constexpr int A_RAW_BYTES = 8192;             // fp32 only: one stage of V as it lies in global memory (4 chunks x 2 KB)
+constexpr int GEMM_CONV_WARPS = 4;            // fp32 only: warps that split a raw stage into its tf32 hi / lo planes
 constexpr int MAX_BN = 256;
 constexpr int B_STAGE_MAX = 128 * MAX_BN;     // fp32: 2 x 4 x BN x 16; int8: 8 x BN x 16  (= 128*BN)
 constexpr int GEMM_EPI_WARPS = 8;
-constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32;
+constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32 + GEMM_CONV_WARPS * 32;
 constexpr size_t WORKSPACE_BUDGET = size_t(6) << 30;   // transform-domain buffers per chunk
 
 enum : int { KIND_F32 = 0, KIND_I8 = 1 };
@@ -185,21 +189,11 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__
         const size_t off = ((((static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4;
         *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) + off) = live ? w : 0u;
       } else {
-        // stage = this channel block; planes hi / lo; chunk = quad
-        float4 hi, lo;
-        float *hp = &hi.x, *lp = &lo.x;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t hb;
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v[j][c]));
-          const float h = __uint_as_float(hb);
-          hp[c] = h;
-          lp[c] = __fsub_rn(v[j][c], h);
-        }
+        // stage = this channel block, chunk = quad; plain fp32 (the GEMM kernel splits it into its
+        // tf32 hi / lo planes in shared memory, so V crosses HBM once, not twice)
         const size_t stage = (static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + cb;
-        float *base = static_cast<float *>(p.a_img) + stage * (A_STAGE_BYTES / 4);
-        *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = hi;
-        *reinterpret_cast<float4 *>(base + ((4 + quad) * BM + row) * 4) = lo;
+        float *base = static_cast<float *>(p.a_img) + stage * (A_RAW_BYTES / 4);
+        *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
       }
     }
   }
@@ -221,9 +215,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_MAX;
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + GEMM_STAGES * STAGE_BYTES);
+  // ring of operand stages, then (fp32 only) the ring of raw fp32 A stages the copies land in
+  uint8_t *raw_ring = smem + GEMM_STAGES * STAGE_BYTES;
+  uint64_t *full = reinterpret_cast<uint64_t *>(raw_ring + GEMM_STAGES * A_RAW_BYTES);
   uint64_t *empty = full + GEMM_STAGES;
-  uint64_t *tfull = empty + GEMM_STAGES;
+  uint64_t *cfull = empty + GEMM_STAGES;       // fp32: hi / lo planes of stage s are written
+  uint64_t *tfull = cfull + GEMM_STAGES;
   uint64_t *tempty = tfull + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -239,6 +236,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     for (int s = 0; s < GEMM_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      mbar_init(&cfull[s], GEMM_CONV_WARPS);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
@@ -263,18 +261,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const int a = tile / tiles_per_a;
       const int r = tile - a * tiles_per_a;
       const int nt = r / p.m_tiles, mt = r - nt * p.m_tiles;
-      const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + mt) * p.k_stages * A_STAGE_BYTES;
+      // fp32: A arrives as plain fp32 (8 KB per stage) in the raw ring; int8: straight into the stage
+      const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
+      const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + mt) * p.k_stages * a_gbytes;
       const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * b_stage_bytes;
       for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
         const int s = it % GEMM_STAGES;
         const uint32_t ph = (it / GEMM_STAGES) & 1u;
+        // empty[s] is committed by the MMAs of the stage's previous use, which also implies that the
+        // splitter warps are done with raw slot s
         if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
-        if (lane == 0) {
-          uint8_t *a_dst = smem + s * STAGE_BYTES;
-          mbar_arrive_expect_tx(&full[s], A_STAGE_BYTES + b_stage_bytes);
-          tma_bulk_g2s(a_dst, a_src + static_cast<size_t>(ks) * A_STAGE_BYTES, A_STAGE_BYTES, &full[s]);
-          tma_bulk_g2s(a_dst + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_stage_bytes, b_stage_bytes, &full[s]);
-        }
+        uint8_t *stage = smem + s * STAGE_BYTES;
+        uint8_t *a_dst = p.kind == KIND_F32 ? raw_ring + s * A_RAW_BYTES : stage;
+        if (lane == 0) mbar_arrive_expect_tx(&full[s], a_gbytes + b_stage_bytes);
+        __syncwarp();
+        // A and B are issued by two different lanes so that both copies are in flight together
+        if (lane == 0) tma_bulk_g2s(a_dst, a_src + static_cast<size_t>(ks) * a_gbytes, a_gbytes, &full[s]);
+        if (lane == 1)
+          tma_bulk_g2s(stage + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_stage_bytes, b_stage_bytes, &full[s]);
         __syncwarp();
       }
     }
@@ -294,6 +298,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           const int s = it % GEMM_STAGES;
           const uint32_t ph = (it / GEMM_STAGES) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          if (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
@@ -323,6 +328,43 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       }
     }
     __syncwarp();
+  } else if (warp >= 2 + GEMM_EPI_WARPS) {
+    // -------- splitter (fp32 only): raw fp32 stage -> tf32 hi plane + residual lo plane, the
+    // operands of the 3xTF32 product.  hi = round-to-nearest tf32(x), lo = x - hi (exact).
+    if (p.kind == KIND_F32) {
+      const int tid_c = (warp - 2 - GEMM_EPI_WARPS) * 32 + lane;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = it % GEMM_STAGES;
+          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          if (!mbar_wait_warp(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          const float4 *raw = reinterpret_cast<const float4 *>(raw_ring + s * A_RAW_BYTES);
+          float4 *hi = reinterpret_cast<float4 *>(smem + s * STAGE_BYTES);
+          float4 *lo = hi + A_RAW_BYTES / 16;
+#pragma unroll
+          for (int j = 0; j < A_RAW_BYTES / 16 / (GEMM_CONV_WARPS * 32); ++j) {
+            const int u = tid_c + j * GEMM_CONV_WARPS * 32;
+            const float4 v = raw[u];
+            const float x[4] = {v.x, v.y, v.z, v.w};
+            float h[4], l[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t hb;
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[c]));
+              h[c] = __uint_as_float(hb);
+              l[c] = __fsub_rn(x[c], h[c]);
+            }
+            hi[u] = make_float4(h[0], h[1], h[2], h[3]);
+            lo[u] = make_float4(l[0], l[1], l[2], l[3]);
+          }
+          fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&cfull[s]);
+        }
+      }
+    }
   } else {
     // -------- epilogue: one tile row (= one Winograd tile) per thread, 16 channels at a time
     const int quarter = warp & 3, half = (warp - 2) >> 2;
@@ -382,7 +424,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   }
 }
 
-constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * (A_STAGE_BYTES + B_STAGE_MAX) + (2 * GEMM_STAGES + 4) * 8 + 16 + 128;
+constexpr int GEMM_SMEM_BYTES =
+    GEMM_STAGES * (A_STAGE_BYTES + B_STAGE_MAX + A_RAW_BYTES) + (3 * GEMM_STAGES + 4) * 8 + 16 + 128;
+static_assert(GEMM_SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 
 // ------------------------------------------------------------------------------ output transform
 struct WinoOutParams {
@@ -579,7 +623,8 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   w->BN = host::alignup((w->OCP + w->n_tiles - 1) / w->n_tiles, 16);
   // chunk of whole images whose transform-domain buffers fit the budget
   const size_t tiles_img = static_cast<size_t>(g.ht) * g.wt;
-  const size_t per_tile = static_cast<size_t>(36) * (static_cast<size_t>(g.k_stages) * A_STAGE_BYTES / BM + static_cast<size_t>(w->OCP) * 4);
+  const size_t a_gbytes = w->kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;    // one stage of A in global memory
+  const size_t per_tile = static_cast<size_t>(36) * (static_cast<size_t>(g.k_stages) * a_gbytes / BM + static_cast<size_t>(w->OCP) * 4);
   size_t imgs = WORKSPACE_BUDGET / (per_tile * tiles_img);
   if (imgs < 1) imgs = 1;
   if (imgs > static_cast<size_t>(d.n)) imgs = d.n;
@@ -588,7 +633,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   g.T = static_cast<int>(imgs * tiles_img);
   g.m_tiles = (g.T + BM - 1) / BM;
   g.Tpad = g.m_tiles * BM;
-  w->a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * A_STAGE_BYTES;
+  w->a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * a_gbytes;
   w->b_bytes = static_cast<size_t>(36) * w->n_tiles * g.k_stages * 128 * w->BN;
   w->m_bytes = static_cast<size_t>(36) * g.OCB * g.Tpad * 16 * 4;
   w->in_img_bytes = static_cast<size_t>(w->ICP) * d.ih * d.iw * (d.dt_input == ELB_F32 ? 4 : 1);
@@ -915,7 +960,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   const int n_tiles = (OCP + MAX_BN - 1) / MAX_BN;
   const int BN = host::alignup((OCP + n_tiles - 1) / n_tiles, 16);
   const size_t b_bytes = static_cast<size_t>(36) * n_tiles * g.k_stages * 128 * BN;
-  const size_t a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * A_STAGE_BYTES;
+  const size_t a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * A_RAW_BYTES;
   const size_t m_bytes = static_cast<size_t>(36) * g.OCB * g.Tpad * 16 * 4;
   const size_t need = 256 + b_bytes + a_bytes + m_bytes;
   if (need > ELB_NOALLOC_SCRATCH_BYTES) {
