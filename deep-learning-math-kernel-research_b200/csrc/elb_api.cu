@@ -430,6 +430,7 @@ int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
     case ELB_KERNEL_I8_DEPTHWISE: {
       std::string err;
       int nl = 0;
+      pl.wino.trace = pl.d_trace;
       int rc = wino_run(pl.wino, out, in, pl.d_acc_dump, pl.d_status, pl.num_sms, s, nl, err);
       pl.launches += nl;
       if (rc != ELB_OK) return fail(rc, "%s", err.c_str());

@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__
 struct WinoGemmParams {
   const uint8_t *a_img;     // [36][m_tiles][k_stages][A_STAGE_BYTES]
   const uint8_t *b_img;     // [36][n_tiles][k_stages][128*BN bytes]
-  float *m_out;             // [36][OCB][Tpad][16] fp32
+  float *m_out;             // [36][OCB*4 channel quads][Tpad][4] fp32
   const float *scale;       // int8: [36][OCP]
   const float *shift;       // int8: [36][OCP]
   int32_t *acc_dump;        // int8, optional: [36][T][OCP]
@@ -404,9 +404,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
               for (int i = 0; i < 16; ++i) d[i] = static_cast<int>(rr[i]);
             }
           }
-          float4 *o = reinterpret_cast<float4 *>(p.m_out + ((static_cast<size_t>(a) * p.OCB + ocb) * p.Tpad + t) * 16);
+          // M[a][channel quad][tile][4]: the 32 lanes of a warp are 32 consecutive tiles, so each of
+          // the four stores below writes 512 contiguous bytes
+          float *o = p.m_out + ((static_cast<size_t>(a) * p.OCB + ocb) * 4 * p.Tpad + t) * 4;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) o[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<float4 *>(o + static_cast<size_t>(i) * p.Tpad * 4) =
+                make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
         }
       }
       tc_fence_before_sync();
@@ -430,7 +434,7 @@ static_assert(GEMM_SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a 
 
 // ------------------------------------------------------------------------------ output transform
 struct WinoOutParams {
-  const float *m_in;    // [36][OCB][Tpad][16]
+  const float *m_in;    // [36][OCB*4 channel quads][Tpad][4]
   const float *bias;    // [OCP] or null
   void *out;            // nChw16c f32 / u8 / s8, first image of the chunk
   WinoGeom g;
@@ -455,7 +459,7 @@ __global__ void __launch_bounds__(256) wino_output_kernel(const __grid_constant_
 #pragma unroll
     for (int i = 0; i < 6; ++i) {
       const float4 v = *reinterpret_cast<const float4 *>(
-          p.m_in + ((static_cast<size_t>(i * 6 + j) * g.OCB + ocb) * g.Tpad + t) * 16 + quad * 4);
+          p.m_in + (((static_cast<size_t>(i * 6 + j) * g.OCB + ocb) * 4 + quad) * g.Tpad + t) * 4);
       col[i][0] = v.x; col[i][1] = v.y; col[i][2] = v.z; col[i][3] = v.w;
     }
 #pragma unroll

@@ -9,6 +9,7 @@ namespace elb {
 struct WinoImpl;
 struct WinoPlan {
   WinoImpl *impl = nullptr;
+  void *trace = nullptr;     // optional debug timeline of the GEMM kernel (64 int64 slots per CTA)
 };
 
 // Build the launch geometry for pl from the descriptor (no device work).
