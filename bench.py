@@ -165,6 +165,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="images per GPU instead of the workload's own batch (small profiler captures only; "
+                         "the reported line then names the reduced batch)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -173,7 +176,7 @@ def main():
     wl = WORKLOADS[args.workload]
 
     import refutil as R
-    case = R.baseline_case(args.workload)
+    case = R.baseline_case(args.workload, args.batch)
     config = {"workload": f"{args.workload}: {wl['desc']}", "batch_per_gpu": case.n,
               "global_batch": case.n * max(world, 1), "parallelism": f"minibatch split, {max(world,1)} x replicated weights",
               "cache": "ring of buffer sets larger than L2 (126 MB), one set per step"}

@@ -23,6 +23,8 @@
 #   -include string/cstdint include/euler.hpp uses std::string / uint8_t without including them
 #   -faligned-new           alignas(64) classes are new'ed under -std=c++11
 #   -mf16c                  F16C intrinsics used by the half-precision variants
+# and the int8 depthwise units are compiled with -include ref_gxx_unaligned.h (unaligned 64-byte
+# moves where g++ would emit aligned ones; no arithmetic changes).
 set -euo pipefail
 REF=${1:-/root/reference}
 HERE=$(cd "$(dirname "$0")" && pwd)
@@ -56,11 +58,14 @@ fi
 SRCS=$(ls "$REF"/src/*.cpp "$REF"/src/common/el_log.cpp "$OUT"/kgen/*.cpp)
 compile_one() {
   src=$1; obj="$OUT/obj/$(basename "${src%.cpp}").o"
-  if [ ! -f "$obj" ] || [ "$src" -nt "$obj" ]; then
-    $CXX $FLAGS -c "$src" -o "$obj"
+  extra=""
+  # the int8 depthwise units need unaligned 64-byte moves under g++ (see ref_gxx_unaligned.h)
+  case "$(basename "$src")" in *depthwise*) extra="-include $HERE/ref_gxx_unaligned.h";; esac
+  if [ ! -f "$obj" ] || [ "$src" -nt "$obj" ] || { [ -n "$extra" ] && [ "$HERE/ref_gxx_unaligned.h" -nt "$obj" ]; }; then
+    $CXX $FLAGS $extra -c "$src" -o "$obj"
   fi
 }
-export -f compile_one; export OUT CXX FLAGS
+export -f compile_one; export OUT CXX FLAGS HERE
 echo "$SRCS" | xargs -P "$JOBS" -I{} bash -c 'compile_one {}'
 
 # 3. link

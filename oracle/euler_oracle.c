@@ -582,4 +582,100 @@ int orc_direct_f64_conv(const orc_conv_t *p, const float *in, const float *w, co
   return 0;
 }
 
+/* ------------------------------------------------------------------------------------------
+ * INT8 depthwise 3x3 convolution (g = ic = oc), u8 input, f32 goihw weights, u8 / s8 output.
+ * Reference: src/elx_int8_conv_direct_depthwise.cpp (constructor :14-131, weight preparation
+ * trans_weights_3x3 :202-292, conv_c160 :295-318), src/elx_int8_conv_direct_depthwise_xopt.hpp:19-66,
+ * kernel src/kernel/elk_u8s8_depthwise_conv.hxx:288-474.
+ *
+ * Weights, per channel c (:208-237): absmax over the 9 taps, q = (int8) rint((w * 127) / absmax),
+ * Sw = absmax / 127.  Constants (:263-291): scale = (iS * Sw) * (1/oS);
+ * shift = (bias * (1/oS) + oz) - ((iz * Sq) * scale) with Sq = the sum of ALL nine q of the channel
+ * (no border correction: a padded tap contributes 0 to the accumulator but its q stays in Sq).
+ *
+ * Output rows are cut into chunks of T = flatting.t pixels (0 means 1; the last chunk holds the
+ * remainder Tr, :76-80).  Epilogue per pixel f = fma(acc, scale, shift), ReLU clamp, then
+ *   s8 output: round to nearest even, signed saturation;
+ *   u8 output: the first 4*floor(L/4) pixels of a chunk of length L go four at a time through
+ *     u = (int32) floor(f)  (round toward minus infinity, NO saturation),
+ *     word = u0 + (u1 << 8) + (u2 << 16) + (u3 << 24)  in 32-bit wrap-around arithmetic, and byte k
+ *     of word is pixel k (elk_u8s8_depthwise_conv.hxx:257-286, 406-455); the remaining L % 4 pixels
+ *     are rounded to nearest even and saturated as unsigned (:219-255, 456-473).
+ * with_ip_sum is accepted and has no effect (the attribute bit is never read by the kernel).
+ * ------------------------------------------------------------------------------------------ */
+static inline int32_t cvt_i32(float r) {     /* cvtps_epi32 result for an already rounded float */
+  if (!(r >= -2147483648.0f && r < 2147483648.0f)) return INT32_MIN;
+  return (int32_t)r;
+}
+
+int orc_int8_depthwise(const orc_conv_t *p, int T, const uint8_t *in, const float *w, const float *bias,
+                       void *out, int32_t *acc_dump) {
+  if (p->ic != p->oc || p->kh != 3 || p->kw != 3 || p->out_type == ORC_F32) return -2;
+  const int G = ALIGNUP(p->ic, V), g = p->ic;
+  if (T <= 0) T = 1;
+  int8_t *q = (int8_t *)calloc((size_t)G * 9, 1);
+  float *scale = (float *)calloc(G, sizeof(float)), *shift = (float *)calloc(G, sizeof(float));
+  if (!q || !scale || !shift) return -1;
+  const float orepS = 1.0f / p->out_scale;
+  for (int c = 0; c < g; ++c) {
+    float m = 0.0f;
+    for (int k = 0; k < 9; ++k) { float a = fabsf(w[c * 9 + k]); if (a > m) m = a; }
+    int sq = 0;
+    for (int k = 0; k < 9; ++k) {
+      float t = w[c * 9 + k] * 127.0f;
+      t = t / m;
+      q[c * 9 + k] = (int8_t)rintf(t);
+      sq += q[c * 9 + k];
+    }
+    float Sw = m / 127.0f;
+    float qs = p->in_scale * Sw;
+    qs = qs * orepS;
+    float b = (p->with_bias && bias) ? bias[c] : 0.0f;
+    float t0 = fmaf(b, orepS, p->out_z);
+    float zq = p->in_z * (float)sq;
+    scale[c] = qs;
+    shift[c] = fmaf(-zq, qs, t0);
+  }
+  const int wt = (p->ow + T - 1) / T;
+  const int Tr = p->ow % T ? p->ow % T : T;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int n = 0; n < p->n; ++n)
+    for (int c = 0; c < g; ++c)
+      for (int oh = 0; oh < p->oh; ++oh)
+        for (int ck = 0; ck < wt; ++ck) {
+          const int L = ck == wt - 1 ? Tr : T;
+          const int nfloor = p->out_type == ORC_U8 ? 4 * (L / 4) : 0;
+          float f[64 * 4];
+          for (int j = 0; j < L; ++j) {
+            const int ow = ck * T + j;
+            int32_t acc = 0;
+            for (int kh = 0; kh < 3; ++kh) {
+              int ih = oh * p->stride_h - p->pad_t + kh;
+              if (ih < 0 || ih >= p->ih) continue;
+              for (int kw = 0; kw < 3; ++kw) {
+                int iw = ow * p->stride_w - p->pad_l + kw;
+                if (iw < 0 || iw >= p->iw) continue;
+                acc += (int32_t)in[in_index(p, n, c, ih, iw)] * (int32_t)q[c * 9 + kh * 3 + kw];
+              }
+            }
+            if (acc_dump) acc_dump[out_index(p, n, c, oh, ow)] = acc;
+            float v = fmaf((float)acc, scale[c], shift[c]);
+            if (p->with_relu) {
+              v = v > p->relu_lo ? v : p->relu_lo;
+              v = v < p->relu_hi ? v : p->relu_hi;
+            }
+            f[j] = v;
+          }
+          for (int j = 0; j < nfloor; j += 4) {
+            uint32_t word = 0;
+            for (int k = 0; k < 4; ++k) word += (uint32_t)cvt_i32(floorf(f[j + k])) << (8 * k);
+            for (int k = 0; k < 4; ++k)
+              ((uint8_t *)out)[out_index(p, n, c, oh, ck * T + j + k)] = (uint8_t)(word >> (8 * k));
+          }
+          for (int j = nfloor; j < L; ++j) store_q(p, out, out_index(p, n, c, oh, ck * T + j), f[j]);
+        }
+  free(q); free(scale); free(shift);
+  return 0;
+}
+
 int orc_struct_size(void) { return (int)sizeof(orc_conv_t); }
