@@ -1,11 +1,12 @@
 #!/usr/bin/env python
 """Benchmark of the convolution hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|dw] [--impl reference]
 
 One "step" is one convolution call (elx_conv) over one batch of synthetic input of the named
 workload.  Workloads are the benchmark configurations: c1 FP32 Winograd F(4x4,3x3) VGG conv3_2,
-c2 INT8 1x1 ResNet-50 res4 reduce (default), c3 INT8 3x3 stride 2, c4 INT8 Winograd.
+c2 INT8 1x1 ResNet-50 res4 reduce (default), c3 INT8 3x3 stride 2, c4 INT8 Winograd, dw INT8 depthwise 3x3
+(a MobileNet-v1 layer shape; the benchmark configurations name no depthwise case).
 
 Own arm (default): rank r owns one GPU and the whole batch of the workload (weak scaling over the
 minibatch: the path shards by image with replicated weights and has no exchange step, so there is
@@ -49,6 +50,8 @@ WORKLOADS = {
                desc="INT8 u8s8 3x3 stride 2 pad 1 N=64 C=128 K=256 56x56->28x28 bias+ReLU u8 out nChw16c"),
     "c4": dict(metric="effective_conv_tops_int8_winograd", unit="TOP/s", dtype="u8",
                desc="INT8 Winograd F(4x4,3x3) N=128 C=K=512 28x28 s1 p1 f32 out nChw16c"),
+    "dw": dict(metric="effective_conv_tops_int8_depthwise", unit="TOP/s", dtype="u8",
+               desc="INT8 depthwise 3x3 MobileNet-v1 Conv2d_3 N=64 C=128 56x56 s1 p1 bias+ReLU u8 out nChw16c T=14"),
 }
 # published number for exactly this metric/config (2 x Xeon 8180, reference's tuned script comment)
 PUBLISHED = {"c1": 11.2}
@@ -148,7 +151,8 @@ def cpu_reference_run(case, t, steps, warmup, budget_s=12.0):
     import dataclasses
     small = dataclasses.replace(case, n=max(1, min(case.n, 2)))
     ts = R.make_tensors(small)
-    fn = {"fp32": R.oracle_wino_f32}.get(case.types, R.oracle_int8_wino if case.algo == "wino" else R.oracle_int8_conv)
+    fn = {"fp32": R.oracle_wino_f32}.get(case.types, R.oracle_int8_wino if case.algo == "wino" else
+                                         R.oracle_int8_depthwise if case.g > 1 else R.oracle_int8_conv)
     t0 = time.perf_counter()
     fn(small, ts)
     dt = time.perf_counter() - t0

@@ -22,7 +22,7 @@ ROOT = PKG_DIR.parent
 LIB_PATH = PKG_DIR / "lib" / "libeuler_b200.so"
 HOST_LIB_PATH = PKG_DIR / "lib" / "libel.so"
 CSRC = PKG_DIR / "csrc"
-CU_SOURCES = ["elb_api.cu", "int8_conv.cu", "wino.cu", "misc.cu"]
+CU_SOURCES = ["elb_api.cu", "int8_conv.cu", "wino.cu", "depthwise.cu", "misc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
 
@@ -43,7 +43,8 @@ KERNEL_NAMES = {0: "none", 1: "i8_gemm_umma", 2: "i8_conv_umma", 3: "i8_simt", 4
 
 def build(verbose: bool = False) -> Path:
     """Compile csrc/*.cu for sm_100a into lib/libeuler_b200.so (nvcc cross-compiles without a GPU)
-    and the C++ host library lib/libel.so that implements include/euler.hpp on top of it."""
+    and the C++ host library lib/libel.so, which exports the reference's own C++ symbols
+    (eld_conv_t, elx_conv, reorder<>) on top of it."""
     LIB_PATH.parent.mkdir(exist_ok=True)
     srcs = [str(CSRC / s) for s in CU_SOURCES]
     deps = list(CSRC.glob("*")) + [ROOT / "include" / "euler_b200.h"]
@@ -52,14 +53,17 @@ def build(verbose: bool = False) -> Path:
         if verbose:
             print(" ".join(cmd))
         subprocess.check_call(cmd)
+    # The C++ host library defines the reference's own exported symbols and is therefore compiled
+    # with the reference's public headers; where that tree is absent the prebuilt library is kept.
     host_src = PKG_DIR / "host" / "euler_host.cpp"
-    hdeps = [host_src, ROOT / "include" / "euler.hpp", ROOT / "include" / "euler_reorder.hpp", LIB_PATH]
-    if host_src.exists() and (not HOST_LIB_PATH.exists()
-                              or any(p.stat().st_mtime > HOST_LIB_PATH.stat().st_mtime for p in hdeps)):
+    ref_inc = Path(os.environ.get("EULER_REFERENCE_INCLUDE", "/root/reference/include"))
+    hdeps = [host_src, LIB_PATH, ROOT / "include" / "euler_b200.h"]
+    if (ref_inc / "euler.hpp").exists() and (
+            not HOST_LIB_PATH.exists() or any(p.stat().st_mtime > HOST_LIB_PATH.stat().st_mtime for p in hdeps)):
         cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{ROOT / 'include'}",
-               "-o", str(HOST_LIB_PATH), str(host_src), f"-L{LIB_PATH.parent}", "-leuler_b200",
-               "-Wl,-rpath,$ORIGIN"]
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-include", "string",
+               "-include", "cstdint", f"-I{ref_inc}", f"-I{ROOT / 'include'}", "-o", str(HOST_LIB_PATH),
+               str(host_src), f"-L{LIB_PATH.parent}", "-leuler_b200", "-Wl,-rpath,$ORIGIN"]
         if verbose:
             print(" ".join(cmd))
         subprocess.check_call(cmd)
@@ -77,7 +81,7 @@ class ElbConvDesc(C.Structure):
                [("relu_lower", C.c_float), ("relu_upper", C.c_float), ("execution_mode", C.c_int32)] + \
                [(k, C.c_float) for k in ("input_scale", "input_z", "tinput_scale", "tinput_z", "output_scale",
                                          "output_z", "sum_scale", "sum_z")] + \
-               [("sampling_kind", C.c_int32), ("device", C.c_int32)]
+               [("sampling_kind", C.c_int32), ("flatting_t", C.c_int32), ("device", C.c_int32)]
 
 
 class ElbConvInfo(C.Structure):
@@ -192,7 +196,7 @@ class eld_conv_t:
             int(self.f16c_opt), int(self.disable_autoparam), self.relu_bound.lower, self.relu_bound.upper,
             self.execution_mode, self.input_quant.scale, self.input_quant.z, self.wino_tinput_quant.scale,
             self.wino_tinput_quant.z, self.output_quant.scale, self.output_quant.z, self.sum_quant.scale,
-            self.sum_quant.z, int(self.sampling_kind), self.device)
+            self.sum_quant.z, int(self.sampling_kind), int(self.flatting.t), self.device)
 
     def setup(self, fully_setup: bool = True) -> int:
         desc = self._c_desc()

@@ -14,6 +14,7 @@
 #include "elb_common.cuh"
 #include "host_prep.hpp"
 #include "wino.cuh"
+#include "depthwise.cuh"
 
 using namespace elb;
 
@@ -147,12 +148,15 @@ struct elb_conv {
   const void *tmap_for = nullptr;       // input pointer the tensor maps were encoded for
   // winograd
   WinoPlan wino{};
+  // int8 depthwise
+  DwPlan dw{};
 
   ~elb_conv() {
     cudaSetDevice(device);
     for (void *p : {d_wpack, d_wplain, d_scale, d_shift, (void *)d_status, d_in_stage, d_out_stage})
       if (p) cudaFree(p);
     wino_release(wino);
+    dw_release(dw);
     if (stream) cudaStreamDestroy(stream);
   }
 };
@@ -202,6 +206,7 @@ int choose_kernel(const elb_conv_desc_t &d, int algorithm, int tile, const char 
     if (algorithm == ELB_CONV_DIRECT_1X1 && (d.kh != 1 || d.kw != 1)) { *why = "1x1 algorithm on a non-1x1 filter"; return ELB_KERNEL_NONE; }
     if (depthwise) {
       if (d.kh != 3 || d.kw != 3 || d.dt_output == ELB_F32) { *why = "depthwise needs 3x3 and u8/s8 output"; return ELB_KERNEL_NONE; }
+      if (d.fmt_weights != ELB_GOIHW) { *why = "depthwise weights must be goihw"; return ELB_KERNEL_NONE; }
       return ELB_KERNEL_I8_DEPTHWISE;
     }
     if (d.fmt_weights != ELB_OIHW16I16O) { *why = "weights must be OIhw16i16o"; return ELB_KERNEL_NONE; }
@@ -407,10 +412,15 @@ int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
     case ELB_KERNEL_I8_CONV_UMMA:
     case ELB_KERNEL_I8_SIMT: rc = prepare_i8_direct(pl, weights, bias); break;
     case ELB_KERNEL_WINO_F32_UMMA:
-    case ELB_KERNEL_WINO_I8_UMMA:
-    case ELB_KERNEL_I8_DEPTHWISE: {
+    case ELB_KERNEL_WINO_I8_UMMA: {
       std::string err;
       rc = wino_prepare(pl.wino, pl.d, pl.info, weights, bias, err);
+      if (rc != ELB_OK) fail(rc, "%s", err.c_str());
+      break;
+    }
+    case ELB_KERNEL_I8_DEPTHWISE: {
+      std::string err;
+      rc = dw_prepare(pl.dw, pl.d, pl.info, weights, bias, err);
       if (rc != ELB_OK) fail(rc, "%s", err.c_str());
       break;
     }
@@ -425,9 +435,16 @@ int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
     case ELB_KERNEL_I8_GEMM_UMMA:
     case ELB_KERNEL_I8_CONV_UMMA:
     case ELB_KERNEL_I8_SIMT: return run_i8_direct(pl, out, in, s);
-    case ELB_KERNEL_WINO_F32_UMMA:
-    case ELB_KERNEL_WINO_I8_UMMA:
     case ELB_KERNEL_I8_DEPTHWISE: {
+      std::string err;
+      int nl = 0;
+      int rc = dw_run(pl.dw, out, in, pl.d_acc_dump, s, nl, err);
+      pl.launches += nl;
+      if (rc != ELB_OK) return fail(rc, "%s", err.c_str());
+      return rc;
+    }
+    case ELB_KERNEL_WINO_F32_UMMA:
+    case ELB_KERNEL_WINO_I8_UMMA: {
       std::string err;
       int nl = 0;
       pl.wino.trace = pl.d_trace;
@@ -523,6 +540,12 @@ int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
     case ELB_KERNEL_I8_GEMM_UMMA:
     case ELB_KERNEL_I8_CONV_UMMA:
     case ELB_KERNEL_I8_SIMT: rc = setup_i8_direct(*pl); break;
+    case ELB_KERNEL_I8_DEPTHWISE: {
+      std::string err;
+      rc = dw_setup(pl->dw, pl->d, pl->info, pl->num_sms, err);
+      if (rc != ELB_OK) fail(rc, "%s", err.c_str());
+      break;
+    }
     default: {
       std::string err;
       rc = wino_setup(pl->wino, pl->d, pl->info, err);

@@ -605,7 +605,6 @@ struct WinoImpl {
 };
 
 int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, std::string &err) {
-  if (info.kernel == ELB_KERNEL_I8_DEPTHWISE) { err = "int8 depthwise is not implemented yet"; return ELB_UNIMPLEMENTED; }
   if (d.pad_t != 1 || d.pad_l != 1) { err = "Winograd needs pad 1"; return ELB_UNIMPLEMENTED; }
   WinoImpl *w = new WinoImpl();
   pl.impl = w;

@@ -48,8 +48,10 @@ enum { ELB_FORWARD_TRAINING = 0, ELB_FORWARD_INFERENCE = 1, ELB_BACKWARD_DATA = 
 enum { ELB_FINE = 0, ELB_COARSE = 1, ELB_CALIBRATED = 2 };
 
 /* Plain-C mirror of euler::eld_conv_t (include/euler.hpp:110-187).  Tuning knobs of the CPU
- * implementation (flatting / blocking / partition / nthreads / streaming_hint) have no meaning on
- * the GPU and are not part of this struct; execution_mode is carried only to be validated. */
+ * implementation (blocking / partition / nthreads / streaming_hint, flatting.o) have no meaning on
+ * the GPU and are not part of this struct; execution_mode is carried only to be validated.
+ * flatting.t is carried because the reference's int8 depthwise kernel rounds a u8 output pixel
+ * differently depending on its position inside a chunk of flatting.t pixels. */
 typedef struct elb_conv_desc {
   int32_t n, g, ic, oc, ih, iw, oh, ow, kh, kw;        /* dims                      :113-115 */
   int32_t pad_l, pad_r, pad_t, pad_b;                  /* pads                      :116     */
@@ -68,6 +70,7 @@ typedef struct elb_conv_desc {
   float output_scale, output_z;                        /* output_quant              :168     */
   float sum_scale, sum_z;                              /* sum_quant                 :168     */
   int32_t sampling_kind;                               /*                           :169     */
+  int32_t flatting_t;                                  /* flatting.t (depthwise)    :158     */
   int32_t device;                                      /* CUDA device ordinal; -1 = current device */
 } elb_conv_desc_t;
 

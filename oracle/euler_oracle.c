@@ -638,41 +638,59 @@ int orc_int8_depthwise(const orc_conv_t *p, int T, const uint8_t *in, const floa
   }
   const int wt = (p->ow + T - 1) / T;
   const int Tr = p->ow % T ? p->ow % T : T;
+  /* Channels are handled in pairs (2j, 2j+1): the packing adds of the floor path are written with
+   * operator+= on __m512i, which g++ compiles as EIGHT 64-BIT adds, so a carry or borrow out of an
+   * even channel's 32-bit word runs into the odd channel's word (only reachable when a floored
+   * value lies outside [0, 255], i.e. without ReLU or with an output scale that overflows u8). */
 #pragma omp parallel for collapse(2) schedule(static)
   for (int n = 0; n < p->n; ++n)
-    for (int c = 0; c < g; ++c)
+    for (int cp = 0; cp < G / 2; ++cp)
       for (int oh = 0; oh < p->oh; ++oh)
         for (int ck = 0; ck < wt; ++ck) {
           const int L = ck == wt - 1 ? Tr : T;
           const int nfloor = p->out_type == ORC_U8 ? 4 * (L / 4) : 0;
-          float f[64 * 4];
-          for (int j = 0; j < L; ++j) {
-            const int ow = ck * T + j;
-            int32_t acc = 0;
-            for (int kh = 0; kh < 3; ++kh) {
-              int ih = oh * p->stride_h - p->pad_t + kh;
-              if (ih < 0 || ih >= p->ih) continue;
-              for (int kw = 0; kw < 3; ++kw) {
-                int iw = ow * p->stride_w - p->pad_l + kw;
-                if (iw < 0 || iw >= p->iw) continue;
-                acc += (int32_t)in[in_index(p, n, c, ih, iw)] * (int32_t)q[c * 9 + kh * 3 + kw];
+          float *f = (float *)malloc(sizeof(float) * 2 * (size_t)L);
+          for (int e = 0; e < 2; ++e) {
+            const int c = 2 * cp + e;
+            for (int j = 0; j < L; ++j) {
+              const int ow = ck * T + j;
+              int32_t acc = 0;
+              if (c < g)
+                for (int kh = 0; kh < 3; ++kh) {
+                  int ih = oh * p->stride_h - p->pad_t + kh;
+                  if (ih < 0 || ih >= p->ih) continue;
+                  for (int kw = 0; kw < 3; ++kw) {
+                    int iw = ow * p->stride_w - p->pad_l + kw;
+                    if (iw < 0 || iw >= p->iw) continue;
+                    acc += (int32_t)in[in_index(p, n, c, ih, iw)] * (int32_t)q[c * 9 + kh * 3 + kw];
+                  }
+                }
+              if (acc_dump) acc_dump[out_index(p, n, c, oh, ow)] = acc;
+              float v = fmaf((float)acc, scale[c], shift[c]);
+              if (p->with_relu) {
+                v = v > p->relu_lo ? v : p->relu_lo;
+                v = v < p->relu_hi ? v : p->relu_hi;
               }
+              f[e * L + j] = v;
             }
-            if (acc_dump) acc_dump[out_index(p, n, c, oh, ow)] = acc;
-            float v = fmaf((float)acc, scale[c], shift[c]);
-            if (p->with_relu) {
-              v = v > p->relu_lo ? v : p->relu_lo;
-              v = v < p->relu_hi ? v : p->relu_hi;
-            }
-            f[j] = v;
           }
           for (int j = 0; j < nfloor; j += 4) {
-            uint32_t word = 0;
-            for (int k = 0; k < 4; ++k) word += (uint32_t)cvt_i32(floorf(f[j + k])) << (8 * k);
-            for (int k = 0; k < 4; ++k)
-              ((uint8_t *)out)[out_index(p, n, c, oh, ck * T + j + k)] = (uint8_t)(word >> (8 * k));
+            uint64_t sum = 0;
+            for (int k = 0; k < 4; ++k) {
+              uint32_t lo = (uint32_t)cvt_i32(floorf(f[j + k])) << (8 * k);           /* slli_epi32 */
+              uint32_t hi = (uint32_t)cvt_i32(floorf(f[L + j + k])) << (8 * k);
+              sum += (uint64_t)lo | ((uint64_t)hi << 32);                             /* 64-bit add */
+            }
+            for (int e = 0; e < 2; ++e) {
+              uint32_t word = (uint32_t)(sum >> (32 * e));
+              for (int k = 0; k < 4; ++k)
+                ((uint8_t *)out)[out_index(p, n, 2 * cp + e, oh, ck * T + j + k)] = (uint8_t)(word >> (8 * k));
+            }
           }
-          for (int j = nfloor; j < L; ++j) store_q(p, out, out_index(p, n, c, oh, ck * T + j), f[j]);
+          for (int e = 0; e < 2; ++e)
+            for (int j = nfloor; j < L; ++j)
+              store_q(p, out, out_index(p, n, 2 * cp + e, oh, ck * T + j), f[e * L + j]);
+          free(f);
         }
   free(q); free(scale); free(shift);
   return 0;

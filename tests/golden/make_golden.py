@@ -40,17 +40,30 @@ def cases():
         C("g_wino_f32_sum", 1, 16, 32, 8, 8, types="fp32", algo="wino", tile=6, bias=True, sum=True),
         C("g_wino_i8_f32", 1, 32, 32, 8, 8, types="u8f32f32f32", algo="wino", tile=6),
         C("g_wino_i8_u8", 1, 32, 16, 8, 8, types="u8f32u8f32", algo="wino", tile=6, relu=True, bias=True, oscale=2.0),
+        # int8 depthwise 3x3 (g = channels, goihw weights); flt_t is the reference's row chunk T, which
+        # decides which u8 pixels are floored and which are rounded to nearest
+        C("g_dw_s1_u8_t14", 1, 32, 32, 28, 28, g=32, algo="direct", knobs=dict(flt_t=14), **i8),
+        C("g_dw_s1_u8_t7", 1, 48, 48, 14, 14, g=48, algo="direct", knobs=dict(flt_t=7), **i8),
+        C("g_dw_s2_u8_t7", 1, 64, 64, 28, 28, g=64, stride=2, algo="direct", knobs=dict(flt_t=7), **i8),
+        C("g_dw_s2_p0_s8", 1, 32, 32, 15, 15, g=32, stride=2, pad=0, algo="direct", types="u8f32s8f32", bias=True,
+          knobs=dict(flt_t=7)),
+        C("g_dw_s1_u8_norelu_wrap", 1, 32, 32, 12, 20, g=32, algo="direct", types="u8f32u8f32", bias=True, oscale=0.02,
+          knobs=dict(flt_t=6)),
+        C("g_dw_s1_u8_iz", 1, 32, 32, 10, 10, g=32, algo="direct", iz=3.0, knobs=dict(flt_t=5), **i8),
     ]
     return out
 
 
 def main():
     assert R.reference_available(), "oracle/_ref is missing or this CPU has no AVX-512 VNNI"
+    only = sys.argv[1:]           # optional: name prefixes of the fixtures to (re)generate
     for case in cases():
+        if only and not any(case.name.startswith(o) for o in only):
+            continue
         t = R.make_tensors(case)
         if case.algo == "wino" and case.types != "fp32":
             case = R.calibrate_tinput(case, t)
-        if case.algo != "wino":
+        if case.algo != "wino" and case.g == 1:
             # the reference's direct kernels need explicit blocking (its defaults divide by zero):
             # all input-channel blocks in one pass, one 16-channel output block, T <= 7 pixels
             case = dataclasses.replace(case, knobs=dict(blk_i=R.alignup(case.ic) // 16, blk_o=1, flt_o=1,

@@ -36,6 +36,7 @@ def make_desc(case: ConvCase, device: int = -1):
         if case.tscale is not None:
             d.wino_tinput_quant.scale, d.wino_tinput_quant.z = case.tscale, case.tz
         d.sampling_kind = E.CALIBRATED
+    d.flatting.t = int(case.knobs.get("flt_t", 0))     # only the int8 depthwise path reads it
     d.device = device
     return d
 

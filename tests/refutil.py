@@ -139,6 +139,9 @@ def baseline_case(cid: str, n: int | None = None) -> ConvCase:
     if cid == "c4":
         return ConvCase("c4_int8_wino", n or 128, 512, 512, 28, 28, types="u8f32f32f32", algo="wino",
                         tile=6, knobs=dict(xopt=0xa161, blk_i=32, blk_o=1, flt_o=2, flt_t=11, pat_o=16))
+    if cid == "dw":   # MobileNet-v1 Conv2d_3_depthwise shape; chunk T = 14 as in the reference's tuned script
+        return ConvCase("dw_int8_mobilenet_conv3", n or 64, 128, 128, 56, 56, g=128, types="u8f32u8f32",
+                        algo="direct", relu=True, bias=True, knobs=dict(xopt=0xc160, flt_t=14))
     raise KeyError(cid)
 
 
@@ -253,6 +256,20 @@ def oracle_int8_conv(case: ConvCase, t: dict, fused: bool = True, want_acc: bool
     return (out, acc) if want_acc else out
 
 
+def oracle_int8_depthwise(case: ConvCase, t: dict, want_acc: bool = False):
+    """Depthwise 3x3 (g = ic = oc).  The chunk length T of the reference (flatting.t) comes from
+    ``case.knobs['flt_t']``; it decides which pixels of a u8 output are floored and which are
+    rounded to nearest."""
+    lib = oracle_lib()
+    out = np.zeros(out_shape(case), dtype=case.out_dtype)
+    acc = np.zeros(out_shape(case), dtype=np.int32) if want_acc else None
+    p = orc_params(case)
+    rc = lib.orc_int8_depthwise(C.byref(p), int(case.knobs.get("flt_t", 0)), _p(t["input"]), _p(t["weights"]),
+                                _p(t["bias"]), _p(out), _p(acc))
+    assert rc == 0, rc
+    return (out, acc) if want_acc else out
+
+
 def oracle_wino_f32(case: ConvCase, t: dict):
     lib = oracle_lib()
     out = np.zeros(out_shape(case), dtype=np.float32)
@@ -339,10 +356,16 @@ def reference_args(case: ConvCase, knobs: bool = True) -> list:
     return a
 
 
+DROPIN_DRIVER = ROOT / "tests" / "bin" / "euler_driver_b200"   # ref_driver.cpp linked against the product's libel.so
+
+
 def run_reference(case: ConvCase, t: dict, iters: int = 0, warmup: int = 0, threads: int | None = None,
-                  knobs: bool = True, want_output: bool = True):
-    """Run the unmodified reference library on the tensors of ``t``.  Returns (output, info)."""
-    assert reference_available(), "oracle/_ref is not built or this CPU lacks AVX-512 VNNI"
+                  knobs: bool = True, want_output: bool = True, driver: Path | None = None):
+    """Run the unmodified reference library on the tensors of ``t``.  Returns (output, info).
+    ``driver`` selects another build of the same command-line driver (the drop-in test links it
+    against this repository's C++ host library instead of the reference's)."""
+    if driver is None:
+        assert reference_available(), "oracle/_ref is not built or this CPU lacks AVX-512 VNNI"
     with tempfile.TemporaryDirectory(prefix="eulerref_") as td:
         td = Path(td)
         t["input"].tofile(td / "in.bin")
@@ -359,7 +382,7 @@ def run_reference(case: ConvCase, t: dict, iters: int = 0, warmup: int = 0, thre
         ncpu = threads or os.cpu_count() or 1
         env.update(OMP_NUM_THREADS=str(ncpu), KMP_AFFINITY="compact,granularity=fine", KMP_BLOCKTIME="infinite"
                    if iters else "0")
-        r = subprocess.run([str(REF_DIR / "ref_driver")] + args, capture_output=True, text=True, env=env)
+        r = subprocess.run([str(driver or REF_DIR / "ref_driver")] + args, capture_output=True, text=True, env=env)
         line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
         if r.returncode != 0 or not line:
             raise RuntimeError(f"reference failed rc={r.returncode}\nstdout={r.stdout[-2000:]}\nstderr={r.stderr[-2000:]}")

@@ -32,8 +32,8 @@ def test_library_exports_every_declared_symbol(pkg):
 
 
 def test_struct_layout_matches_header(pkg):
-    # 35 int32 + 2 float + 1 int32 + 8 float + 2 int32 = 48 four-byte fields
-    assert C.sizeof(pkg.ElbConvDesc) == 48 * 4
+    # 35 int32 + 2 float + 1 int32 + 8 float + 3 int32 = 49 four-byte fields
+    assert C.sizeof(pkg.ElbConvDesc) == 49 * 4
     assert C.sizeof(pkg.ElbConvInfo) == 4 * 4 + 9 * 8 + 2 * 4
 
 
@@ -100,3 +100,24 @@ def test_cal_ops_matches_reference_formula():
     assert R.baseline_case("c1").cal_ops() == 231_156_482_048 or abs(R.baseline_case("c1").cal_ops() / 231.156e9 - 1) < 1e-3
     assert abs(R.baseline_case("c3").cal_ops() / 28.895e9 - 1) < 1e-3
     assert abs(R.baseline_case("c4").cal_ops() / 451.240e9 - 1) < 1e-3
+
+
+def test_host_library_exports_the_reference_symbols(pkg):
+    """lib/libel.so must define the mangled C++ symbols a program compiled against the reference's
+    euler.hpp / euler_reorder.hpp binds (include/euler.hpp:110-190, src/elx_reorder.cpp:209-232)."""
+    import subprocess
+    lib = pkg.HOST_LIB_PATH
+    if not lib.exists():
+        pytest.skip("libel.so not built (reference headers missing at build time)")
+    out = subprocess.run(["nm", "-D", "--defined-only", str(lib)], capture_output=True, text=True, check=True).stdout
+    syms = {ln.split()[-1] for ln in out.splitlines() if ln.strip()}
+    need = ["_ZN5euler10eld_conv_tC1Ev", "_ZN5euler10eld_conv_tD1Ev", "_ZN5euler10eld_conv_t5setupEb",
+            "_ZN5euler8elx_convERNS_10eld_conv_tEPvS2_S2_S2_"]
+    # reorder<T, dst, src>::reorder(T*, T*, int x4|x5): formats are the enum values of euler.hpp
+    pairs4 = [(1, 2), (2, 1), (1, 3), (3, 1), (5, 7), (7, 5), (5, 6), (6, 5)]
+    pairs5 = [(9, 11), (11, 9), (9, 10), (10, 9)]
+    for t in ("f", "h"):
+        need += [f"_ZN5euler7reorderI{t}Li{d}ELi{s}EJEEC1EP{t}S2_iiii" for d, s in pairs4]
+        need += [f"_ZN5euler7reorderI{t}Li{d}ELi{s}EJEEC1EP{t}S2_iiiii" for d, s in pairs5]
+    missing = [n for n in need if n not in syms]
+    assert not missing, missing

@@ -67,3 +67,29 @@ def test_int8_winograd_close():
     case = R.calibrate_tinput(case, t)
     ref, _ = R.run_reference(case, t)
     assert R.rel_l2(R.oracle_int8_wino(case, t), ref) < 2e-6
+
+
+DW = dict(algo="direct", bias=True)
+
+
+@pytest.mark.parametrize("case", [
+    R.ConvCase("ovr_dw_s1", 2, 32, 32, 16, 16, g=32, types="u8f32u8f32", relu=True, knobs=dict(flt_t=8), **DW),
+    R.ConvCase("ovr_dw_s1_t7", 1, 32, 32, 24, 24, g=32, types="u8f32u8f32", relu=True, knobs=dict(flt_t=7), **DW),
+    R.ConvCase("ovr_dw_s1_t28", 1, 32, 32, 28, 28, g=32, types="u8f32u8f32", relu=True, knobs=dict(flt_t=28), **DW),
+    R.ConvCase("ovr_dw_s2", 2, 64, 64, 16, 16, g=64, stride=2, types="u8f32u8f32", relu=True, knobs=dict(flt_t=8), **DW),
+    R.ConvCase("ovr_dw_s2_p0", 1, 48, 48, 15, 15, g=48, stride=2, pad=0, types="u8f32u8f32", relu=True, oscale=0.05,
+               knobs=dict(flt_t=7), **DW),
+    R.ConvCase("ovr_dw_s8", 1, 32, 32, 28, 28, g=32, types="u8f32s8f32", knobs=dict(flt_t=14), **DW),
+    R.ConvCase("ovr_dw_norelu", 1, 32, 32, 28, 28, g=32, types="u8f32u8f32", knobs=dict(flt_t=14), **DW),
+    R.ConvCase("ovr_dw_overflow", 1, 32, 32, 20, 12, g=32, types="u8f32u8f32", oscale=0.003, knobs=dict(flt_t=6), **DW),
+    R.ConvCase("ovr_dw_iz", 1, 32, 32, 14, 14, g=32, types="u8f32u8f32", relu=True, iz=3.0, knobs=dict(flt_t=5), **DW),
+    R.ConvCase("ovr_dw_t1", 1, 32, 32, 9, 9, g=32, types="u8f32u8f32", relu=True, **DW),
+], ids=lambda c: c.name)
+def test_int8_depthwise_bit_exact(case):
+    """Includes the floor / nearest split by chunk position, the 64-bit packing adds (values outside
+    [0,255] without ReLU or with a small output scale) and a non-zero input zero point."""
+    t = R.make_tensors(case)
+    ref, _ = R.run_reference(case, t)
+    got = R.oracle_int8_depthwise(case, t)
+    cb = case.oc // 16
+    assert np.array_equal(got[:, :cb], ref[:, :cb])
