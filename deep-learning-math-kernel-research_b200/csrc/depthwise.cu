@@ -43,11 +43,14 @@ struct DwParams {
   int32_t *acc_dump;       // optional nChw16c int32
   int N, CB, IH, IW, OH, OW, pad_t, pad_l;
   int T;                   // chunk length of an output row (OW when every pixel is rounded to nearest)
-  int items_chunk;         // ceil(T / 4): 4-pixel items per chunk
   int chunks;              // ceil(OW / T)
-  int items_row;           // chunks * items_chunk
+  int groups_full;         // floored 4-pixel groups in a full chunk  (T / 4, or 0 without floor mode)
+  int floored_row;         // floored groups per output row
+  int rest_row;            // nearest-rounded items per output row (chunk remainders, or ceil(OW/4))
+  int rest_every_chunk;    // floor mode: 1 when full chunks have a remainder (T % 4 != 0)
   int rows_strip;          // output rows per thread
   int strips;              // ceil(OH / rows_strip)
+  long long blocks_floored;   // blocks [0, blocks_floored) work on floored groups, the rest on nearest items
   int out_type, relu, floor_mode;   // floor_mode: u8 output with T >= 4
   float relu_lo, relu_hi;
 };
@@ -81,18 +84,19 @@ template <int S> struct RowWin;
 template <> struct RowWin<1> { uint32_t a[4], b[4]; };             // pixels base..base+3, base+2..base+5
 template <> struct RowWin<2> { uint32_t a[4], b[4], c[4]; };       // base..+3, base+4..+7, (base+8, 0, 0, 0)
 
+// col[k] = address of this thread's word of pixel base+k in row 0 of the plane, or null when the
+// column lies outside the image (its taps then contribute zero)
 template <int S>
-__device__ __forceinline__ void load_row(const DwParams &p, const uint8_t *plane, int ih, int base, int quad,
+__device__ __forceinline__ void load_row(const uint32_t *const (&col)[S == 1 ? 6 : 9], int ih, int IH, int row_words,
                                          RowWin<S> &w) {
   constexpr int NPIX = S == 1 ? 6 : 9;
   uint32_t px[NPIX];
-  const bool row_ok = ih >= 0 && ih < p.IH;
+  const bool row_ok = ih >= 0 && ih < IH;
+  const size_t off = static_cast<size_t>(row_ok ? ih : 0) * row_words;
 #pragma unroll
   for (int k = 0; k < NPIX; ++k) {
-    const int iw = base + k;
     px[k] = 0u;
-    if (row_ok && iw >= 0 && iw < p.IW)
-      px[k] = __ldg(reinterpret_cast<const uint32_t *>(plane + (static_cast<size_t>(ih) * p.IW + iw) * 16) + quad);
+    if (row_ok && col[k] != nullptr) px[k] = __ldg(col[k] + off);
   }
   if constexpr (S == 1) {
     const uint32_t wa[4] = {px[0], px[1], px[2], px[3]}, wb[4] = {px[2], px[3], px[4], px[5]};
@@ -107,125 +111,211 @@ __device__ __forceinline__ void load_row(const DwParams &p, const uint8_t *plane
   }
 }
 
-// acc[pixel][channel] += one filter row (weights word wq = w0 | w1<<8 | w2<<16) over one input row
+// Filter row of 4 channels in the alignments dp4a needs: f0 = (w0,w1,w2,0); stride 1: f1 = (0,w0,w1,w2);
+// stride 2: f1 = (0,0,w0,w1), f2 = (w2,0,0,0).
+struct FilterRow { uint32_t f0[4], f1[4], f2[4]; };
+
+// acc[pixel][channel] += one filter row over one input row
 template <int S>
-__device__ __forceinline__ void mac_row(const RowWin<S> &w, const uint32_t (&wq)[4], int (&acc)[4][4]) {
+__device__ __forceinline__ void mac_row(const RowWin<S> &w, const FilterRow &f, int (&acc)[4][4]) {
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    const uint32_t f = wq[c];
     if constexpr (S == 1) {
-      acc[0][c] = dp4a_us(w.a[c], f, acc[0][c]);            // pixels base+0..2
-      acc[1][c] = dp4a_us(w.a[c], f << 8, acc[1][c]);       // base+1..3
-      acc[2][c] = dp4a_us(w.b[c], f, acc[2][c]);            // base+2..4
-      acc[3][c] = dp4a_us(w.b[c], f << 8, acc[3][c]);       // base+3..5
+      acc[0][c] = dp4a_us(w.a[c], f.f0[c], acc[0][c]);       // pixels base+0..2
+      acc[1][c] = dp4a_us(w.a[c], f.f1[c], acc[1][c]);       // base+1..3
+      acc[2][c] = dp4a_us(w.b[c], f.f0[c], acc[2][c]);       // base+2..4
+      acc[3][c] = dp4a_us(w.b[c], f.f1[c], acc[3][c]);       // base+3..5
     } else {
-      const RowWin<2> &w2 = w;
-      const uint32_t lo2 = f << 16, hi1 = (f >> 16) & 0xFFu;   // (0,0,w0,w1) and (w2,0,0,0)
-      acc[0][c] = dp4a_us(w2.a[c], f, acc[0][c]);            // base+0..2
-      acc[1][c] = dp4a_us(w2.a[c], lo2, acc[1][c]);          // base+2,3 ...
-      acc[1][c] = dp4a_us(w2.b[c], hi1, acc[1][c]);          // ... and base+4
-      acc[2][c] = dp4a_us(w2.b[c], f, acc[2][c]);            // base+4..6
-      acc[3][c] = dp4a_us(w2.b[c], lo2, acc[3][c]);          // base+6,7 ...
-      acc[3][c] = dp4a_us(w2.c[c], hi1, acc[3][c]);          // ... and base+8
+      acc[0][c] = dp4a_us(w.a[c], f.f0[c], acc[0][c]);       // base+0..2
+      acc[1][c] = dp4a_us(w.a[c], f.f1[c], acc[1][c]);       // base+2,3 ...
+      acc[1][c] = dp4a_us(w.b[c], f.f2[c], acc[1][c]);       // ... and base+4
+      acc[2][c] = dp4a_us(w.b[c], f.f0[c], acc[2][c]);       // base+4..6
+      acc[3][c] = dp4a_us(w.b[c], f.f1[c], acc[3][c]);       // base+6,7 ...
+      acc[3][c] = dp4a_us(w.c[c], f.f2[c], acc[3][c]);       // ... and base+8
     }
   }
 }
 
-template <int S>
-__global__ void __launch_bounds__(256) dw_kernel(const __grid_constant__ DwParams p) {
+#ifndef DW_MIN_BLOCKS
+#define DW_MIN_BLOCKS 3      // resident 256-thread blocks per SM the register allocation must allow
+#endif
+constexpr uint32_t MAGIC_BITS = 0x4B400000u;      // bit pattern of 1.5 * 2^23
+constexpr float MAGIC = 12582912.0f;              // 1.5 * 2^23: float(MAGIC_BITS + i) == MAGIC + i for |i| < 2^22
+
+// FAST: every value the epilogue can produce is known (from the folded constants) to lie inside
+// (-2^22, 2^22), and either the output is s8 or ReLU with a non-negative lower bound is on.  Then
+// int <-> float conversions can be done exactly on the FMA pipe by adding 1.5 * 2^23 (the
+// accumulators even start at that bit pattern), rounding toward minus infinity is an add with
+// the .rm modifier, and a floored group whose four values all fit a byte is packed with three
+// multiply-adds; a group with a value above 255 (possible only with an overflowing output scale)
+// takes the exact 64-bit path of the general epilogue instead.
+template <int S, bool FAST>
+__global__ void __launch_bounds__(256, DW_MIN_BLOCKS) dw_kernel(const __grid_constant__ DwParams p) {
   const int quad = threadIdx.x & 3;
-  const long long lin = static_cast<long long>(blockIdx.x) * 64 + (threadIdx.x >> 2);
-  if (lin >= static_cast<long long>(p.strips) * p.items_row) return;
-  const int strip = static_cast<int>(lin / p.items_row);
-  const int item = static_cast<int>(lin - static_cast<long long>(strip) * p.items_row);
-  const int chunk = item / p.items_chunk, j = item - chunk * p.items_chunk;
-  const int x0 = chunk * p.T + 4 * j;                       // first output column of this item
-  const int L = min(p.T, p.OW - chunk * p.T);               // length of this chunk
-  const int width = min(4, L - 4 * j);                      // columns this item owns
-  if (width <= 0) return;
-  const bool floored = p.floor_mode && j < (L >> 2);        // whole 4-pixel group inside 4*floor(L/4)
-  const int n = blockIdx.y / p.CB, cb = blockIdx.y - n * p.CB;
-  const uint8_t *plane = p.in + (static_cast<size_t>(n) * p.CB + cb) * p.IH * p.IW * 16;
+  // Blocks are split by rounding rule so that a warp never has to run both epilogues.
+  const bool floored = static_cast<long long>(blockIdx.x) < p.blocks_floored;
+  const int per_row = floored ? p.floored_row : p.rest_row;
+  // (the host refuses problems whose item count does not fit 31 bits)
+  const unsigned per_plane = static_cast<unsigned>(p.strips) * per_row;
+  const unsigned lin = (floored ? blockIdx.x : blockIdx.x - static_cast<unsigned>(p.blocks_floored)) * 64u + (threadIdx.x >> 2);
+  if (lin >= per_plane * static_cast<unsigned>(p.N * p.CB)) return;
+  const int plane_idx = static_cast<int>(lin / per_plane);
+  const int rem = static_cast<int>(lin - plane_idx * per_plane);
+  const int strip = rem / per_row;
+  const int item = rem - strip * per_row;
+  int x0, width;
+  if (floored) {
+    const int chunk = min(item / p.groups_full, p.chunks - 1);        // the last chunk may hold fewer groups
+    x0 = chunk * p.T + 4 * (item - chunk * p.groups_full);
+    width = 4;
+  } else if (p.floor_mode) {
+    // remainder of a chunk: the L % 4 pixels behind its floored groups
+    const int chunk = p.rest_every_chunk ? item : p.chunks - 1;
+    const int L = min(p.T, p.OW - chunk * p.T);
+    x0 = chunk * p.T + (L & ~3);
+    width = L & 3;
+  } else {
+    x0 = 4 * item;
+    width = min(4, p.OW - x0);
+  }
+  const int n = plane_idx / p.CB, cb = plane_idx - n * p.CB;
   const int ch0 = cb * 16 + quad * 4;
 
-  uint32_t wq[3][4];
+  FilterRow filt[3];
   float sc[4], sh[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
 #pragma unroll
-    for (int kh = 0; kh < 3; ++kh) wq[kh][c] = __ldg(p.wq + (ch0 + c) * 3 + kh);
+    for (int kh = 0; kh < 3; ++kh) {
+      const uint32_t f = __ldg(p.wq + (ch0 + c) * 3 + kh);
+      filt[kh].f0[c] = f;
+      filt[kh].f1[c] = S == 1 ? f << 8 : f << 16;
+      filt[kh].f2[c] = (f >> 16) & 0xFFu;
+    }
     sc[c] = __ldg(p.scale + ch0 + c);
     sh[c] = __ldg(p.shift + ch0 + c);
   }
 
+  constexpr int NPIX = S == 1 ? 6 : 9;
   const int base = x0 * S - p.pad_l;
+  const uint32_t *plane = reinterpret_cast<const uint32_t *>(p.in + static_cast<size_t>(plane_idx) * p.IH * p.IW * 16) + quad;
+  const uint32_t *col[NPIX];
+#pragma unroll
+  for (int k = 0; k < NPIX; ++k) {
+    const int iw = base + k;
+    col[k] = (iw >= 0 && iw < p.IW) ? plane + iw * 4 : nullptr;
+  }
+  const int row_words = p.IW * 4;
   const int oh0 = strip * p.rows_strip;
   const int oh1 = min(p.OH, oh0 + p.rows_strip);
+  const bool clamp_hi = p.relu_hi < 3.0e38f;
+  constexpr int ACC0 = FAST ? static_cast<int>(MAGIC_BITS) : 0;
   // rows[k] = input row oh*S - pad_t + k of the current output row
   RowWin<S> rows[3];
-  load_row<S>(p, plane, oh0 * S - p.pad_t, base, quad, rows[0]);
-  if constexpr (S == 1) load_row<S>(p, plane, oh0 * S - p.pad_t + 1, base, quad, rows[1]);
+  load_row<S>(col, oh0 * S - p.pad_t, p.IH, row_words, rows[0]);
+  if constexpr (S == 1) load_row<S>(col, oh0 * S - p.pad_t + 1, p.IH, row_words, rows[1]);
 
   for (int oh = oh0; oh < oh1; ++oh) {
     const int ih0 = oh * S - p.pad_t;
     if constexpr (S == 1) {
-      load_row<S>(p, plane, ih0 + 2, base, quad, rows[2]);
+      load_row<S>(col, ih0 + 2, p.IH, row_words, rows[2]);
     } else {
-      load_row<S>(p, plane, ih0 + 1, base, quad, rows[1]);
-      load_row<S>(p, plane, ih0 + 2, base, quad, rows[2]);
+      load_row<S>(col, ih0 + 1, p.IH, row_words, rows[1]);
+      load_row<S>(col, ih0 + 2, p.IH, row_words, rows[2]);
     }
     int acc[4][4];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) acc[k][c] = 0;
+      for (int c = 0; c < 4; ++c) acc[k][c] = ACC0;
 #pragma unroll
-    for (int kh = 0; kh < 3; ++kh) mac_row<S>(rows[kh], wq[kh], acc);
+    for (int kh = 0; kh < 3; ++kh) mac_row<S>(rows[kh], filt[kh], acc);
 
     // ---- epilogue: f = fma(acc, scale, shift), ReLU clamp, round, pack, transpose back, store
-    const size_t opix = ((static_cast<size_t>(n) * p.CB + cb) * p.OH + oh) * p.OW + x0;
+    const size_t opix = (static_cast<size_t>(plane_idx) * p.OH + oh) * p.OW + x0;
     if (p.acc_dump) {
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         if (k < width)
           *reinterpret_cast<int4 *>(p.acc_dump + (opix + k) * 16 + quad * 4) =
-              make_int4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+              make_int4(acc[k][0] - ACC0, acc[k][1] - ACC0, acc[k][2] - ACC0, acc[k][3] - ACC0);
     }
     float f[4][4];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        float v = __fmaf_rn(__int2float_rn(acc[k][c]), sc[c], sh[c]);
-        if (p.relu) v = fminf(fmaxf(v, p.relu_lo), p.relu_hi);
+        const float a = FAST ? __fsub_rn(__int_as_float(acc[k][c]), MAGIC) : __int2float_rn(acc[k][c]);
+        float v = __fmaf_rn(a, sc[c], sh[c]);
+        if (p.relu) {
+          v = fmaxf(v, p.relu_lo);
+          if (clamp_hi) v = fminf(v, p.relu_hi);
+        }
         f[k][c] = v;
       }
     uint32_t cw[4] = {0u, 0u, 0u, 0u};       // per channel: bytes = pixels 0..3
-    if (floored) {
-      // word = u0 + (u1 << 8) + (u2 << 16) + (u3 << 24) with 64-bit adds over channel pairs
+    bool packed = false;
+    if (FAST) {
+      if (floored) {
+        uint32_t any = 0u, bits[4][4];
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        unsigned long long sum = 0ull;
+        for (int k = 0; k < 4; ++k)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t lo = static_cast<uint32_t>(cvt_x86(floorf(f[k][2 * e]))) << (8 * k);
-          const uint32_t hi = static_cast<uint32_t>(cvt_x86(floorf(f[k][2 * e + 1]))) << (8 * k);
-          sum += static_cast<unsigned long long>(lo) | (static_cast<unsigned long long>(hi) << 32);
+          for (int c = 0; c < 4; ++c) {
+            bits[k][c] = __float_as_uint(__fadd_rd(f[k][c], MAGIC));     // MAGIC_BITS + floor(f)
+            any |= bits[k][c];
+          }
+        if ((any & 0x003FFF00u) == 0u) {      // all sixteen floored values fit a byte: no carries anywhere
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            cw[c] = bits[0][c] + (bits[1][c] << 8) + (bits[2][c] << 16) + (bits[3][c] << 24) -
+                    MAGIC_BITS * 0x01010101u;
+          packed = true;
         }
-        cw[2 * e] = static_cast<uint32_t>(sum);
-        cw[2 * e + 1] = static_cast<uint32_t>(sum >> 32);
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
+      } else {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const int r = cvt_x86(rintf(f[k][c]));
-          uint32_t b;
-          if (p.out_type == OUT_U8) b = static_cast<uint32_t>(r) > 255u ? 255u : static_cast<uint32_t>(r);
-          else b = static_cast<uint32_t>(max(-128, min(127, r))) & 0xFFu;
-          cw[c] |= b << (8 * k);
+          uint32_t b[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int r = static_cast<int>(__float_as_uint(__fadd_rn(f[k][c], MAGIC)));   // MAGIC_BITS + rne(f)
+            b[k] = static_cast<uint32_t>(p.out_type == OUT_U8
+                                             ? min(r, static_cast<int>(MAGIC_BITS) + 255)
+                                             : max(static_cast<int>(MAGIC_BITS) - 128, min(static_cast<int>(MAGIC_BITS) + 127, r)));
+          }
+          // low bytes of the four words (the low byte of MAGIC_BITS is zero)
+          cw[c] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
         }
+        packed = true;
+      }
+    }
+    if (!packed) {
+      if (floored) {
+        // word = u0 + (u1 << 8) + (u2 << 16) + (u3 << 24) with 64-bit adds over channel pairs
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          unsigned long long sum = 0ull;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t lo = static_cast<uint32_t>(cvt_x86(floorf(f[k][2 * e]))) << (8 * k);
+            const uint32_t hi = static_cast<uint32_t>(cvt_x86(floorf(f[k][2 * e + 1]))) << (8 * k);
+            sum += static_cast<unsigned long long>(lo) | (static_cast<unsigned long long>(hi) << 32);
+          }
+          cw[2 * e] = static_cast<uint32_t>(sum);
+          cw[2 * e + 1] = static_cast<uint32_t>(sum >> 32);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int r = cvt_x86(rintf(f[k][c]));
+            uint32_t b;
+            if (p.out_type == OUT_U8) b = static_cast<uint32_t>(r) > 255u ? 255u : static_cast<uint32_t>(r);
+            else b = static_cast<uint32_t>(max(-128, min(127, r))) & 0xFFu;
+            cw[c] |= b << (8 * k);
+          }
+      }
     }
     uint32_t pw[4];
     transpose4(cw, pw);
@@ -246,6 +336,7 @@ struct DwImpl {
   DwParams p{};
   int stride = 1;
   int G = 0;
+  bool fast = false;       // epilogue values provably inside (-2^22, 2^22), see dw_kernel
   void *d_wq = nullptr, *d_scale = nullptr, *d_shift = nullptr;
 };
 
@@ -281,16 +372,30 @@ int dw_setup(DwPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, int nu
   p.relu = d.with_relu; p.relu_lo = d.relu_lower; p.relu_hi = d.relu_upper;
   p.floor_mode = (p.out_type == OUT_U8 && T >= 4) ? 1 : 0;
   p.T = p.floor_mode ? T : d.ow;       // without floored groups the chunking has no effect
-  p.items_chunk = (p.T + 3) / 4;
   p.chunks = (d.ow + p.T - 1) / p.T;
-  p.items_row = p.chunks * p.items_chunk;
-  // rows per thread: as tall as possible (input rows are reused down the strip) while the grid
-  // still has a few waves of threads for every SM
-  const long long want_threads = static_cast<long long>(num_sms) * 2048 * 3;
-  int rs = 8;
-  while (rs > 1 && static_cast<long long>(d.n) * p.CB * 4 * p.items_row * ((d.oh + rs - 1) / rs) < want_threads) rs >>= 1;
+  const int last = d.ow - (p.chunks - 1) * p.T;           // length of the last chunk
+  if (p.floor_mode) {
+    p.groups_full = p.T / 4;
+    p.floored_row = (p.chunks - 1) * p.groups_full + last / 4;
+    p.rest_every_chunk = (p.T % 4) != 0;
+    p.rest_row = p.rest_every_chunk ? (p.chunks - 1) + ((last % 4) != 0) : ((last % 4) != 0);
+  } else {
+    p.groups_full = 1;
+    p.floored_row = 0;
+    p.rest_every_chunk = 0;
+    p.rest_row = (d.ow + 3) / 4;
+  }
+  // rows per thread: input rows are reused down a strip (2 extra rows per strip at stride 1), but
+  // short strips keep many more threads in flight; 4 to 7 rows measured best on B200
+  int rs = d.oh >= 28 ? 7 : 4;
+  if (d.oh < rs) rs = d.oh;
+  if (const char *e = getenv("ELB_DW_ROWS")) {      // tuning experiments only
+    const int v = atoi(e);
+    if (v >= 1 && v <= 64) rs = v;
+  }
   p.rows_strip = rs;
   p.strips = (d.oh + rs - 1) / rs;
+  p.blocks_floored = (static_cast<long long>(d.n) * p.CB * p.strips * p.floored_row + 63) / 64;
   info.launches_per_call = 1;
   return ELB_OK;
 }
@@ -346,6 +451,11 @@ int dw_prepare(DwPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, cons
     err = "cudaMemcpy of the depthwise constants failed";
     return ELB_GENERAL_ERROR;
   }
+  // largest magnitude the epilogue can see: |acc| <= 9 * 255 * 127
+  float bound = 0.0f;
+  for (int c = 0; c < g; ++c) bound = std::fmax(bound, 291465.0f * std::fabs(scale[c]) + std::fabs(shift[c]));
+  w->fast = bound < 4194304.0f &&
+            (w->p.out_type == OUT_S8 || (d.with_relu && d.relu_lower >= 0.0f));
   w->p.wq = static_cast<const uint32_t *>(w->d_wq);
   w->p.scale = static_cast<const float *>(w->d_scale);
   w->p.shift = static_cast<const float *>(w->d_shift);
@@ -364,11 +474,16 @@ int dw_run(DwPlan &pl, void *out, const void *in, void *acc_dump, cudaStream_t s
   p.in = static_cast<const uint8_t *>(in);
   p.out = out;
   p.acc_dump = static_cast<int32_t *>(acc_dump);
-  const long long items = static_cast<long long>(p.strips) * p.items_row;
-  if (static_cast<long long>(p.N) * p.CB > 65535) { err = "depthwise: n * channel blocks exceeds 65535"; return ELB_UNIMPLEMENTED; }
-  dim3 grid(static_cast<unsigned>((items + 63) / 64), static_cast<unsigned>(p.N * p.CB));
-  if (w->stride == 1) dw_kernel<1><<<grid, 256, 0, s>>>(p);
-  else dw_kernel<2><<<grid, 256, 0, s>>>(p);
+  const long long blocks_rest = (static_cast<long long>(p.N) * p.CB * p.strips * p.rest_row + 63) / 64;
+  if ((p.blocks_floored + blocks_rest) * 64 > 0x7FFFFFFFll) { err = "depthwise: problem too large for one launch"; return ELB_UNIMPLEMENTED; }
+  dim3 grid(static_cast<unsigned>(p.blocks_floored + blocks_rest));
+  if (w->stride == 1) {
+    if (w->fast) dw_kernel<1, true><<<grid, 256, 0, s>>>(p);
+    else dw_kernel<1, false><<<grid, 256, 0, s>>>(p);
+  } else {
+    if (w->fast) dw_kernel<2, true><<<grid, 256, 0, s>>>(p);
+    else dw_kernel<2, false><<<grid, 256, 0, s>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { err = std::string("depthwise launch failed: ") + cudaGetErrorString(e); return ELB_GENERAL_ERROR; }
   launches = 1;
