@@ -107,6 +107,7 @@ def _load():
         "elb_conv_set_accumulator_dump": (i32, [vp, vp]),
         "elb_conv_device_status": (i32, [vp]),
         "elb_conv_launch_count": (u64, [vp]),
+        "elb_conv_set_stage_events": (i32, [vp, C.POINTER(vp)]),
         "elb_conv_destroy": (None, [vp]),
         "elb_last_error": (C.c_char_p, []),
         "elb_device_supported": (i32, [i32]),
@@ -123,7 +124,7 @@ def _load():
 lib = _load()
 EXPORTED_SYMBOLS = ["elb_conv_sizes", "elb_conv_create", "elb_conv_info", "elb_conv_execute", "elb_conv_enqueue",
                     "elb_conv_prepare", "elb_conv_set_accumulator_dump", "elb_conv_device_status",
-                    "elb_conv_launch_count", "elb_conv_destroy", "elb_last_error", "elb_device_supported",
+                    "elb_conv_launch_count", "elb_conv_set_stage_events", "elb_conv_destroy", "elb_last_error", "elb_device_supported",
                     "elb_reorder_nchw_to_nChw16c", "elb_reorder_nChw16c_to_nchw"]
 
 
@@ -240,6 +241,13 @@ class eld_conv_t:
 
     def launch_count(self) -> int:
         return int(lib.elb_conv_launch_count(self.xc))
+
+    def set_stage_events(self, handles) -> int:
+        """Four cudaEvent_t handles (ints) recorded around the three Winograd kernels; None = off."""
+        if handles is None:
+            return lib.elb_conv_set_stage_events(self.xc, None)
+        arr = (C.c_void_p * 4)(*[int(h) for h in handles])
+        return lib.elb_conv_set_stage_events(self.xc, arr)
 
     def close(self):
         if self.xc is not None:

@@ -620,6 +620,16 @@ ELB_API int elb_conv_set_trace(elb_conv_t *plan, void *device_int64) {
   return ELB_OK;
 }
 
+// Measurement hook (not part of the reference surface): four CUDA events that the Winograd path
+// records before its input transform, between its three kernels and after the output transform of
+// the first chunk of every following call, so that a benchmark can time each kernel on the
+// launching stream.  NULL switches it off.  Do not leave it on while capturing a CUDA graph.
+ELB_API int elb_conv_set_stage_events(elb_conv_t *plan, void **cuda_events4) {
+  if (!plan) return ELB_GENERAL_ERROR;
+  for (int i = 0; i < 4; ++i) plan->wino.stage_ev[i] = cuda_events4 ? static_cast<cudaEvent_t>(cuda_events4[i]) : nullptr;
+  return ELB_OK;
+}
+
 int elb_conv_device_status(elb_conv_t *plan) {
   if (!plan) return -1;
   DeviceGuard guard(plan->device);

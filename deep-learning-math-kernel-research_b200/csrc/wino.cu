@@ -769,9 +769,12 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     ip.g.Tpad = m_tiles_run * BM;
     ip.mrepS = w->mrepS; ip.tz = w->tz;
     dim3 gi((m_tiles_run * BM + 63) / 64, g.CB);
+    const bool timed = pl.stage_ev[0] != nullptr && n0 == 0;
+    if (timed) W_TRY(cudaEventRecord(pl.stage_ev[0], s));
     if (w->kind == KIND_I8) wino_input_kernel<true><<<gi, 256, 0, s>>>(ip);
     else wino_input_kernel<false><<<gi, 256, 0, s>>>(ip);
     W_TRY(cudaGetLastError());
+    if (timed) W_TRY(cudaEventRecord(pl.stage_ev[1], s));
     // 2. batched GEMM
     WinoGemmParams gp{};
     gp.a_img = static_cast<const uint8_t *>(w->d_a);
@@ -788,6 +791,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     const int total = 36 * gp.m_tiles * gp.n_tiles;
     wino_gemm_kernel<<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
     W_TRY(cudaGetLastError());
+    if (timed) W_TRY(cudaEventRecord(pl.stage_ev[2], s));
     // 3. output transform
     WinoOutParams op{};
     op.m_in = static_cast<const float *>(w->d_m);
@@ -800,6 +804,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     dim3 go((g.T + 63) / 64, g.OCB);
     wino_output_kernel<<<go, 256, 0, s>>>(op);
     W_TRY(cudaGetLastError());
+    if (timed) W_TRY(cudaEventRecord(pl.stage_ev[3], s));
     launches += 3;
   }
   return ELB_OK;

@@ -10,6 +10,7 @@ struct WinoImpl;
 struct WinoPlan {
   WinoImpl *impl = nullptr;
   void *trace = nullptr;     // optional debug timeline of the GEMM kernel (64 int64 slots per CTA)
+  cudaEvent_t stage_ev[4] = {nullptr, nullptr, nullptr, nullptr};   // optional: recorded before / between / after the three kernels
 };
 
 // Build the launch geometry for pl from the descriptor (no device work).

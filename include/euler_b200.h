@@ -136,6 +136,12 @@ ELB_API int elb_conv_set_accumulator_dump(elb_conv_t *plan, void *device_int32);
  * gave up (see csrc/elb_common.cuh).  Also returned as ELB_GENERAL_ERROR by execute. */
 ELB_API int elb_conv_device_status(elb_conv_t *plan);
 
+/* Measurement hook, no counterpart in the reference: four cudaEvent_t handles which the Winograd
+ * path records before, between and after its three kernels (input transform, batched GEMM,
+ * output transform) on every following call; NULL switches it off.  Must be off during CUDA
+ * graph capture. */
+ELB_API int elb_conv_set_stage_events(elb_conv_t *plan, void **cuda_events4);
+
 /* Number of kernels this plan has launched since it was created. */
 ELB_API uint64_t elb_conv_launch_count(const elb_conv_t *plan);
 
