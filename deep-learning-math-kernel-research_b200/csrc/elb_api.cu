@@ -244,7 +244,7 @@ int encode_i8_tmaps(elb_conv &pl, const void *input) {
     // the copy engine moves whole rows (4-D map: x in 8-byte units, h, channel block, image)
     cuuint64_t dims[4] = {(cuuint64_t)IW * 2, (cuuint64_t)IH, (cuuint64_t)CB, (cuuint64_t)pl.i8.N};
     cuuint64_t strides[3] = {(cuuint64_t)IW * 16, (cuuint64_t)IH * IW * 16, (cuuint64_t)CB * IH * IW * 16};
-    cuuint32_t box[4] = {(cuuint32_t)pl.i8.BW * 2, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8cfg.KC, 1};
+    cuuint32_t box[4] = {(cuuint32_t)pl.i8.BW * 2, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8.box_c, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(&pl.i8.tmap[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(input), dims, strides, box,
                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -259,7 +259,7 @@ int encode_i8_tmaps(elb_conv &pl, const void *input) {
       cuuint64_t dims[5] = {16, Wp, Hp, (cuuint64_t)CB, (cuuint64_t)pl.i8.N};
       cuuint64_t strides[4] = {(cuuint64_t)s * 16, (cuuint64_t)s * IW * 16, (cuuint64_t)IH * IW * 16,
                                (cuuint64_t)CB * IH * IW * 16};
-      cuuint32_t box[5] = {16, (cuuint32_t)pl.i8.BW, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8cfg.KC, 1};
+      cuuint32_t box[5] = {16, (cuuint32_t)pl.i8.BW, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8.box_c, 1};
       cuuint32_t estr[5] = {1, 1, 1, 1, 1};
       void *base = (void *)((const uint8_t *)input + ((size_t)ph * IW + pw) * 16);
       CUresult r = enc(&pl.i8.tmap[ph * s + pw], CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base, dims, strides, box, estr,
@@ -309,7 +309,11 @@ int setup_i8_direct(elb_conv &pl) {
     pl.i8cfg = i8_umma_config(p.OCB, p.CB, p.taps, mode);
     p.n_tiles = (p.OCB * V + pl.i8cfg.BN - 1) / pl.i8cfg.BN;
     p.CBG = (p.CB + pl.i8cfg.KC - 1) / pl.i8cfg.KC;
-    p.k_stages = p.taps * p.CBG;
+    p.Q = p.taps * p.CB;
+    p.k_stages = (p.Q + pl.i8cfg.KC - 1) / pl.i8cfg.KC;
+    // channel blocks one tiled copy fetches: the largest power of two that divides CB, at most KC
+    p.box_c = 1;
+    while (p.box_c * 2 <= pl.i8cfg.KC && p.CB % (p.box_c * 2) == 0) p.box_c *= 2;
     if (mode == I8_MODE_FLAT) {
       p.m_tiles = (p.M + 127) / 128;
     } else {

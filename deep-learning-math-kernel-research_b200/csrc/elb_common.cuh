@@ -125,7 +125,8 @@ struct I8ConvParams {
   int N, IH, IW, OH, OW, KH, KW, stride, pad_t, pad_l;
   int CB, OCB;                       // channel blocks of 16 (input / output)
   int M, HW;                         // FLAT mode: M = N*OH*OW rows, HW = OH*OW
-  int taps, CBG, k_stages;           // K loop: stage = (tap, group of KC channel blocks)
+  int taps, CBG, k_stages;           // K loop over chunks q = tap*CB + cb (16 channels each), KC chunks per stage
+  int Q, box_c;                      // Q = taps*CB chunks in all; one tiled copy fetches box_c chunks of one tap
   int n_tiles, m_tiles;
   int BW, BH, tiles_w, tiles_h;      // BOX mode tile = BH x BW output pixels (BH*BW = 128)
   int merged_rows;                   // BOX mode, stride 1: 4-D tensor map over 8-byte elements

@@ -99,21 +99,23 @@ inline void fold_constants_i8(const I8Weights &wq, const float *bias, bool with_
   }
 }
 
-// Operand image of B for the tcgen05 kernels: [n_tile][k_stage][KC chunks][BN rows][16 bytes],
-// k_stage = tap*CBG + g, chunk j of a stage = channel block g*KC + j, zero where out of range.
+// Operand image of B for the tcgen05 kernels: [n_tile][k_stage][KC chunks][BN rows][16 bytes].
+// K runs over chunks q = tap*CB + cb of 16 input channels (tap-major); stage ks holds chunks
+// ks*KC .. ks*KC+KC-1, zero where q is past the end of K or the row past the last output channel.
 inline std::vector<int8_t> pack_b_i8(const I8Weights &wq, int BN, int KC, int &n_tiles, int &CBG,
                                      int &k_stages) {
   const int CB = wq.ICP / 16;
+  const int Q = wq.taps * CB;
   n_tiles = (wq.OCP + BN - 1) / BN;
   CBG = (CB + KC - 1) / KC;
-  k_stages = wq.taps * CBG;
+  k_stages = (Q + KC - 1) / KC;
   std::vector<int8_t> out((size_t)n_tiles * k_stages * KC * BN * 16, 0);
   for (int nt = 0; nt < n_tiles; ++nt)
-    for (int ks = 0; ks < k_stages; ++ks) {
-      const int tap = ks / CBG, g = ks % CBG;
+    for (int ks = 0; ks < k_stages; ++ks)
       for (int j = 0; j < KC; ++j) {
-        const int cb = g * KC + j;
-        if (cb >= CB) continue;
+        const int q = ks * KC + j;
+        if (q >= Q) continue;
+        const int tap = q / CB, cb = q % CB;
         for (int r = 0; r < BN; ++r) {
           const int o = nt * BN + r;
           if (o >= wq.OCP) continue;
@@ -121,7 +123,6 @@ inline std::vector<int8_t> pack_b_i8(const I8Weights &wq, int BN, int KC, int &n
           std::memcpy(dst, &wq.q[((size_t)o * wq.taps + tap) * wq.ICP + cb * 16], 16);
         }
       }
-    }
   return out;
 }
 

@@ -135,10 +135,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
         uint8_t *a_dst = smem + s * L::STAGE_BYTES;
         uint8_t *b_dst = a_dst + L::A_BYTES;
-        const int tap = ks / p.CBG, g = ks - tap * p.CBG;
-        const int cb0 = g * KC;
         const int8_t *b_src = p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES;
         if (MODE == I8_MODE_FLAT) {
+          const int cb0 = ks * KC;
           const int nchunks = min(KC, p.CB - cb0);
           if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(nchunks * rows * 16 + L::B_BYTES));
           __syncwarp();
@@ -157,13 +156,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
             tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
           }
         } else {
-          // The two copies of a stage are issued by two different lanes: a copy occupies its issuing
-          // thread for a few hundred cycles, and measured ingest is ~30% higher when A and B are in
-          // flight together (45 vs 34 B/clk/SM in a copy-only probe).
-          if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(L::A_BYTES + L::B_BYTES));
+          // K chunks of this stage: q0 .. q0+KC-1 of the flattened (tap, channel block) index; one
+          // tiled copy brings box_c consecutive channel blocks of ONE tap (box_c divides CB, so a
+          // copy never straddles two taps).  Every copy and the weight panel are issued by their
+          // own lane: a copy occupies its issuing thread for a few hundred cycles, and measured
+          // ingest is ~30% higher when the copies of a stage are in flight together.  Chunks past
+          // the end of K are not fetched: their weights are zero, whatever the stage slot holds.
+          const int q0 = ks * KC;
+          const int valid = min(KC, p.Q - q0);
+          if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(valid * (BM * 16) + L::B_BYTES));
           __syncwarp();
-          if (lane == 1) tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
-          if (lane == 0) {
+          if (lane == KC) tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
+          const int q = q0 + lane * p.box_c;
+          if (lane * p.box_c < valid) {
+            const int tap = q / p.CB, cb0 = q - tap * p.CB;
             // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
             const int kh = tap / p.KW, kw = tap - kh * p.KW;
             const int eh = kh - p.pad_t, ew = kw - p.pad_l;
@@ -171,10 +177,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
             const int dw = (ew >= 0) ? ew / p.stride : -((-ew + p.stride - 1) / p.stride);
             const int par_h = eh - dh * p.stride, par_w = ew - dw * p.stride;
             const CUtensorMap *tm = &p.tmap[par_h * p.stride + par_w];
+            uint8_t *dst = a_dst + lane * p.box_c * (BM * 16);
             // stride 1: rows of the box are contiguous in memory, so the map describes them as runs of
             // 8-byte elements (2 per pixel) and the TMA unit moves whole rows instead of 16-byte items
-            if (p.merged_rows) tma_tile_4d(a_dst, tm, (ow0 + dw) * 2, oh0 + dh, cb0, n0, &full[s]);
-            else tma_tile_5d(a_dst, tm, 0, ow0 + dw, oh0 + dh, cb0, n0, &full[s]);
+            if (p.merged_rows) tma_tile_4d(dst, tm, (ow0 + dw) * 2, oh0 + dh, cb0, n0, &full[s]);
+            else tma_tile_5d(dst, tm, 0, ow0 + dw, oh0 + dh, cb0, n0, &full[s]);
           }
           __syncwarp();
         }
@@ -200,11 +207,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           if (it < 16) ELB_TRACE(20 + it);
           const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t b_addr = a_addr + L::A_BYTES;
+          // K = 32 bytes = two chunks per instruction; the last stage may hold fewer than KC chunks
+          const int pairs = (min(KC, p.Q - ks * KC) + 1) >> 1;
 #pragma unroll
           for (int k2 = 0; k2 < KC / 2; ++k2) {
-            const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 2 * (BM * 16), BM * 16, 128);
-            const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * (BN * 16), BN * 16, 128);
-            umma_i8(d_tmem, ad, bd, IDESC, (ks | k2) != 0 ? 1u : 0u);
+            if (k2 < pairs) {
+              const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 2 * (BM * 16), BM * 16, 128);
+              const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * (BN * 16), BN * 16, 128);
+              umma_i8(d_tmem, ad, bd, IDESC, (ks | k2) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
         }
