@@ -47,6 +47,13 @@ constexpr int GEMM_CONV_WARPS = 4;            // fp32 only: warps that split a r
 constexpr int MAX_BN = 256;
 constexpr int B_STAGE_MAX = 128 * MAX_BN;     // fp32: 2 x 4 x BN x 16; int8: 8 x BN x 16  (= 128*BN)
 constexpr int GEMM_EPI_WARPS = 8;
+// Transform kernels: one thread holds a whole 6x6 patch of 4 channels (about 190 registers), so
+// an SM fits ~340 threads.  Small blocks let several of them be resident and drift apart, which
+// overlaps one block's loads with another's arithmetic and stores.
+#ifndef TRANS_THREADS
+#define TRANS_THREADS 64
+#endif
+constexpr int TRANS_TILES = TRANS_THREADS / 4;      // tiles per block (4 threads = the 16 channels of a block)
 constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32 + GEMM_CONV_WARPS * 32;
 constexpr size_t WORKSPACE_BUDGET = size_t(6) << 30;   // transform-domain buffers per chunk
 
@@ -103,15 +110,15 @@ struct WinoInParams {
 };
 
 template <bool IN_U8>
-__global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__ WinoInParams p) {
+__global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_constant__ WinoInParams p) {
   const WinoGeom &g = p.g;
   const int quad = threadIdx.x & 3;
-  const int t = blockIdx.x * 64 + (threadIdx.x >> 2);
+  const int t = blockIdx.x * TRANS_TILES + (threadIdx.x >> 2);
   const int cb = blockIdx.y;
   if (t >= g.Tpad) return;
   const int mt = t >> 7, row = t & 127;
 
-  float m[6][6][4];   // after the pass along h: m[i][w][channel]
+  float m[6][6][4];   // first the 6x6 input patch d[h][w][channel], then (in place) the pass along h: m[i][w][channel]
   const bool live = t < g.T;
   int n = 0, th = 0, tw = 0;
   if (live) {
@@ -123,35 +130,50 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const __grid_constant__
   const int ih0 = 4 * th - g.pad_t, iw0 = 4 * tw - g.pad_l;
   // is_border of the reference's tile iterator (src/elx_conv_wino_trans_input.hpp:247-249)
   const bool border = th == 0 || tw == 0 || th == g.ht - 1 || tw == g.wt - 1;
+  // All 36 loads of the patch are issued before the first use: the kernel is bandwidth-bound and
+  // runs few warps per SM (the patch lives in registers), so the bytes in flight per thread are
+  // what keeps HBM busy.
+  if (IN_U8) {
+    uint32_t raw[6][6];
 #pragma unroll
-  for (int w = 0; w < 6; ++w) {
-    float col[6][4];
-    const int iw = iw0 + w;
+    for (int h = 0; h < 6; ++h)
 #pragma unroll
-    for (int h = 0; h < 6; ++h) {
-      const int ih = ih0 + h;
-      const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
-      const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
-      if (IN_U8) {
-        uchar4 v = make_uchar4(0, 0, 0, 0);
-        if (ok) v = *reinterpret_cast<const uchar4 *>(static_cast<const uint8_t *>(p.in) + pix * 16 + quad * 4);
-        col[h][0] = static_cast<float>(v.x); col[h][1] = static_cast<float>(v.y);
-        col[h][2] = static_cast<float>(v.z); col[h][3] = static_cast<float>(v.w);
-      } else {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ok) v = *reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16 + quad * 4);
-        col[h][0] = v.x; col[h][1] = v.y; col[h][2] = v.z; col[h][3] = v.w;
+      for (int w = 0; w < 6; ++w) {
+        const int ih = ih0 + h, iw = iw0 + w;
+        const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+        const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
+        raw[h][w] = ok ? __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(p.in) + pix * 16) + quad) : 0u;
       }
-    }
+#pragma unroll
+    for (int h = 0; h < 6; ++h)
+#pragma unroll
+      for (int w = 0; w < 6; ++w)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) m[h][w][c] = static_cast<float>((raw[h][w] >> (8 * c)) & 0xFFu);
+  } else {
+#pragma unroll
+    for (int h = 0; h < 6; ++h)
+#pragma unroll
+      for (int w = 0; w < 6; ++w) {
+        const int ih = ih0 + h, iw = iw0 + w;
+        const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+        const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ok) v = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16) + quad);
+        m[h][w][0] = v.x; m[h][w][1] = v.y; m[h][w][2] = v.z; m[h][w][3] = v.w;
+      }
+  }
+  // pass along h, in place
+#pragma unroll
+  for (int w = 0; w < 6; ++w)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const float f[6] = {col[0][c], col[1][c], col[2][c], col[3][c], col[4][c], col[5][c]};
+      const float f[6] = {m[0][w][c], m[1][w][c], m[2][w][c], m[3][w][c], m[4][w][c], m[5][w][c]};
       float o[6];
       bt6(f, o);
 #pragma unroll
       for (int i = 0; i < 6; ++i) m[i][w][c] = o[i];
     }
-  }
   // pass along w, one transformed row at a time, stored as soon as it is ready
 #pragma unroll
   for (int i = 0; i < 6; ++i) {
@@ -442,25 +464,31 @@ struct WinoOutParams {
   float orepS, oz;
 };
 
-__global__ void __launch_bounds__(256) wino_output_kernel(const __grid_constant__ WinoOutParams p) {
+__global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid_constant__ WinoOutParams p) {
   const WinoGeom &g = p.g;
   const int quad = threadIdx.x & 3;
-  const int t = blockIdx.x * 64 + (threadIdx.x >> 2);
+  const int t = blockIdx.x * TRANS_TILES + (threadIdx.x >> 2);
   const int ocb = blockIdx.y;
   if (t >= g.T) return;
   const int n = t / (g.ht * g.wt);
   const int r = t - n * g.ht * g.wt;
   const int th = r / g.wt, tw = r - th * g.wt;
 
+  // all 36 loads first (bytes in flight, see the input transform), then the pass along h
+  float4 raw[6][6];
+#pragma unroll
+  for (int i = 0; i < 6; ++i)
+#pragma unroll
+    for (int j = 0; j < 6; ++j)
+      raw[i][j] = __ldg(reinterpret_cast<const float4 *>(
+          p.m_in + (((static_cast<size_t>(i * 6 + j) * g.OCB + ocb) * 4 + quad) * g.Tpad + t) * 4));
   float m[4][6][4];   // after the pass along h: m[i][j][channel]
 #pragma unroll
   for (int j = 0; j < 6; ++j) {
     float col[6][4];
 #pragma unroll
     for (int i = 0; i < 6; ++i) {
-      const float4 v = *reinterpret_cast<const float4 *>(
-          p.m_in + (((static_cast<size_t>(i * 6 + j) * g.OCB + ocb) * 4 + quad) * g.Tpad + t) * 4);
-      col[i][0] = v.x; col[i][1] = v.y; col[i][2] = v.z; col[i][3] = v.w;
+      col[i][0] = raw[i][j].x; col[i][1] = raw[i][j].y; col[i][2] = raw[i][j].z; col[i][3] = raw[i][j].w;
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -768,11 +796,11 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     ip.g = g;
     ip.g.Tpad = m_tiles_run * BM;
     ip.mrepS = w->mrepS; ip.tz = w->tz;
-    dim3 gi((m_tiles_run * BM + 63) / 64, g.CB);
+    dim3 gi((m_tiles_run * BM + TRANS_TILES - 1) / TRANS_TILES, g.CB);
     const bool timed = pl.stage_ev[0] != nullptr && n0 == 0;
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[0], s));
-    if (w->kind == KIND_I8) wino_input_kernel<true><<<gi, 256, 0, s>>>(ip);
-    else wino_input_kernel<false><<<gi, 256, 0, s>>>(ip);
+    if (w->kind == KIND_I8) wino_input_kernel<true><<<gi, TRANS_THREADS, 0, s>>>(ip);
+    else wino_input_kernel<false><<<gi, TRANS_THREADS, 0, s>>>(ip);
     W_TRY(cudaGetLastError());
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[1], s));
     // 2. batched GEMM
@@ -801,8 +829,8 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     op.g.Tpad = w->g.Tpad;
     op.out_type = w->out_type; op.with_bias = w->with_bias; op.with_relu = w->with_relu; op.with_sum = w->with_sum;
     op.orepS = w->orepS; op.oz = w->oz;
-    dim3 go((g.T + 63) / 64, g.OCB);
-    wino_output_kernel<<<go, 256, 0, s>>>(op);
+    dim3 go((g.T + TRANS_TILES - 1) / TRANS_TILES, g.OCB);
+    wino_output_kernel<<<go, TRANS_THREADS, 0, s>>>(op);
     W_TRY(cudaGetLastError());
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[3], s));
     launches += 3;
@@ -990,7 +1018,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
                                                                 OCP, ICP, BN, n_tiles);
   WinoInParams ip{};
   ip.in = input; ip.a_img = a_img; ip.g = g;
-  wino_input_kernel<false><<<dim3((g.Tpad + 63) / 64, g.CB), 256, 0, s>>>(ip);
+  wino_input_kernel<false><<<dim3((g.Tpad + TRANS_TILES - 1) / TRANS_TILES, g.CB), TRANS_THREADS, 0, s>>>(ip);
   WinoGemmParams gp{};
   gp.a_img = a_img; gp.b_img = reinterpret_cast<const uint8_t *>(b_img); gp.m_out = m_buf;
   gp.status = status;
@@ -1002,7 +1030,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;
   op.out_type = OUT_F32; op.with_bias = d.with_bias; op.with_relu = d.with_relu; op.with_sum = d.with_ip_sum;
   op.orepS = 1.0f; op.oz = 0.0f;
-  wino_output_kernel<<<dim3((g.T + 63) / 64, g.OCB), 256, 0, s>>>(op);
+  wino_output_kernel<<<dim3((g.T + TRANS_TILES - 1) / TRANS_TILES, g.OCB), TRANS_THREADS, 0, s>>>(op);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("kernel launch failed: ") + cudaGetErrorString(e));
   return ELB_OK;
