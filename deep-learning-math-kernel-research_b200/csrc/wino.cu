@@ -144,12 +144,15 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
         const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
         raw[h][w] = ok ? __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(p.in) + pix * 16) + quad) : 0u;
       }
+    // u8 -> fp32 without the conversion unit: a byte permute builds the bit pattern of 2^23 + b,
+    // subtracting 2^23 is exact
 #pragma unroll
     for (int h = 0; h < 6; ++h)
 #pragma unroll
       for (int w = 0; w < 6; ++w)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) m[h][w][c] = static_cast<float>((raw[h][w] >> (8 * c)) & 0xFFu);
+        for (int c = 0; c < 4; ++c)
+          m[h][w][c] = __fsub_rn(__uint_as_float(__byte_perm(raw[h][w], 0x4B000000u, 0x7650 + c)), 8388608.0f);
   } else {
 #pragma unroll
     for (int h = 0; h < 6; ++h)
@@ -200,14 +203,22 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
       const int a = i * 6 + j;
       if (IN_U8) {
         // stage = 8 channel blocks; chunk = cb % 8; 4 bytes per thread
-        uint32_t w = 0;
+        // sat_u8(rne(fma(V, mrepS, tz))): adding 1.5 * 2^23 rounds to nearest even and leaves the
+        // integer in the low bits; as an UNSIGNED number a negative result is huge, so one min()
+        // gives the reference's unsigned saturation (below zero -> 255, above 255 -> 255).  Exact
+        // while |fma| < 2^22; anything larger takes the plain conversion.
+        uint32_t b[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const float q = rintf(__fmaf_rn(v[j][c], p.mrepS, p.tz));
-          // a value that rounds below zero saturates to 255 in the reference (unsigned convert)
-          const uint32_t b = (q < 0.0f || q > 255.0f) ? 255u : static_cast<uint32_t>(q);
-          w |= b << (8 * c);
+          const float f = __fmaf_rn(v[j][c], p.mrepS, p.tz);
+          const uint32_t u = __float_as_uint(__fadd_rn(f, 12582912.0f)) - 0x4B400000u;
+          b[c] = min(u, 255u);
+          if (!(fabsf(f) < 4194304.0f)) {
+            const float q = rintf(f);
+            b[c] = (q < 0.0f || q > 255.0f || q != q) ? 255u : static_cast<uint32_t>(q);
+          }
         }
+        const uint32_t w = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
         const size_t off = ((((static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4;
         *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) + off) = live ? w : 0u;
       } else {
@@ -218,6 +229,94 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
         *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
       }
     }
+  }
+}
+
+// u8 variant (INT8 Winograd): the 36 input words of a thread stay packed (4 channels per word)
+// and the four channels are transformed ONE AFTER THE OTHER, so a thread needs ~36 + 36 + 36
+// registers instead of 36 + 144.  That doubles the warps an SM can hold; the kernel is bound by
+// instruction latency (few warps, long dependent fma chains), not by its 51 MB + 116 MB of traffic.
+__global__ void __launch_bounds__(TRANS_THREADS, 512 / TRANS_THREADS) wino_input_u8_kernel(const __grid_constant__ WinoInParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * TRANS_TILES + (threadIdx.x >> 2);
+  const int cb = blockIdx.y;
+  if (t >= g.Tpad) return;
+  const int mt = t >> 7, row = t & 127;
+  const bool live = t < g.T;
+  int n = 0, th = 0, tw = 0;
+  if (live) {
+    n = t / (g.ht * g.wt);
+    const int r = t - n * g.ht * g.wt;
+    th = r / g.wt;
+    tw = r - th * g.wt;
+  }
+  const int ih0 = 4 * th - g.pad_t, iw0 = 4 * tw - g.pad_l;
+  const bool border = th == 0 || tw == 0 || th == g.ht - 1 || tw == g.wt - 1;   // src/elx_conv_wino_trans_input.hpp:247-249
+  uint32_t raw[6][6], outw[36];
+#pragma unroll
+  for (int h = 0; h < 6; ++h)
+#pragma unroll
+    for (int w = 0; w < 6; ++w) {
+      const int ih = ih0 + h, iw = iw0 + w;
+      const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+      const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
+      raw[h][w] = ok ? __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(p.in) + pix * 16) + quad) : 0u;
+    }
+#pragma unroll
+  for (int a = 0; a < 36; ++a) outw[a] = 0u;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t sel_in = 0x7650u + c;                        // byte c of x, then the three high bytes of y
+    const uint32_t sel_out = 0x3210u ^ ((4u ^ c) << (4 * c));   // byte c of the result <- byte 0 of y
+    float m[6][6];
+    // u8 -> fp32 without the conversion unit: the permute builds the bit pattern of 2^23 + b
+#pragma unroll
+    for (int h = 0; h < 6; ++h)
+#pragma unroll
+      for (int w = 0; w < 6; ++w)
+        m[h][w] = __fsub_rn(__uint_as_float(__byte_perm(raw[h][w], 0x4B000000u, sel_in)), 8388608.0f);
+#pragma unroll
+    for (int w = 0; w < 6; ++w) {          // pass along h, in place
+      const float f[6] = {m[0][w], m[1][w], m[2][w], m[3][w], m[4][w], m[5][w]};
+      float o[6];
+      bt6(f, o);
+#pragma unroll
+      for (int i = 0; i < 6; ++i) m[i][w] = o[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {          // pass along w, quantise
+      const float f[6] = {m[i][0], m[i][1], m[i][2], m[i][3], m[i][4], m[i][5]};
+      float v[6];
+      bt6(f, v);
+      // border tiles: the reference's border kernel leaves two corner results partly unfused (see
+      // the fp32 kernel above)
+      if (border) {
+        const float z2 = 0.87890625f, z3 = -2.640625f;
+        if (i == 0) v[5] = __fadd_rn(__fmul_rn(f[3], z3), __fadd_rn(__fmul_rn(f[1], z2), f[5]));
+        if (i == 5) v[0] = __fmaf_rn(f[2], z3, __fadd_rn(__fmul_rn(f[0], z2), f[4]));
+      }
+#pragma unroll
+      for (int j = 0; j < 6; ++j) {
+        // sat_u8(rne(fma(V, mrepS, tz))): adding 1.5 * 2^23 rounds to nearest even and leaves the
+        // integer in the low bits; read as UNSIGNED a negative result is huge, so one min() gives
+        // the reference's unsigned saturation (below zero -> 255, above 255 -> 255).  Exact while
+        // |fma| < 2^22; anything larger takes the plain conversion.
+        const float q = __fmaf_rn(v[j], p.mrepS, p.tz);
+        uint32_t b = min(__float_as_uint(__fadd_rn(q, 12582912.0f)) - 0x4B400000u, 255u);
+        if (!(fabsf(q) < 4194304.0f)) {
+          const float r = rintf(q);
+          b = (r < 0.0f || r > 255.0f || r != r) ? 255u : static_cast<uint32_t>(r);
+        }
+        outw[i * 6 + j] = __byte_perm(outw[i * 6 + j], b, sel_out);
+      }
+    }
+  }
+  // stage = 8 channel blocks; chunk = cb % 8; 4 bytes per thread, 128 contiguous bytes per warp
+#pragma unroll
+  for (int a = 0; a < 36; ++a) {
+    const size_t off = ((((static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4;
+    *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) + off) = live ? outw[a] : 0u;
   }
 }
 
@@ -799,7 +898,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     dim3 gi((m_tiles_run * BM + TRANS_TILES - 1) / TRANS_TILES, g.CB);
     const bool timed = pl.stage_ev[0] != nullptr && n0 == 0;
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[0], s));
-    if (w->kind == KIND_I8) wino_input_kernel<true><<<gi, TRANS_THREADS, 0, s>>>(ip);
+    if (w->kind == KIND_I8) wino_input_u8_kernel<<<gi, TRANS_THREADS, 0, s>>>(ip);
     else wino_input_kernel<false><<<gi, TRANS_THREADS, 0, s>>>(ip);
     W_TRY(cudaGetLastError());
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[1], s));
