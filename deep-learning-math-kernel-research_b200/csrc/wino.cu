@@ -329,8 +329,10 @@ struct WinoGemmParams {
   const float *shift;       // int8: [36][OCP]
   int32_t *acc_dump;        // int8, optional: [36][T][OCP]
   int *status;
+  long long *trace;         // optional per-CTA timeline (SM cycle counter), 64 slots per CTA (debug)
   int m_tiles, m_pitch, n_tiles, k_stages, BN, OCB, Tpad, T, kind;
 };
+#define WG_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid_constant__ WinoGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -345,6 +347,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   uint64_t *tempty = tfull + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // int8 only: per-epilogue-warp copies of the scale / shift slice of the current tile; they live in
+  // the raw-A ring, which only the fp32 path uses
+  float *epi_consts = reinterpret_cast<float *>(raw_ring);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int BN = p.BN;
@@ -386,6 +391,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
       const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + mt) * p.k_stages * a_gbytes;
       const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * b_stage_bytes;
+      if (lane == 0 && it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
       for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
         const int s = it % GEMM_STAGES;
         const uint32_t ph = (it / GEMM_STAGES) & 1u;
@@ -414,6 +420,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
         if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
         tc_fence_after_sync();
+        if (tcount < 8) WG_TRACE(8 + tcount);
         const uint32_t d_tmem = tmem_base + b * MAX_BN;
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const int s = it % GEMM_STAGES;
@@ -421,6 +428,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           tc_fence_after_sync();
+          if (ks == 0 && tcount < 8) WG_TRACE(16 + tcount);
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
           if (p.kind == KIND_F32) {
@@ -446,6 +454,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           umma_commit(&empty[s]);
         }
         if (ok) umma_commit(&tfull[b]);
+        if (tcount < 8) WG_TRACE(24 + tcount);
       }
     }
     __syncwarp();
@@ -501,24 +510,43 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const int t = mt * BM + row;
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
       tc_fence_after_sync();
+      if (threadIdx.x == 64 && tcount < 8) WG_TRACE(32 + tcount);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * MAX_BN;
-#pragma unroll 1
-      for (int ob = half; ob < BN / 16; ob += 2) {
-        uint32_t rr[16];
-        tmem_ld16(t_addr + ob * 16, rr);
-        tmem_ld_wait();
-        const int ocb = nt * (BN / 16) + ob;
+      // int8: this warp's slice of the per-(position, channel) constants goes to a warp-private
+      // piece of shared memory first (one 16-byte load per lane and array), so that the loop below
+      // reads them with broadcast shared-memory loads instead of waiting on global memory
+      float *w_sc = epi_consts + (warp - 2) * 2 * MAX_BN, *w_sh = w_sc + MAX_BN;
+      if (p.kind == KIND_I8) {
+        __syncwarp();
+#pragma unroll
+        for (int c = lane * 4; c < MAX_BN; c += 128) {
+          if (c < BN) {
+            const size_t gi = static_cast<size_t>(a) * OCP + nt * BN + c;
+            const bool in = nt * BN + c < OCP;
+            *reinterpret_cast<float4 *>(w_sc + c) = in ? __ldg(reinterpret_cast<const float4 *>(p.scale + gi)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(w_sh + c) = in ? __ldg(reinterpret_cast<const float4 *>(p.shift + gi)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        __syncwarp();
+      }
+      auto emit = [&](int k, const uint32_t (&rr)[16]) {      // k-th 16-column block of this warp
+        const int blk = half + 2 * k;
+        const int ocb = nt * (BN / 16) + blk;
         if (ocb < p.OCB) {
           float f[16];
           if (p.kind == KIND_F32) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(rr[i]);
           } else {
-            const float *sc = p.scale + static_cast<size_t>(a) * OCP + ocb * 16;
-            const float *sh = p.shift + static_cast<size_t>(a) * OCP + ocb * 16;
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              f[i] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[i])), __ldg(sc + i), __ldg(sh + i));
+            for (int i = 0; i < 4; ++i) {
+              const float4 c = reinterpret_cast<const float4 *>(w_sc)[blk * 4 + i];
+              const float4 h = reinterpret_cast<const float4 *>(w_sh)[blk * 4 + i];
+              f[4 * i + 0] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[4 * i + 0])), c.x, h.x);
+              f[4 * i + 1] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[4 * i + 1])), c.y, h.y);
+              f[4 * i + 2] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[4 * i + 2])), c.z, h.z);
+              f[4 * i + 3] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[4 * i + 3])), c.w, h.w);
+            }
             if (p.acc_dump && t < p.T) {
               int32_t *d = p.acc_dump + (static_cast<size_t>(a) * p.T + t) * OCP + ocb * 16;
 #pragma unroll
@@ -533,9 +561,33 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
             *reinterpret_cast<float4 *>(o + static_cast<size_t>(i) * p.Tpad * 4) =
                 make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
         }
+      };
+      // This warp owns every second 16-column block (half, half+2, ...).  The loads of tensor
+      // memory are software-pipelined: while one pair of blocks is converted and stored, the next
+      // pair is already on its way (wait::ld covers every load issued so far).
+      const int nblk = (BN / 16 - half + 1) / 2;      // blocks of this warp (may be 0)
+      const uint32_t w_addr = t_addr + half * 16;     // k-th block at +32*k columns
+      uint32_t r0[16], r1[16], r2[16], r3[16];
+      if (0 < nblk) tmem_ld16(w_addr, r0);
+      if (1 < nblk) tmem_ld16(w_addr + 32, r1);
+#pragma unroll 1
+      for (int k = 0; k < nblk; k += 4) {
+        tmem_ld_wait16(r0);
+        tmem_ld_wait16(r1);
+        if (k + 2 < nblk) tmem_ld16(w_addr + (k + 2) * 32, r2);
+        if (k + 3 < nblk) tmem_ld16(w_addr + (k + 3) * 32, r3);
+        emit(k, r0);
+        if (k + 1 < nblk) emit(k + 1, r1);
+        tmem_ld_wait16(r2);
+        tmem_ld_wait16(r3);
+        if (k + 4 < nblk) tmem_ld16(w_addr + (k + 4) * 32, r0);
+        if (k + 5 < nblk) tmem_ld16(w_addr + (k + 5) * 32, r1);
+        if (k + 2 < nblk) emit(k + 2, r2);
+        if (k + 3 < nblk) emit(k + 3, r3);
       }
       tc_fence_before_sync();
       mbar_arrive(&tempty[b]);
+      if (threadIdx.x == 64 && tcount < 8) WG_TRACE(40 + tcount);
     }
   }
 
@@ -552,6 +604,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
 constexpr int GEMM_SMEM_BYTES =
     GEMM_STAGES * (A_STAGE_BYTES + B_STAGE_MAX + A_RAW_BYTES) + (3 * GEMM_STAGES + 4) * 8 + 16 + 128;
 static_assert(GEMM_SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+static_assert(GEMM_EPI_WARPS * 2 * MAX_BN * 4 <= GEMM_STAGES * A_RAW_BYTES, "epilogue constants must fit the raw-A ring");
 
 // ------------------------------------------------------------------------------ output transform
 struct WinoOutParams {
@@ -911,6 +964,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.shift = static_cast<const float *>(w->d_shift);
     gp.acc_dump = (w->kind == KIND_I8 && acc_dump && n0 == 0 && imgs == w->N) ? static_cast<int32_t *>(acc_dump) : nullptr;
     gp.status = status;
+    gp.trace = static_cast<long long *>(pl.trace);
     gp.m_tiles = m_tiles_run;            // tiles multiplied in this chunk
     gp.m_pitch = w->g.m_tiles;           // pitch of the operand image (full chunk)
     gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
