@@ -708,7 +708,25 @@ def main():
     assert rc == 0, E.last_error()
     sampler.stop()
 
-    ms_total, e2e_ms = max_over_ranks([ms_total, e2e_ms], dist, device="cuda")
+    # optional exchange step, outside the convolution timing: every rank gathers all output slabs
+    # (what a caller would do to hold the full minibatch on one device); device-timed, max over ranks
+    gather_ms = 0.0
+    if dist is not None:
+        full = torch.empty(world * out_elems, dtype=out_dtype, device="cuda")
+        for _ in range(2):
+            dist.all_gather_into_tensor(full, os_[0])
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            dist.all_gather_into_tensor(full, os_[0])
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = g0.elapsed_time(g1) / 5
+        del full
+    ms_total, e2e_ms, gather_ms = max_over_ranks([ms_total, e2e_ms, gather_ms], dist, device="cuda")
+    if dist is not None:
+        config["output_all_gather_ms"] = round(gather_ms, 4)
 
     ms_step = ms_total / args.steps
     value = aggregate_throughput(ops, ms_step, world)

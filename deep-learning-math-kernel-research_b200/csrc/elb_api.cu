@@ -324,6 +324,10 @@ int setup_i8_direct(elb_conv &pl) {
       p.tiles_h = (p.OH + p.BH - 1) / p.BH;
       p.m_tiles = d.n * p.tiles_w * p.tiles_h;
     }
+    {
+      const char *norot = getenv("ELB_I8_NO_ROTATE_K");            // tuning experiments only
+      p.rotate_k = (norot && atoi(norot) > 0) ? 0 : 1;
+    }
     CUDA_TRY(init_i8_umma(pl.i8cfg));
   }
   pl.info.launches_per_call = 1;

@@ -46,8 +46,15 @@ __device__ __forceinline__ float requant_one(int acc, float sc, float sh) {
 __device__ __forceinline__ void requant_store16(const int (&acc)[16], const float *__restrict__ sc,
                                                 const float *__restrict__ sh, void *out, const Requant &rq) {
   float f[16];
+  // the constants of the 16 channels are 64-byte aligned: four 16-byte loads per array
 #pragma unroll
-  for (int i = 0; i < 16; ++i) f[i] = requant_one(acc[i], sc[i], sh[i]);
+  for (int i = 0; i < 4; ++i) {
+    const float4 c = reinterpret_cast<const float4 *>(sc)[i], h = reinterpret_cast<const float4 *>(sh)[i];
+    f[4 * i + 0] = requant_one(acc[4 * i + 0], c.x, h.x);
+    f[4 * i + 1] = requant_one(acc[4 * i + 1], c.y, h.y);
+    f[4 * i + 2] = requant_one(acc[4 * i + 2], c.z, h.z);
+    f[4 * i + 3] = requant_one(acc[4 * i + 3], c.w, h.w);
+  }
   if (rq.out_type == OUT_F32) {
     if (rq.relu) {
 #pragma unroll
@@ -130,6 +137,7 @@ struct I8ConvParams {
   int n_tiles, m_tiles;
   int BW, BH, tiles_w, tiles_h;      // BOX mode tile = BH x BW output pixels (BH*BW = 128)
   int merged_rows;                   // BOX mode, stride 1: 4-D tensor map over 8-byte elements
+  int rotate_k;                      // tiles start their K loop at different stages (spreads the weight reads over L2)
 };
 
 enum : int { I8_MODE_FLAT = 0, I8_MODE_BOX = 1 };

@@ -6,11 +6,11 @@
 // micro-kernels under them (src/kernel/elk_u8s8_gemm.hxx:269-406, src/kernel/elk_u8s8_conv.hxx:254-677).
 //
 // i8_umma_kernel: implicit GEMM  D[pixel][oc] = sum_k A[pixel][k] * B[oc][k]  on tcgen05 tensor
-// cores.  One CTA = 10 warps with fixed roles:
+// cores.  One CTA = 2 + I8_EPI_WARPS (8) warps with fixed roles:
 //   warp 0      producer: TMA copies global -> shared, STAGES-deep ring, mbarrier complete_tx
 //   warp 1      allocates TMEM; lane 0 issues tcgen05.mma (kind::i8, M=128, N=BN, K=32 per
 //               instruction) and commits to the ring's "empty" barriers / the accumulator barrier
-//   warps 2..9  epilogue: tcgen05.ld the s32 accumulators (one pixel per thread), fused
+//   warps 2..   epilogue: tcgen05.ld the s32 accumulators (one pixel per thread), fused
 //               scale/shift/sum/ReLU/requantise, 16-byte stores into nChw16c
 // Two TMEM accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1.  The grid
 // is persistent: min(#tiles, #SMs) CTAs walk the tile list with stride gridDim.x.
@@ -36,7 +36,14 @@ namespace elb {
 namespace {
 
 constexpr int BM = 128;
-constexpr int NUM_EPI_WARPS = 8;     // two warps per TMEM lane quarter, alternating 16-channel blocks
+#ifndef I8_EPI_WARPS
+#define I8_EPI_WARPS 8
+#endif
+// 2 warps per TMEM lane quarter, interleaved over the 16-channel blocks.  (4 per quarter measured
+// slower on the 1x1 benchmark layer, 15.7 vs 13.6 us: the epilogue is bound by the conversion unit,
+// two int<->float conversions per output, not by the number of warps.)
+constexpr int NUM_EPI_WARPS = I8_EPI_WARPS;
+constexpr int EPI_PER_QUARTER = NUM_EPI_WARPS / 4;
 constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32;
 constexpr int MAX_OC_SMEM = 2048;    // per-channel constants cached in shared memory
 
@@ -82,6 +89,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
 
   if (threadIdx.x == 0) {
     ELB_TRACE(0);
+    // the copy engine fetches a tensor map from global memory on first use (a few microseconds cold):
+    // start that now, behind the barrier and tensor-memory set-up
+    if (MODE == I8_MODE_BOX)
+      for (int i = 0; i < p.stride * p.stride; ++i) tma_prefetch_desc(&p.tmap[i]);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -108,9 +119,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (MODE == I8_MODE_BOX && lane == 0) {
-      for (int i = 0; i < p.stride * p.stride; ++i) tma_prefetch_desc(&p.tmap[i]);
-    }
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -129,7 +137,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         oh0 = (r / p.tiles_w) * p.BH;
         ow0 = (r % p.tiles_w) * p.BW;
       }
-      for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+      // Every tile walks the K stages in a rotated order (start = tile index mod k_stages): the CTAs
+      // of a wave all need the same weight panel, and walking it in lockstep would have them hit the
+      // same L2 lines at the same time.  Integer accumulation does not depend on the order.
+      const int ks0 = p.rotate_k ? tile % p.k_stages : 0;
+      for (int ki = 0; ki < p.k_stages; ++ki, ++it) {
+        const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
@@ -199,7 +212,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + b * BN;
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+        const int ks0 = p.rotate_k ? tile % p.k_stages : 0;      // same rotation as the producer
+        for (int ki = 0; ki < p.k_stages; ++ki, ++it) {
+          const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
@@ -214,7 +229,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
             if (k2 < pairs) {
               const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 2 * (BM * 16), BM * 16, 128);
               const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * (BN * 16), BN * 16, 128);
-              umma_i8(d_tmem, ad, bd, IDESC, (ks | k2) != 0 ? 1u : 0u);
+              umma_i8(d_tmem, ad, bd, IDESC, (ki | k2) != 0 ? 1u : 0u);
             }
           }
           umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
@@ -225,9 +240,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // ------------------------------------------------------------------ epilogue (warps 2..)
     const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter ..
-    const int half = (warp - 2) >> 2;              // which of the two warps of this quarter
+    const int half = (warp - 2) >> 2;              // which of the warps of this quarter
     const int row = quarter * 32 + lane;
     const int elt = p.rq.out_type == OUT_F32 ? 4 : 1;
     uint32_t tcount = 0;
@@ -275,15 +290,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
                           static_cast<uint8_t *>(p.out) + off * elt, p.rq);
         }
       };
-      // two 16-column loads in flight per wait (this warp owns every second 16-channel block)
+      // This warp owns the 16-channel blocks half, half+P, half+2P, ... (P warps per quarter).
+      // Tensor-memory loads are software-pipelined: while one pair of blocks is requantised and
+      // stored, the next pair is already on its way.
+      constexpr int P = EPI_PER_QUARTER;
+      const int nblk = (BN / 16 - half + P - 1) / P;
+      const uint32_t w_addr = t_addr + half * 16;      // k-th block of this warp at +16*P*k columns
+      uint32_t r0[16], r1[16], r2[16], r3[16];
+      if (0 < nblk) tmem_ld16(w_addr, r0);
+      if (1 < nblk) tmem_ld16(w_addr + 16 * P, r1);
 #pragma unroll 1
-      for (int ob = half; ob < BN / 16; ob += 4) {
-        uint32_t r0[16], r1[16];
-        tmem_ld16(t_addr + ob * 16, r0);
-        tmem_ld16(t_addr + (ob + 2) * 16, r1);
-        tmem_ld_wait();
-        emit(ob, r0);
-        emit(ob + 2, r1);
+      for (int k = 0; k < nblk; k += 4) {
+        tmem_ld_wait16(r0);
+        tmem_ld_wait16(r1);
+        if (k + 2 < nblk) tmem_ld16(w_addr + (k + 2) * 16 * P, r2);
+        if (k + 3 < nblk) tmem_ld16(w_addr + (k + 3) * 16 * P, r3);
+        emit(half + P * k, r0);
+        if (k + 1 < nblk) emit(half + P * (k + 1), r1);
+        tmem_ld_wait16(r2);
+        tmem_ld_wait16(r3);
+        if (k + 4 < nblk) tmem_ld16(w_addr + (k + 4) * 16 * P, r0);
+        if (k + 5 < nblk) tmem_ld16(w_addr + (k + 5) * 16 * P, r1);
+        if (k + 2 < nblk) emit(half + P * (k + 2), r2);
+        if (k + 3 < nblk) emit(half + P * (k + 3), r3);
       }
       tc_fence_before_sync();
       mbar_arrive(&tempty[b]);
