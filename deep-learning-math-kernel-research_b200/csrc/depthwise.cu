@@ -462,7 +462,8 @@ int dw_prepare(DwPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, cons
   return ELB_OK;
 }
 
-int dw_run(DwPlan &pl, void *out, const void *in, void *acc_dump, cudaStream_t s, int &launches, std::string &err) {
+int dw_run(DwPlan &pl, void *out, const void *in, void *acc_dump, int first, int count, cudaStream_t s, int &launches,
+           std::string &err) {
   DwImpl *w = pl.impl;
   launches = 0;
   if (!w) { err = "plan not set up"; return ELB_GENERAL_ERROR; }
@@ -471,9 +472,13 @@ int dw_run(DwPlan &pl, void *out, const void *in, void *acc_dump, cudaStream_t s
     return ELB_GENERAL_ERROR;
   }
   DwParams p = w->p;
-  p.in = static_cast<const uint8_t *>(in);
-  p.out = out;
-  p.acc_dump = static_cast<int32_t *>(acc_dump);
+  if (first < 0 || count <= 0 || first + count > p.N) { err = "image range outside the batch"; return ELB_GENERAL_ERROR; }
+  const size_t in_img = static_cast<size_t>(p.CB) * p.IH * p.IW * 16, out_img = static_cast<size_t>(p.CB) * p.OH * p.OW * 16;
+  p.in = static_cast<const uint8_t *>(in) + first * in_img;
+  p.out = static_cast<uint8_t *>(out) + first * out_img;
+  p.acc_dump = acc_dump ? static_cast<int32_t *>(acc_dump) + first * out_img : nullptr;
+  p.N = count;
+  p.blocks_floored = (static_cast<long long>(count) * p.CB * p.strips * p.floored_row + 63) / 64;
   const long long blocks_rest = (static_cast<long long>(p.N) * p.CB * p.strips * p.rest_row + 63) / 64;
   if ((p.blocks_floored + blocks_rest) * 64 > 0x7FFFFFFFll) { err = "depthwise: problem too large for one launch"; return ELB_UNIMPLEMENTED; }
   dim3 grid(static_cast<unsigned>(p.blocks_floored + blocks_rest));

@@ -16,8 +16,9 @@ int dw_setup(DwPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, int nu
 // One-time weight quantisation and constant folding (first execute).
 int dw_prepare(DwPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, const void *weights,
                const void *bias, std::string &err);
-// Enqueue the convolution on stream s.
-int dw_run(DwPlan &pl, void *out, const void *in, void *acc_dump, cudaStream_t s, int &launches, std::string &err);
+// Enqueue images [first, first + count) of the batch on stream s (out / in address the full tensors).
+int dw_run(DwPlan &pl, void *out, const void *in, void *acc_dump, int first, int count, cudaStream_t s, int &launches,
+           std::string &err);
 void dw_release(DwPlan &pl);
 
 }  // namespace elb

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -145,7 +146,11 @@ struct elb_conv {
   // int8 direct
   I8ConvParams i8{};
   I8UmmaConfig i8cfg{};
-  const void *tmap_for = nullptr;       // input pointer the tensor maps were encoded for
+  struct TmapEntry { const void *base; int cnt; CUtensorMap m[4]; };
+  std::vector<TmapEntry> tmaps;         // tensor maps encoded so far, keyed by (first image address, image count)
+  // host-pointer callers: copy streams and events of the chunked, overlapped execute
+  cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
+  std::vector<cudaEvent_t> ev_in, ev_done;
   // winograd
   WinoPlan wino{};
   // int8 depthwise
@@ -158,6 +163,10 @@ struct elb_conv {
     wino_release(wino);
     dw_release(dw);
     if (stream) cudaStreamDestroy(stream);
+    if (s_h2d) cudaStreamDestroy(s_h2d);
+    if (s_d2h) cudaStreamDestroy(s_d2h);
+    for (cudaEvent_t e : ev_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : ev_done) cudaEventDestroy(e);
   }
 };
 
@@ -234,7 +243,7 @@ void choose_box(int oh, int ow, int &BW, int &BH) {
   }
 }
 
-int encode_i8_tmaps(elb_conv &pl, const void *input) {
+int encode_i8_tmaps(elb_conv &pl, const void *input, int cnt, CUtensorMap *out) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
   // IH/IW are the plan's view of the input plane (a 1x1 stride-1 convolution sees it as one row)
@@ -242,32 +251,30 @@ int encode_i8_tmaps(elb_conv &pl, const void *input) {
   if (pl.i8.merged_rows) {
     // stride 1: a row of the box is BW*16 contiguous bytes; describe it as 2*BW 8-byte elements so
     // the copy engine moves whole rows (4-D map: x in 8-byte units, h, channel block, image)
-    cuuint64_t dims[4] = {(cuuint64_t)IW * 2, (cuuint64_t)IH, (cuuint64_t)CB, (cuuint64_t)pl.i8.N};
+    cuuint64_t dims[4] = {(cuuint64_t)IW * 2, (cuuint64_t)IH, (cuuint64_t)CB, (cuuint64_t)cnt};
     cuuint64_t strides[3] = {(cuuint64_t)IW * 16, (cuuint64_t)IH * IW * 16, (cuuint64_t)CB * IH * IW * 16};
     cuuint32_t box[4] = {(cuuint32_t)pl.i8.BW * 2, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8.box_c, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(&pl.i8.tmap[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(input), dims, strides, box,
+    CUresult r = enc(&out[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(input), dims, strides, box,
                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    pl.tmap_for = input;
     return ELB_OK;
   }
   for (int ph = 0; ph < s; ++ph)
     for (int pw = 0; pw < s; ++pw) {
       const cuuint64_t Hp = (IH - ph + s - 1) / s, Wp = (IW - pw + s - 1) / s;
-      cuuint64_t dims[5] = {16, Wp, Hp, (cuuint64_t)CB, (cuuint64_t)pl.i8.N};
+      cuuint64_t dims[5] = {16, Wp, Hp, (cuuint64_t)CB, (cuuint64_t)cnt};
       cuuint64_t strides[4] = {(cuuint64_t)s * 16, (cuuint64_t)s * IW * 16, (cuuint64_t)IH * IW * 16,
                                (cuuint64_t)CB * IH * IW * 16};
       cuuint32_t box[5] = {16, (cuuint32_t)pl.i8.BW, (cuuint32_t)pl.i8.BH, (cuuint32_t)pl.i8.box_c, 1};
       cuuint32_t estr[5] = {1, 1, 1, 1, 1};
       void *base = (void *)((const uint8_t *)input + ((size_t)ph * IW + pw) * 16);
-      CUresult r = enc(&pl.i8.tmap[ph * s + pw], CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base, dims, strides, box, estr,
+      CUresult r = enc(&out[ph * s + pw], CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base, dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     }
-  pl.tmap_for = input;
   return ELB_OK;
 }
 
@@ -371,22 +378,41 @@ int prepare_i8_direct(elb_conv &pl, const void *weights, const void *bias) {
   return ELB_OK;
 }
 
-int run_i8_direct(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
-  I8ConvParams &p = pl.i8;
+// Images [n0, n0 + cnt) of the batch; `out` / `in` address the FULL tensors.
+int run_i8_direct(elb_conv &pl, void *out, const void *in, int n0, int cnt, cudaStream_t s) {
   if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15)
     return fail(ELB_GENERAL_ERROR, "input/output tensors must be 16-byte aligned");
-  p.in = (const uint8_t *)in;
-  p.out = out;
-  p.acc_dump = (int32_t *)pl.d_acc_dump;
+  I8ConvParams p = pl.i8;
+  const size_t in_img = pl.info.bytes_input / pl.d.n, out_img = pl.info.bytes_output / pl.d.n;
+  p.in = (const uint8_t *)in + (size_t)n0 * in_img;
+  p.out = (uint8_t *)out + (size_t)n0 * out_img;
+  p.acc_dump = pl.d_acc_dump ? (int32_t *)pl.d_acc_dump + (size_t)n0 * p.OCB * V * pl.d.oh * pl.d.ow : nullptr;
   p.status = pl.d_status;
   p.trace = (long long *)pl.d_trace;
+  p.N = cnt;
+  p.M = cnt * p.HW;
   cudaError_t e;
   if (pl.info.kernel == ELB_KERNEL_I8_SIMT) {
     e = launch_i8_simt(p, s);
   } else {
-    if (pl.i8cfg.mode == I8_MODE_BOX && pl.tmap_for != in) {
-      int rc = encode_i8_tmaps(pl, in);
-      if (rc != ELB_OK) return rc;
+    if (pl.i8cfg.mode == I8_MODE_FLAT) {
+      p.m_tiles = (p.M + 127) / 128;
+    } else {
+      p.m_tiles = cnt * p.tiles_w * p.tiles_h;
+      const elb_conv::TmapEntry *hit = nullptr;
+      for (const auto &t : pl.tmaps)
+        if (t.base == p.in && t.cnt == cnt) { hit = &t; break; }
+      if (!hit) {
+        elb_conv::TmapEntry t{};
+        t.base = p.in;
+        t.cnt = cnt;
+        int rc = encode_i8_tmaps(pl, p.in, cnt, t.m);
+        if (rc != ELB_OK) return rc;
+        if (pl.tmaps.size() >= 64) pl.tmaps.erase(pl.tmaps.begin());
+        pl.tmaps.push_back(t);
+        hit = &pl.tmaps.back();
+      }
+      for (int i = 0; i < 4; ++i) p.tmap[i] = hit->m[i];
     }
     e = launch_i8_umma(p, pl.i8cfg, pl.num_sms, s);
   }
@@ -438,15 +464,16 @@ int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
   return rc;
 }
 
-int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
+// Enqueue images [n0, n0 + cnt) of the batch on stream s; `out` / `in` address the full tensors.
+int do_enqueue_range(elb_conv &pl, void *out, const void *in, int n0, int cnt, cudaStream_t s) {
   switch (pl.info.kernel) {
     case ELB_KERNEL_I8_GEMM_UMMA:
     case ELB_KERNEL_I8_CONV_UMMA:
-    case ELB_KERNEL_I8_SIMT: return run_i8_direct(pl, out, in, s);
+    case ELB_KERNEL_I8_SIMT: return run_i8_direct(pl, out, in, n0, cnt, s);
     case ELB_KERNEL_I8_DEPTHWISE: {
       std::string err;
       int nl = 0;
-      int rc = dw_run(pl.dw, out, in, pl.d_acc_dump, s, nl, err);
+      int rc = dw_run(pl.dw, out, in, pl.d_acc_dump, n0, cnt, s, nl, err);
       pl.launches += nl;
       if (rc != ELB_OK) return fail(rc, "%s", err.c_str());
       return rc;
@@ -456,13 +483,17 @@ int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
       std::string err;
       int nl = 0;
       pl.wino.trace = pl.d_trace;
-      int rc = wino_run(pl.wino, out, in, pl.d_acc_dump, pl.d_status, pl.num_sms, s, nl, err);
+      int rc = wino_run(pl.wino, out, in, pl.d_acc_dump, pl.d_status, pl.num_sms, n0, cnt, s, nl, err);
       pl.launches += nl;
       if (rc != ELB_OK) return fail(rc, "%s", err.c_str());
       return rc;
     }
     default: return fail(ELB_UNIMPLEMENTED, "no kernel");
   }
+}
+
+int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
+  return do_enqueue_range(pl, out, in, 0, pl.d.n, s);
 }
 
 }  // namespace
@@ -593,24 +624,66 @@ int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const vo
   int rc = do_prepare(pl, weights, bias);
   if (rc != ELB_OK) return rc;
   const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
-  const void *din = input;
-  void *dout = output;
-  if (!in_dev) {
-    if (!pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.info.bytes_input));
-    CUDA_TRY(cudaMemcpyAsync(pl.d_in_stage, input, pl.info.bytes_input, cudaMemcpyHostToDevice, pl.stream));
-    din = pl.d_in_stage;
+  if (in_dev && out_dev) {
+    rc = do_enqueue(pl, output, input, pl.stream);
+    if (rc != ELB_OK) return rc;
+    CUDA_TRY(cudaStreamSynchronize(pl.stream));
+    return check_status(pl);
   }
-  if (!out_dev) {
-    if (!pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.info.bytes_output));
-    if (pl.d.with_ip_sum)
-      CUDA_TRY(cudaMemcpyAsync(pl.d_out_stage, output, pl.info.bytes_output, cudaMemcpyHostToDevice, pl.stream));
-    dout = pl.d_out_stage;
+  // Host tensors (what a caller of the reference holds): the batch is cut into chunks of whole
+  // images, and the host->device copy of chunk k+1, the kernels of chunk k and the device->host
+  // copy of chunk k-1 run at the same time on three streams (the two copy directions use different
+  // copy engines), so a call costs about the longer of the two transfers instead of their sum.
+  const int N = pl.d.n;
+  const size_t in_img = pl.info.bytes_input / N, out_img = pl.info.bytes_output / N;
+  if (!in_dev && !pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.info.bytes_input));
+  if (!out_dev && !pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.info.bytes_output));
+  if (!pl.s_h2d) {
+    CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_h2d, cudaStreamNonBlocking));
+    CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_d2h, cudaStreamNonBlocking));
   }
-  rc = do_enqueue(pl, dout, din, pl.stream);
-  if (rc != ELB_OK) return rc;
-  if (!out_dev)
-    CUDA_TRY(cudaMemcpyAsync(output, pl.d_out_stage, pl.info.bytes_output, cudaMemcpyDeviceToHost, pl.stream));
+  int chunks = 1;
+  {
+    const size_t moved = (in_dev ? 0 : pl.info.bytes_input) + (out_dev ? 0 : pl.info.bytes_output);
+    const size_t target = size_t(4) << 20;                       // at least ~4 MB of transfers per chunk
+    chunks = (int)std::min<size_t>(8, std::max<size_t>(1, moved / target));
+    if (chunks > N) chunks = N;
+    if (const char *e = getenv("ELB_HOST_CHUNKS")) {             // tuning experiments only
+      const int v = atoi(e);
+      if (v >= 1) chunks = v < N ? v : N;
+    }
+  }
+  while ((int)pl.ev_in.size() < chunks) {
+    cudaEvent_t a = nullptr, b = nullptr;
+    CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+    pl.ev_in.push_back(a);
+    pl.ev_done.push_back(b);
+  }
+  const void *din = in_dev ? input : pl.d_in_stage;
+  void *dout = out_dev ? output : pl.d_out_stage;
+  for (int k = 0; k < chunks; ++k) {
+    const int n0 = (int)((long long)N * k / chunks), n1 = (int)((long long)N * (k + 1) / chunks);
+    const int cnt = n1 - n0;
+    if (!in_dev)
+      CUDA_TRY(cudaMemcpyAsync((uint8_t *)pl.d_in_stage + n0 * in_img, (const uint8_t *)input + n0 * in_img, cnt * in_img,
+                               cudaMemcpyHostToDevice, pl.s_h2d));
+    if (!out_dev && pl.d.with_ip_sum)
+      CUDA_TRY(cudaMemcpyAsync((uint8_t *)pl.d_out_stage + n0 * out_img, (const uint8_t *)output + n0 * out_img,
+                               cnt * out_img, cudaMemcpyHostToDevice, pl.s_h2d));
+    CUDA_TRY(cudaEventRecord(pl.ev_in[k], pl.s_h2d));
+    CUDA_TRY(cudaStreamWaitEvent(pl.stream, pl.ev_in[k], 0));
+    rc = do_enqueue_range(pl, dout, din, n0, cnt, pl.stream);
+    if (rc != ELB_OK) { cudaDeviceSynchronize(); return rc; }
+    if (!out_dev) {
+      CUDA_TRY(cudaEventRecord(pl.ev_done[k], pl.stream));
+      CUDA_TRY(cudaStreamWaitEvent(pl.s_d2h, pl.ev_done[k], 0));
+      CUDA_TRY(cudaMemcpyAsync((uint8_t *)output + n0 * out_img, (uint8_t *)pl.d_out_stage + n0 * out_img, cnt * out_img,
+                               cudaMemcpyDeviceToHost, pl.s_d2h));
+    }
+  }
   CUDA_TRY(cudaStreamSynchronize(pl.stream));
+  if (!out_dev) CUDA_TRY(cudaStreamSynchronize(pl.s_d2h));
   return check_status(pl);
 }
 

@@ -924,7 +924,7 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
 }
 
 int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *status, int num_sms,
-             cudaStream_t s, int &launches, std::string &err) {
+             int first, int count, cudaStream_t s, int &launches, std::string &err) {
   WinoImpl *w = pl.impl;
   launches = 0;
   if (!w) { err = "plan not set up"; return ELB_GENERAL_ERROR; }
@@ -932,9 +932,10 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     err = "input/output tensors must be 16-byte aligned";
     return ELB_GENERAL_ERROR;
   }
-  for (int n0 = 0; n0 < w->N; n0 += w->imgs_per_chunk) {
+  if (first < 0 || count <= 0 || first + count > w->N) { err = "image range outside the batch"; return ELB_GENERAL_ERROR; }
+  for (int n0 = first; n0 < first + count; n0 += w->imgs_per_chunk) {
     WinoGeom g = w->g;
-    const int imgs = std::min(w->imgs_per_chunk, w->N - n0);
+    const int imgs = std::min(w->imgs_per_chunk, first + count - n0);
     g.N = imgs;
     g.T = imgs * g.ht * g.wt;
     g.m_tiles = (g.T + BM - 1) / BM;
@@ -949,7 +950,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     ip.g.Tpad = m_tiles_run * BM;
     ip.mrepS = w->mrepS; ip.tz = w->tz;
     dim3 gi((m_tiles_run * BM + TRANS_TILES - 1) / TRANS_TILES, g.CB);
-    const bool timed = pl.stage_ev[0] != nullptr && n0 == 0;
+    const bool timed = pl.stage_ev[0] != nullptr && n0 == first;
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[0], s));
     if (w->kind == KIND_I8) wino_input_u8_kernel<<<gi, TRANS_THREADS, 0, s>>>(ip);
     else wino_input_kernel<false><<<gi, TRANS_THREADS, 0, s>>>(ip);

@@ -18,9 +18,10 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
 // One-time weight transform / quantisation / packing into device memory.
 int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, const void *weights,
                  const void *bias, std::string &err);
-// Enqueue the kernels of one convolution on stream s; launches = number of kernels launched.
+// Enqueue the kernels for images [first, first + count) of the batch on stream s (out / in address
+// the full tensors); launches = number of kernels launched.
 int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *status, int num_sms,
-             cudaStream_t s, int &launches, std::string &err);
+             int first, int count, cudaStream_t s, int &launches, std::string &err);
 void wino_release(WinoPlan &pl);
 
 }  // namespace elb
