@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the convolution hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|c5i8|dw] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c3s|c4|c5|c5i8|dw] [--impl reference]
 
 One "step" is one convolution call (elx_conv) over one batch of synthetic input of the named
 workload.  Workloads are the benchmark configurations: c1 FP32 Winograd F(4x4,3x3) VGG conv3_2,
@@ -50,6 +50,9 @@ WORKLOADS = {
                desc="INT8 u8s8 1x1 ResNet-50 res4 reduce N=64 C=1024 K=256 14x14 bias+ReLU u8 out nChw16c"),
     "c3": dict(metric="effective_conv_tops_int8", unit="TOP/s", dtype="u8",
                desc="INT8 u8s8 3x3 stride 2 pad 1 N=64 C=128 K=256 56x56->28x28 bias+ReLU u8 out nChw16c"),
+    "c3s": dict(metric="effective_conv_tops_int8", unit="TOP/s", dtype="u8",
+                desc="INT8 u8s8 3x3 stride 2 pad 1 N=64 C=128 K=256 56x56->28x28 bias+ReLU+sum (u8 residual in the output "
+                     "tensor, sum scale 1.0) u8 out nChw16c; the reference's KxK path ignores the sum flag"),
     "c4": dict(metric="effective_conv_tops_int8_winograd", unit="TOP/s", dtype="u8",
                desc="INT8 Winograd F(4x4,3x3) N=128 C=K=512 28x28 s1 p1 f32 out nChw16c"),
     "dw": dict(metric="effective_conv_tops_int8_depthwise", unit="TOP/s", dtype="u8",
@@ -611,9 +614,16 @@ def main():
     out_bytes = out_elems * np.dtype(case.out_dtype).itemsize
     nsets = max(2, -(-int(1.5 * L2_BYTES) // (in_bytes + out_bytes)))
     nsets = min(nsets, 64)
+    if os.environ.get("ELB_BENCH_SETS"):      # experiments only: e.g. 1 = operands stay in L2 (not a valid bench number)
+        nsets = int(os.environ["ELB_BENCH_SETS"])
+        config["cache"] = f"EXPERIMENT: {nsets} buffer set(s)"
     x0 = torch.from_numpy(t["input"]).cuda()
     xs = [x0] + [x0.clone() for _ in range(nsets - 1)]
-    os_ = [torch.zeros(out_elems, dtype=out_dtype, device="cuda") for _ in range(nsets)]
+    if case.sum:      # in-place sum: the output tensors start as the residual
+        r0 = torch.from_numpy(t["residual"]).cuda().reshape(-1)
+        os_ = [r0.clone() for _ in range(nsets)]
+    else:
+        os_ = [torch.zeros(out_elems, dtype=out_dtype, device="cuda") for _ in range(nsets)]
     config["buffer_sets"] = nsets
 
     stream = torch.cuda.Stream()
@@ -693,7 +703,7 @@ def main():
 
     # ---- end to end through the drop-in call with pinned host buffers
     hx = torch.from_numpy(t["input"]).pin_memory()
-    ho = torch.zeros(out_elems, dtype=out_dtype).pin_memory()
+    ho = (torch.from_numpy(t["residual"]).reshape(-1).clone() if case.sum else torch.zeros(out_elems, dtype=out_dtype)).pin_memory()
     e2e_steps = max(3, min(args.steps, 200))
     for _ in range(3):
         assert E.elx_conv(d, ho, hx, None, None) == 0, E.last_error()
@@ -741,7 +751,7 @@ def main():
             "vs_baseline": (value / PUBLISHED[args.workload]) if args.workload in PUBLISHED else None,
             "dtype": wl["dtype"], "data": "synthetic", "config": config,
             "clocks": sampler.summary(),
-            "e2e": {"value": e2e_value, "unit": wl["unit"], "h2d_bytes_per_step": in_bytes,
+            "e2e": {"value": e2e_value, "unit": wl["unit"], "h2d_bytes_per_step": in_bytes + (out_bytes if case.sum else 0),
                     "d2h_bytes_per_step": out_bytes, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(launches), "roofline": roofline, "cal_ops_per_step": ops}
 

@@ -248,6 +248,12 @@ int encode_i8_tmaps(elb_conv &pl, const void *input, int cnt, CUtensorMap *out) 
   if (!enc) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
   // IH/IW are the plan's view of the input plane (a 1x1 stride-1 convolution sees it as one row)
   const int s = pl.i8.stride, CB = pl.i8.CB, IH = pl.i8.IH, IW = pl.i8.IW;
+  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+  if (const char *e = getenv("ELB_I8_L2PROMO")) {                  // tuning experiments only
+    const int v = atoi(e);
+    promo = v == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+          : v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+  }
   if (pl.i8.merged_rows) {
     // stride 1: a row of the box is BW*16 contiguous bytes; describe it as 2*BW 8-byte elements so
     // the copy engine moves whole rows (4-D map: x in 8-byte units, h, channel block, image)
@@ -257,7 +263,7 @@ int encode_i8_tmaps(elb_conv &pl, const void *input, int cnt, CUtensorMap *out) 
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(&out[0], CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(input), dims, strides, box,
                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     return ELB_OK;
   }
@@ -271,7 +277,7 @@ int encode_i8_tmaps(elb_conv &pl, const void *input, int cnt, CUtensorMap *out) 
       cuuint32_t estr[5] = {1, 1, 1, 1, 1};
       void *base = (void *)((const uint8_t *)input + ((size_t)ph * IW + pw) * 16);
       CUresult r = enc(&out[ph * s + pw], CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base, dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, promo,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     }
@@ -321,6 +327,10 @@ int setup_i8_direct(elb_conv &pl) {
     // channel blocks one tiled copy fetches: the largest power of two that divides CB, at most KC
     p.box_c = 1;
     while (p.box_c * 2 <= pl.i8cfg.KC && p.CB % (p.box_c * 2) == 0) p.box_c *= 2;
+    if (const char *e = getenv("ELB_I8_BOXC")) {                   // tuning experiments only
+      const int v = atoi(e);
+      if (v >= 1 && v <= p.box_c && p.box_c % v == 0) p.box_c = v;
+    }
     if (mode == I8_MODE_FLAT) {
       p.m_tiles = (p.M + 127) / 128;
     } else {
@@ -335,6 +345,13 @@ int setup_i8_direct(elb_conv &pl) {
       const char *norot = getenv("ELB_I8_NO_ROTATE_K");            // tuning experiments only
       p.rotate_k = (norot && atoi(norot) > 0) ? 0 : 1;
     }
+    // Pairs of SMs (int8_conv2.cu) wherever there are enough pixel tiles to pair up: each CTA then
+    // fetches half of the weight panel.  ELB_I8_NO_CTA2=1 keeps the single-CTA kernel.
+    {
+      const char *no2 = getenv("ELB_I8_NO_CTA2");
+      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && !(no2 && atoi(no2) > 0)) ? 1 : 0;
+    }
+    if (pl.i8cfg.cta2) CUDA_TRY(init_i8_umma2(pl.i8cfg, pl.num_sms));
     CUDA_TRY(init_i8_umma(pl.i8cfg));
   }
   pl.info.launches_per_call = 1;
@@ -364,7 +381,8 @@ int prepare_i8_direct(elb_conv &pl, const void *weights, const void *bias) {
     pl.info.workspace_bytes += wq.q.size();
   } else {
     int n_tiles, CBG, k_stages;
-    std::vector<int8_t> pk = host::pack_b_i8(wq, pl.i8cfg.BN, pl.i8cfg.KC, n_tiles, CBG, k_stages);
+    std::vector<int8_t> pk = host::pack_b_i8(wq, pl.i8cfg.BN, pl.i8cfg.KC, n_tiles, CBG, k_stages,
+                                             pl.i8cfg.cta2 ? 2 : 1);
     if (n_tiles != pl.i8.n_tiles || CBG != pl.i8.CBG || k_stages != pl.i8.k_stages)
       return fail(ELB_GENERAL_ERROR, "internal: weight packing geometry mismatch");
     CUDA_TRY(cudaMalloc(&pl.d_wpack, pk.size()));
@@ -414,7 +432,8 @@ int run_i8_direct(elb_conv &pl, void *out, const void *in, int n0, int cnt, cuda
       }
       for (int i = 0; i < 4; ++i) p.tmap[i] = hit->m[i];
     }
-    e = launch_i8_umma(p, pl.i8cfg, pl.num_sms, s);
+    // (a sub-range of fewer than two pixel tiles still runs on pairs: the weights are packed for them)
+    e = pl.i8cfg.cta2 ? launch_i8_umma2(p, pl.i8cfg, pl.num_sms, s) : launch_i8_umma(p, pl.i8cfg, pl.num_sms, s);
   }
   pl.launches += 1;
   if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "kernel launch failed: %s", cudaGetErrorString(e));

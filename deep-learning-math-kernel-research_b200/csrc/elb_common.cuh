@@ -146,11 +146,15 @@ enum : int { I8_MODE_FLAT = 0, I8_MODE_BOX = 1 };
 struct I8UmmaConfig {
   int BN, KC, STAGES, mode;
   size_t smem_bytes;
+  int cta2;            // 1: the two-CTA kernel (int8_conv2.cu): weight rows split over a pair of SMs
+  int max_clusters;    // two-CTA kernel: clusters the device holds at once (persistent grid size)
 };
 I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode);
 cudaError_t init_i8_umma(const I8UmmaConfig &cfg);   // per-device kernel attributes, call once per plan
 cudaError_t launch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s);
 cudaError_t launch_i8_simt(const I8ConvParams &p, cudaStream_t s);
+cudaError_t init_i8_umma2(I8UmmaConfig &cfg, int num_sms);    // two-CTA kernel: attributes + cluster occupancy
+cudaError_t launch_i8_umma2(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s);
 
 // Bounded-wait self test: one CTA waits on an mbarrier nobody arrives at, gives up after
 // `limit_ns`, writes ST_WAIT_TIMEOUT_TEST to *status and returns normally.

@@ -102,8 +102,10 @@ inline void fold_constants_i8(const I8Weights &wq, const float *bias, bool with_
 // Operand image of B for the tcgen05 kernels: [n_tile][k_stage][KC chunks][BN rows][16 bytes].
 // K runs over chunks q = tap*CB + cb of 16 input channels (tap-major); stage ks holds chunks
 // ks*KC .. ks*KC+KC-1, zero where q is past the end of K or the row past the last output channel.
+// halves = 2 (two-CTA kernel): the BN rows of a stage are stored as two images of BN/2 rows,
+// [n_tile][k_stage][half][KC][BN/2][16], one per CTA of the pair.
 inline std::vector<int8_t> pack_b_i8(const I8Weights &wq, int BN, int KC, int &n_tiles, int &CBG,
-                                     int &k_stages) {
+                                     int &k_stages, int halves = 1) {
   const int CB = wq.ICP / 16;
   const int Q = wq.taps * CB;
   n_tiles = (wq.OCP + BN - 1) / BN;
@@ -119,7 +121,8 @@ inline std::vector<int8_t> pack_b_i8(const I8Weights &wq, int BN, int KC, int &n
         for (int r = 0; r < BN; ++r) {
           const int o = nt * BN + r;
           if (o >= wq.OCP) continue;
-          int8_t *dst = &out[((((size_t)nt * k_stages + ks) * KC + j) * BN + r) * 16];
+          const int BH = BN / halves, h = r / BH, rr = r % BH;
+          int8_t *dst = &out[(((((size_t)nt * k_stages + ks) * halves + h) * KC + j) * BH + rr) * 16];
           std::memcpy(dst, &wq.q[((size_t)o * wq.taps + tap) * wq.ICP + cb * 16], 16);
         }
       }

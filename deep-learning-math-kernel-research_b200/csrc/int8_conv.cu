@@ -44,7 +44,8 @@ constexpr int BM = 128;
 // two int<->float conversions per output, not by the number of warps.)
 constexpr int NUM_EPI_WARPS = I8_EPI_WARPS;
 constexpr int EPI_PER_QUARTER = NUM_EPI_WARPS / 4;
-constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32;
+constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32 + 32;    // + a second producer warp (the last warp)
+constexpr int PRODUCER2_WARP = 2 + NUM_EPI_WARPS;
 constexpr int MAX_OC_SMEM = 2048;    // per-channel constants cached in shared memory
 
 __device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
@@ -117,9 +118,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   if (threadIdx.x == 0) ELB_TRACE(1);
   int fail_code = 0;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ producer
-    uint32_t it = 0;
+  if (warp == 0 || (warp == PRODUCER2_WARP && MODE == I8_MODE_BOX)) {
+    // ------------------------------------------------------------------ producer(s)
+    // BOX mode runs two producer warps that take turns on the passes (two stages each) of the K
+    // loop, so that four stages are being issued at any time; see the comment in the loop.
+    const uint32_t pw = warp == 0 ? 0u : 1u;
+    uint32_t it = 0, gpass = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
@@ -141,15 +145,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
       // of a wave all need the same weight panel, and walking it in lockstep would have them hit the
       // same L2 lines at the same time.  Integer accumulation does not depend on the order.
       const int ks0 = p.rotate_k ? tile % p.k_stages : 0;
-      for (int ki = 0; ki < p.k_stages; ++ki, ++it) {
-        const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
-        if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
-        uint8_t *a_dst = smem + s * L::STAGE_BYTES;
-        uint8_t *b_dst = a_dst + L::A_BYTES;
-        const int8_t *b_src = p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES;
-        if (MODE == I8_MODE_FLAT) {
+      if (MODE == I8_MODE_FLAT) {
+        for (int ki = 0; ki < p.k_stages; ++ki, ++it) {
+          const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+          uint8_t *a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t *b_dst = a_dst + L::A_BYTES;
+          const int8_t *b_src = p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES;
           const int cb0 = ks * KC;
           const int nchunks = min(KC, p.CB - cb0);
           if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(nchunks * rows * 16 + L::B_BYTES));
@@ -168,37 +172,67 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           } else if (lane == KC) {
             tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
           }
-        } else {
-          // K chunks of this stage: q0 .. q0+KC-1 of the flattened (tap, channel block) index; one
-          // tiled copy brings box_c consecutive channel blocks of ONE tap (box_c divides CB, so a
-          // copy never straddles two taps).  Every copy and the weight panel are issued by their
-          // own lane: a copy occupies its issuing thread for a few hundred cycles, and measured
-          // ingest is ~30% higher when the copies of a stage are in flight together.  Chunks past
-          // the end of K are not fetched: their weights are zero, whatever the stage slot holds.
-          const int q0 = ks * KC;
-          const int valid = min(KC, p.Q - q0);
-          if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(valid * (BM * 16) + L::B_BYTES));
-          __syncwarp();
-          if (lane == KC) tma_bulk_g2s(b_dst, b_src, L::B_BYTES, &full[s]);
-          const int q = q0 + lane * p.box_c;
-          if (lane * p.box_c < valid) {
-            const int tap = q / p.CB, cb0 = q - tap * p.CB;
-            // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
-            const int kh = tap / p.KW, kw = tap - kh * p.KW;
-            const int eh = kh - p.pad_t, ew = kw - p.pad_l;
-            const int dh = (eh >= 0) ? eh / p.stride : -((-eh + p.stride - 1) / p.stride);
-            const int dw = (ew >= 0) ? ew / p.stride : -((-ew + p.stride - 1) / p.stride);
-            const int par_h = eh - dh * p.stride, par_w = ew - dw * p.stride;
-            const CUtensorMap *tm = &p.tmap[par_h * p.stride + par_w];
-            uint8_t *dst = a_dst + lane * p.box_c * (BM * 16);
-            // stride 1: rows of the box are contiguous in memory, so the map describes them as runs of
-            // 8-byte elements (2 per pixel) and the TMA unit moves whole rows instead of 16-byte items
-            if (p.merged_rows) tma_tile_4d(dst, tm, (ow0 + dw) * 2, oh0 + dh, cb0, n0, &full[s]);
-            else tma_tile_5d(dst, tm, 0, ow0 + dw, oh0 + dh, cb0, n0, &full[s]);
+          if (lane == 0 && it < 16) ELB_TRACE(2 + it);
+        }
+      } else {
+        // BOX mode.  Issuing a copy occupies the issuing warp for about a thousand cycles whatever
+        // its size, but the lanes of ONE instruction issue their copies together.  So the warp works
+        // on TWO pipeline stages per pass: lanes 0..15 serve one stage, lanes 16..31 the next; in
+        // each group lanes 0..7 fetch the pixels (one tiled copy per box_c channel blocks of one
+        // tap: box_c divides CB, so a copy never straddles two taps) and lane 8 the weight panel.
+        // Chunks past the end of K are not fetched: their weights are zero, whatever the slot holds.
+        const int grp = lane >> 4, gl = lane & 15;
+        for (int ki0 = 0; ki0 < p.k_stages; ki0 += 2, it += 2, ++gpass) {
+          if ((gpass & 1u) != pw) continue;          // the other producer warp's pass
+          const int ki = ki0 + grp;
+          const bool active = ki < p.k_stages;
+          const uint32_t my_it = it + grp;
+          const int s = my_it % STAGES;
+          const uint32_t ph = (my_it / STAGES) & 1u;
+          int w_ok = 1;
+          if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
+          if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+          if (active) {
+            while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
+            }      // every issuing lane observes the completed phase itself
+            const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
+            uint8_t *a_dst = smem + s * L::STAGE_BYTES;
+            uint8_t *b_dst = a_dst + L::A_BYTES;
+            const int8_t *b_src = p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES;
+            const int q0 = ks * KC;
+            const int valid = min(KC, p.Q - q0);
+            if (gl == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(valid * (BM * 16) + L::B_BYTES));
           }
           __syncwarp();
+          if (active) {
+            const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
+            uint8_t *a_dst = smem + s * L::STAGE_BYTES;
+            const int q0 = ks * KC;
+            const int valid = min(KC, p.Q - q0);
+            if (gl == KC) {
+              tma_bulk_g2s(a_dst + L::A_BYTES, p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES,
+                           L::B_BYTES, &full[s]);
+            } else if (gl < KC && gl * p.box_c < valid) {
+              const int q = q0 + gl * p.box_c;
+              const int tap = q / p.CB, cb0 = q - tap * p.CB;
+              // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
+              const int kh = tap / p.KW, kw = tap - kh * p.KW;
+              const int eh = kh - p.pad_t, ew = kw - p.pad_l;
+              const int dh = (eh >= 0) ? eh / p.stride : -((-eh + p.stride - 1) / p.stride);
+              const int dw = (ew >= 0) ? ew / p.stride : -((-ew + p.stride - 1) / p.stride);
+              const int par_h = eh - dh * p.stride, par_w = ew - dw * p.stride;
+              const CUtensorMap *tm = &p.tmap[par_h * p.stride + par_w];
+              uint8_t *dst = a_dst + gl * p.box_c * (BM * 16);
+              // stride 1: rows of the box are contiguous in memory, so the map describes them as runs of
+              // 8-byte elements (2 per pixel) and the TMA unit moves whole rows instead of 16-byte items
+              if (p.merged_rows) tma_tile_4d(dst, tm, (ow0 + dw) * 2, oh0 + dh, cb0, n0, &full[s]);
+              else tma_tile_5d(dst, tm, 0, ow0 + dw, oh0 + dh, cb0, n0, &full[s]);
+            }
+          }
+          __syncwarp();
+          if (gl == 0 && active && my_it < 16) ELB_TRACE(2 + my_it);
         }
-        if (lane == 0 && it < 16) ELB_TRACE(2 + it);
+        if (p.k_stages & 1) --it;      // the last pass of an odd K loop served one stage only
       }
     }
   } else if (warp == 1) {
@@ -239,7 +273,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < PRODUCER2_WARP) {
     // ------------------------------------------------------------------ epilogue (warps 2..)
     const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter ..
     const int half = (warp - 2) >> 2;              // which of the warps of this quarter
@@ -419,7 +453,7 @@ cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool 
 // Tile configuration.  BN (output channels per tile) in {64, 128, 256}; 8 K-chunks (128 bytes of K)
 // per stage; as many stages as fit 227 KB.  ELB_I8_BN overrides the choice (tuning experiments).
 I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
-  I8UmmaConfig c;
+  I8UmmaConfig c{};
   c.mode = mode;
   const int ocp = ocb * 16;
   // Per-SM copy ingest (about 50 B/clk) is what bounds these kernels, and the bytes a tile pulls

@@ -124,6 +124,9 @@ class ConvCase:
 
 # The benchmark configurations (shapes, distributions and knobs as the baseline document states).
 def baseline_case(cid: str, n: int | None = None) -> ConvCase:
+    """c3s is configuration 3 exactly as named (bias + ReLU + in-place sum of a u8 residual); c3 is
+    the same layer without the sum, the variant the reference can pin bit for bit (its KxK int8
+    path ignores with_ip_sum, src/elx_int8_conv_direct.cpp:121)."""
     if cid == "c1":
         return ConvCase("c1_fp32_wino_vgg_conv3_2", n or 64, 256, 256, 56, 56, types="fp32", algo="wino",
                         tile=6, relu=True, bias=True,
@@ -135,6 +138,10 @@ def baseline_case(cid: str, n: int | None = None) -> ConvCase:
     if cid == "c3":
         return ConvCase("c3_int8_3x3_s2", n or 64, 128, 256, 56, 56, stride=2, types="u8f32u8f32",
                         algo="direct", relu=True, bias=True,
+                        knobs=dict(xopt=0xc160, blk_i=8, blk_o=4, flt_o=2, flt_t=14))
+    if cid == "c3s":
+        return ConvCase("c3s_int8_3x3_s2_sum", n or 64, 128, 256, 56, 56, stride=2, types="u8f32u8f32",
+                        algo="direct", relu=True, bias=True, sum=True, sscale=1.0, sz=0.0,
                         knobs=dict(xopt=0xc160, blk_i=8, blk_o=4, flt_o=2, flt_t=14))
     if cid == "c4":
         return ConvCase("c4_int8_wino", n or 128, 512, 512, 28, 28, types="u8f32f32f32", algo="wino",

@@ -46,6 +46,11 @@ BOX_CASES = [
     _case("box_5x5", 1, 16, 32, 12, 12, kh=5, kw=5, pad=2, algo="direct"),
     _case("box_3x3_s8", 1, 32, 32, 8, 8, algo="direct", types="u8f32s8f32", relu=False, oscale=8.0),
     _case("box_3x3_224", 1, 16, 16, 224, 224, algo="direct"),                          # exact 32x4 tiling
+    # in-place sum on the KxK path: the reference ignores the flag there, so this pins the library's
+    # documented semantics (those of the 1x1 path) against the restatement only
+    _case("box_c3s_small", 2, 128, 256, 56, 56, stride=2, algo="direct", sum=True, sscale=1.0),
+    _case("box_3x3_sum_s8", 1, 32, 32, 10, 10, algo="direct", types="u8f32s8f32", relu=False, sum=True, sscale=0.25,
+          oscale=8.0),
 ]
 
 
