@@ -345,11 +345,13 @@ int setup_i8_direct(elb_conv &pl) {
       const char *norot = getenv("ELB_I8_NO_ROTATE_K");            // tuning experiments only
       p.rotate_k = (norot && atoi(norot) > 0) ? 0 : 1;
     }
-    // Pairs of SMs (int8_conv2.cu) wherever there are enough pixel tiles to pair up: each CTA then
-    // fetches half of the weight panel.  ELB_I8_NO_CTA2=1 keeps the single-CTA kernel.
+    // Pairs of SMs (int8_conv2.cu: each CTA fetches half of the weight panel) are opt-in with
+    // ELB_I8_CTA2=1: measured on B200 they are slower than the single-CTA kernel (1x1 benchmark layer
+    // 16.3 vs 13.7 us, 3x3 stride 2 42.9 vs 37.6 us): the kernel is bound by the rate at which copies
+    // can be ISSUED, which pairing does not change, and it pays a cluster start-up.
     {
-      const char *no2 = getenv("ELB_I8_NO_CTA2");
-      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && !(no2 && atoi(no2) > 0)) ? 1 : 0;
+      const char *on2 = getenv("ELB_I8_CTA2");
+      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && on2 && atoi(on2) > 0) ? 1 : 0;
     }
     if (pl.i8cfg.cta2) CUDA_TRY(init_i8_umma2(pl.i8cfg, pl.num_sms));
     CUDA_TRY(init_i8_umma(pl.i8cfg));

@@ -40,10 +40,15 @@ namespace elb {
 namespace {
 
 constexpr int BM = 128;
-constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_STAGES_1 = 4;             // pipeline stages: one CTA per tile (16 KB A + 32 KB B each)
+constexpr int GEMM_STAGES_2 = 6;             // pairs of CTAs (16 KB A + 16 KB of B each)
+constexpr int EPI_CONST_BYTES = 16384;       // int8: per-epilogue-warp copies of the tile's scale / shift slice
 constexpr int A_STAGE_BYTES = 16384;          // in shared memory. fp32: hi + lo planes x 4 chunks x 2 KB; int8: 8 chunks x 2 KB
 constexpr int A_RAW_BYTES = 8192;             // fp32 only: one stage of V as it lies in global memory (4 chunks x 2 KB)
 constexpr int GEMM_CONV_WARPS = 4;            // fp32 only: warps that split a raw stage into its tf32 hi / lo planes
+#ifndef GEMM_CONV_GROUPS
+#define GEMM_CONV_GROUPS 1                    // groups of such warps taking turns on the stages (2 measured slower: 0.43 vs 0.42 ms on VGG conv3_2, and the extra 128 threads push the epilogue into register spills)
+#endif
 constexpr int MAX_BN = 256;
 constexpr int B_STAGE_MAX = 128 * MAX_BN;     // fp32: 2 x 4 x BN x 16; int8: 8 x BN x 16  (= 128*BN)
 constexpr int GEMM_EPI_WARPS = 8;
@@ -54,7 +59,8 @@ constexpr int GEMM_EPI_WARPS = 8;
 #define TRANS_THREADS 64
 #endif
 constexpr int TRANS_TILES = TRANS_THREADS / 4;      // tiles per block (4 threads = the 16 channels of a block)
-constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32 + GEMM_CONV_WARPS * 32;
+constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32 + GEMM_CONV_GROUPS * GEMM_CONV_WARPS * 32 + 32;    // + the second producer warp (last)
+constexpr int GEMM_PRODUCER2_WARP = 2 + GEMM_EPI_WARPS + GEMM_CONV_GROUPS * GEMM_CONV_WARPS;
 constexpr size_t WORKSPACE_BUDGET = size_t(6) << 30;   // transform-domain buffers per chunk
 
 enum : int { KIND_F32 = 0, KIND_I8 = 1 };
@@ -332,30 +338,44 @@ struct WinoGemmParams {
   long long *trace;         // optional per-CTA timeline (SM cycle counter), 64 slots per CTA (debug)
   int m_tiles, m_pitch, n_tiles, k_stages, BN, OCB, Tpad, T, kind;
 };
+// CTA2 = true: the kernel runs as clusters of two CTAs.  A pair multiplies TWO 128-tile row blocks
+// (one per CTA) by the BN transformed weights with one tcgen05.mma.cta_group::2 per K step; each
+// CTA stages only ITS half of the weight rows, which halves both the bytes it pulls from L2 and the
+// shared-memory reads of the B operand per MMA (the fp32 path is bound by shared-memory bandwidth:
+// three tf32 MMAs per K step, each reading A and B).  Warp 1 of the peer CTA forwards "my stage is
+// ready" to the leader; commits are multicast to both CTAs.
 #define WG_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
+template <bool CTA2>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid_constant__ WinoGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_MAX;
-  // ring of operand stages, then (fp32 only) the ring of raw fp32 A stages the copies land in
-  uint8_t *raw_ring = smem + GEMM_STAGES * STAGE_BYTES;
-  uint64_t *full = reinterpret_cast<uint64_t *>(raw_ring + GEMM_STAGES * A_RAW_BYTES);
+  constexpr int GEMM_STAGES = CTA2 ? GEMM_STAGES_2 : GEMM_STAGES_1;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + (CTA2 ? B_STAGE_MAX / 2 : B_STAGE_MAX);
+  // ring of operand stages (fp32: the copy of V lands in the first half of the A region and is split
+  // IN PLACE into its hi plane there and its lo plane behind it), then the epilogue constants
+  uint8_t *consts_area = smem + GEMM_STAGES * STAGE_BYTES;
+  uint64_t *full = reinterpret_cast<uint64_t *>(consts_area + EPI_CONST_BYTES);
   uint64_t *empty = full + GEMM_STAGES;
   uint64_t *cfull = empty + GEMM_STAGES;       // fp32: hi / lo planes of stage s are written
-  uint64_t *tfull = cfull + GEMM_STAGES;
+  uint64_t *pfull = cfull + GEMM_STAGES;       // pairs, leader only: the peer's stage s is ready
+  uint64_t *tfull = pfull + GEMM_STAGES;
   uint64_t *tempty = tfull + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  // int8 only: per-epilogue-warp copies of the scale / shift slice of the current tile; they live in
-  // the raw-A ring, which only the fp32 path uses
-  float *epi_consts = reinterpret_cast<float *>(raw_ring);
+  // int8 only: per-epilogue-warp copies of the scale / shift slice of the current tile
+  float *epi_consts = reinterpret_cast<float *>(consts_area);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int BN = p.BN;
-  const uint32_t b_stage_bytes = 128u * BN;
-  const int tiles_per_a = p.m_tiles * p.n_tiles;
+  const uint32_t rank = CTA2 ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  const int BNL = CTA2 ? BN / 2 : BN;                      // weight rows this CTA stages
+  const uint32_t b_stage_bytes = 128u * BNL;
+  const int m_units = CTA2 ? (p.m_tiles + 1) / 2 : p.m_tiles;    // row blocks (pairs of them) per position and n tile
+  const int tiles_per_a = m_units * p.n_tiles;
   const int total_tiles = 36 * tiles_per_a;
+  const int first = CTA2 ? blockIdx.x >> 1 : blockIdx.x, step = CTA2 ? gridDim.x >> 1 : gridDim.x;
   constexpr uint32_t TMEM_COLS = 512;     // two accumulator buffers of up to 256 columns
 
   if (threadIdx.x == 0) {
@@ -363,60 +383,103 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       mbar_init(&cfull[s], GEMM_CONV_WARPS);
+      mbar_init(&pfull[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], GEMM_EPI_WARPS * 32);
+      mbar_init(&tempty[b], CTA2 ? 2 * GEMM_EPI_WARPS : GEMM_EPI_WARPS * 32);
     }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 1) {
+    if (CTA2) tmem_alloc2(tmem_slot, TMEM_COLS);
+    else tmem_alloc(tmem_slot, TMEM_COLS);
+  }
   tc_fence_before_sync();
   __syncthreads();
+  if (CTA2) cluster_sync_all();          // the peer's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   int fail_code = 0;
 
-  if (warp == 0) {
-    // -------- producer: two contiguous bulk copies per stage
-    uint32_t it = 0;
+  if (warp == 0 || warp == GEMM_PRODUCER2_WARP) {
+    // -------- producers: two contiguous bulk copies per stage.  Issuing a copy occupies the issuing
+    // warp for about a thousand cycles whatever its size, but the lanes of one instruction issue
+    // together: each pass serves TWO stages (lanes 0/1: A and B of one stage, lanes 2/3: of the
+    // next), and the two producer warps take turns on the passes, so the whole four-stage ring is
+    // being refilled at any time.
+    const uint32_t pw = warp == 0 ? 0u : 1u;
+    const int grp = lane >> 1, gl = lane & 1;      // lanes 0..3 work: stage-in-pass, A / B
+    uint32_t it = 0, gpass = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int tile = first; tile < total_tiles && ok; tile += step) {
       const int a = tile / tiles_per_a;
       const int r = tile - a * tiles_per_a;
-      const int nt = r / p.m_tiles, mt = r - nt * p.m_tiles;
+      const int nt = r / m_units, mu = r - nt * m_units;
+      const int mt = CTA2 ? 2 * mu + static_cast<int>(rank) : mu;
+      const bool live = mt < p.m_tiles;            // an odd number of row blocks leaves the last peer without one
       // fp32: A arrives as plain fp32 (8 KB per stage) in the raw ring; int8: straight into the stage
       const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
-      const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + mt) * p.k_stages * a_gbytes;
-      const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * b_stage_bytes;
-      if (lane == 0 && it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
-      for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-        const int s = it % GEMM_STAGES;
-        const uint32_t ph = (it / GEMM_STAGES) & 1u;
+      const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + (live ? mt : 0)) * p.k_stages * a_gbytes;
+      // pairs: the weight image holds the two halves of every stage one after the other
+      const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * (CTA2 ? 2 : 1) * b_stage_bytes +
+                             (CTA2 ? rank * b_stage_bytes : 0);
+      const size_t b_pitch = static_cast<size_t>(CTA2 ? 2 : 1) * b_stage_bytes;
+      if (pw == 0 && lane == 0 && it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
+      for (int ks0 = 0; ks0 < p.k_stages; ks0 += 2, it += 2, ++gpass) {
+        if ((gpass & 1u) != pw) continue;            // the other producer warp's pass
+        const int ks = ks0 + grp;
+        const bool active = lane < 4 && ks < p.k_stages;
+        const uint32_t my_it = it + grp;
+        const int s = my_it % GEMM_STAGES;
+        const uint32_t ph = (my_it / GEMM_STAGES) & 1u;
         // empty[s] is committed by the MMAs of the stage's previous use, which also implies that the
         // splitter warps are done with raw slot s
-        if (!mbar_wait_warp(&empty[s], ph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+        int w_ok = 1;
+        if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
+        if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
         uint8_t *stage = smem + s * STAGE_BYTES;
-        uint8_t *a_dst = p.kind == KIND_F32 ? raw_ring + s * A_RAW_BYTES : stage;
-        if (lane == 0) mbar_arrive_expect_tx(&full[s], a_gbytes + b_stage_bytes);
+        if (active) {
+          while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
+          }        // every issuing lane observes the completed phase itself
+          if (gl == 0) mbar_arrive_expect_tx(&full[s], (live ? a_gbytes : 0u) + b_stage_bytes);
+        }
         __syncwarp();
-        // A and B are issued by two different lanes so that both copies are in flight together
-        if (lane == 0) tma_bulk_g2s(a_dst, a_src + static_cast<size_t>(ks) * a_gbytes, a_gbytes, &full[s]);
-        if (lane == 1)
-          tma_bulk_g2s(stage + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_stage_bytes, b_stage_bytes, &full[s]);
+        if (active) {
+          if (gl == 0) {
+            if (live)
+              tma_bulk_g2s(stage, a_src + static_cast<size_t>(ks) * a_gbytes, a_gbytes, &full[s]);
+          } else {
+            tma_bulk_g2s(stage + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_pitch, b_stage_bytes, &full[s]);
+          }
+        }
         __syncwarp();
       }
+      if (p.k_stages & 1) --it;        // the last pass of an odd K loop served one stage only
     }
   } else if (warp == 1) {
-    // -------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = p.kind == KIND_F32 ? umma_idesc(1, 2, 2, BM, BN) : umma_idesc(2, 0, 1, BM, BN);
-      const uint32_t b_lbo = 16u * BN;
+    // -------- MMA issuer (pairs: in the leader CTA only; the peer's lane forwards stage readiness)
+    if (lane == 0 && CTA2 && !leader) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = first; tile < total_tiles && ok; tile += step) {
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = it % GEMM_STAGES;
+          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, abort_flag) ||
+              (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag))) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          mbar_arrive_cluster(mapa_u32(&pfull[s], 0));
+        }
+      }
+    } else if (lane == 0) {
+      const int MM = CTA2 ? 2 * BM : BM;
+      const uint32_t idesc = p.kind == KIND_F32 ? umma_idesc(1, 2, 2, MM, BN) : umma_idesc(2, 0, 1, MM, BN);
+      const uint32_t b_lbo = 16u * BNL;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = first; tile < total_tiles && ok; tile += step, ++tcount) {
         const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
         if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
         tc_fence_after_sync();
@@ -427,6 +490,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           const uint32_t ph = (it / GEMM_STAGES) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          if (CTA2 && !mbar_wait(&pfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           tc_fence_after_sync();
           if (ks == 0 && tcount < 8) WG_TRACE(16 + tcount);
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
@@ -439,39 +503,53 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
               const uint64_t alo = umma_desc_kmajor(a_addr + 8192 + k2 * 4096, 2048, 128);
               const uint64_t bhi = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
               const uint64_t blo = umma_desc_kmajor(b_addr + 4 * b_lbo + k2 * 2 * b_lbo, b_lbo, 128);
-              umma_tf32(d_tmem, alo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
-              umma_tf32(d_tmem, ahi, blo, idesc, 1u);
-              umma_tf32(d_tmem, ahi, bhi, idesc, 1u);
+              if (CTA2) {
+                umma_tf32_2cta(d_tmem, alo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
+                umma_tf32_2cta(d_tmem, ahi, blo, idesc, 1u);
+                umma_tf32_2cta(d_tmem, ahi, bhi, idesc, 1u);
+              } else {
+                umma_tf32(d_tmem, alo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
+                umma_tf32(d_tmem, ahi, blo, idesc, 1u);
+                umma_tf32(d_tmem, ahi, bhi, idesc, 1u);
+              }
             }
           } else {
 #pragma unroll
             for (int k2 = 0; k2 < 4; ++k2) {
               const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 4096, 2048, 128);
               const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
-              umma_i8(d_tmem, ad, bd, idesc, (ks | k2) != 0 ? 1u : 0u);
+              if (CTA2) umma_i8_2cta(d_tmem, ad, bd, idesc, (ks | k2) != 0 ? 1u : 0u);
+              else umma_i8(d_tmem, ad, bd, idesc, (ks | k2) != 0 ? 1u : 0u);
             }
           }
-          umma_commit(&empty[s]);
+          if (CTA2) umma_commit_2cta(&empty[s]);
+          else umma_commit(&empty[s]);
         }
-        if (ok) umma_commit(&tfull[b]);
+        if (ok) {
+          if (CTA2) umma_commit_2cta(&tfull[b]);
+          else umma_commit(&tfull[b]);
+        }
         if (tcount < 8) WG_TRACE(24 + tcount);
       }
     }
     __syncwarp();
-  } else if (warp >= 2 + GEMM_EPI_WARPS) {
+  } else if (warp >= 2 + GEMM_EPI_WARPS) {      // (the second producer warp took the first branch)
     // -------- splitter (fp32 only): raw fp32 stage -> tf32 hi plane + residual lo plane, the
     // operands of the 3xTF32 product.  hi = round-to-nearest tf32(x), lo = x - hi (exact).
     if (p.kind == KIND_F32) {
-      const int tid_c = (warp - 2 - GEMM_EPI_WARPS) * 32 + lane;
+      const int cgrp = (warp - 2 - GEMM_EPI_WARPS) / GEMM_CONV_WARPS;       // this warp's group
+      const int tid_c = ((warp - 2 - GEMM_EPI_WARPS) % GEMM_CONV_WARPS) * 32 + lane;
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = first; tile < total_tiles && ok; tile += step) {
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          if (static_cast<int>(it % GEMM_CONV_GROUPS) != cgrp) continue;       // the other group's stage
           const int s = it % GEMM_STAGES;
           const uint32_t ph = (it / GEMM_STAGES) & 1u;
           if (!mbar_wait_warp(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-          const float4 *raw = reinterpret_cast<const float4 *>(raw_ring + s * A_RAW_BYTES);
-          float4 *hi = reinterpret_cast<float4 *>(smem + s * STAGE_BYTES);
+          if (tid_c == 0 && it < 8) WG_TRACE(48 + 2 * it);
+          float4 *hi = reinterpret_cast<float4 *>(smem + s * STAGE_BYTES);     // holds the raw fp32 values on arrival
+          const float4 *raw = hi;
           float4 *lo = hi + A_RAW_BYTES / 16;
 #pragma unroll
           for (int j = 0; j < A_RAW_BYTES / 16 / (GEMM_CONV_WARPS * 32); ++j) {
@@ -492,6 +570,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           fence_proxy_async_smem();      // generic-proxy stores -> visible to the tensor core's reads
           __syncwarp();
           if (lane == 0) mbar_arrive(&cfull[s]);
+          if (tid_c == 0 && it < 8) WG_TRACE(49 + 2 * it);
         }
       }
     }
@@ -502,10 +581,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     const int OCP = p.OCB * 16;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+    const uint32_t tempty_leader0 = CTA2 ? mapa_u32(&tempty[0], 0) : 0u, tempty_leader1 = CTA2 ? mapa_u32(&tempty[1], 0) : 0u;
+    for (int tile = first; tile < total_tiles && ok; tile += step, ++tcount) {
       const int a = tile / tiles_per_a;
       const int r = tile - a * tiles_per_a;
-      const int nt = r / p.m_tiles, mt = r - nt * p.m_tiles;
+      const int nt = r / m_units, mu = r - nt * m_units;
+      const int mt = CTA2 ? 2 * mu + static_cast<int>(rank) : mu;
+      const bool live = mt < p.m_tiles;
       const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
       const int t = mt * BM + row;
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
@@ -532,7 +614,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       auto emit = [&](int k, const uint32_t (&rr)[16]) {      // k-th 16-column block of this warp
         const int blk = half + 2 * k;
         const int ocb = nt * (BN / 16) + blk;
-        if (ocb < p.OCB) {
+        if (live && ocb < p.OCB) {
           float f[16];
           if (p.kind == KIND_F32) {
 #pragma unroll
@@ -586,7 +668,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         if (k + 3 < nblk) emit(k + 3, r3);
       }
       tc_fence_before_sync();
-      mbar_arrive(&tempty[b]);
+      if (CTA2) {
+        // one arrival per warp on the LEADER's barrier: the accumulator is reused by MMAs that write
+        // both CTAs' tensor memory
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(b ? tempty_leader1 : tempty_leader0);
+      } else {
+        mbar_arrive(&tempty[b]);
+      }
       if (threadIdx.x == 64 && tcount < 8) WG_TRACE(40 + tcount);
     }
   }
@@ -594,17 +683,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   if (fail_code != 0) atomicCAS(p.status, 0, fail_code);
   tc_fence_before_sync();
   __syncthreads();
+  if (CTA2) cluster_sync_all();    // nobody leaves (or frees tensor memory) while the other CTA may still signal it
   tc_fence_after_sync();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (CTA2) tmem_dealloc2(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
-constexpr int GEMM_SMEM_BYTES =
-    GEMM_STAGES * (A_STAGE_BYTES + B_STAGE_MAX + A_RAW_BYTES) + (3 * GEMM_STAGES + 4) * 8 + 16 + 128;
+constexpr int GEMM_SMEM_BYTES_1 = GEMM_STAGES_1 * (A_STAGE_BYTES + B_STAGE_MAX) + EPI_CONST_BYTES + (4 * GEMM_STAGES_1 + 4) * 8 + 16 + 128;
+constexpr int GEMM_SMEM_BYTES_2 = GEMM_STAGES_2 * (A_STAGE_BYTES + B_STAGE_MAX / 2) + EPI_CONST_BYTES + (4 * GEMM_STAGES_2 + 4) * 8 + 16 + 128;
+constexpr int GEMM_SMEM_BYTES = GEMM_SMEM_BYTES_1 > GEMM_SMEM_BYTES_2 ? GEMM_SMEM_BYTES_1 : GEMM_SMEM_BYTES_2;
 static_assert(GEMM_SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
-static_assert(GEMM_EPI_WARPS * 2 * MAX_BN * 4 <= GEMM_STAGES * A_RAW_BYTES, "epilogue constants must fit the raw-A ring");
+static_assert(GEMM_EPI_WARPS * 2 * MAX_BN * 4 <= EPI_CONST_BYTES, "epilogue constants must fit their area");
 
 // ------------------------------------------------------------------------------ output transform
 struct WinoOutParams {
@@ -781,6 +873,8 @@ struct WinoImpl {
   float orepS = 1.f, oz = 0.f, mrepS = 1.f, tz = 0.f;
   size_t in_img_bytes = 0, out_img_bytes = 0;
   size_t a_bytes = 0, b_bytes = 0, m_bytes = 0;
+  bool cta2 = false;       // GEMM on pairs of CTAs (weight rows split over the pair)
+  int max_clusters = 0;    // pairs the device holds at once
   void *d_a = nullptr, *d_b = nullptr, *d_m = nullptr, *d_bias = nullptr, *d_scale = nullptr, *d_shift = nullptr;
 };
 
@@ -832,8 +926,37 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
     volatile float rep = 1.0f / d.tinput_scale;
     w->mrepS = d.input_scale * rep;                                      // src/elx_conv_wino_trans_input.cpp:617
   }
-  cudaError_t e = cudaFuncSetAttribute(wino_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(wino_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(wino_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return ELB_GENERAL_ERROR; }
+  {
+    // Pairs of CTAs are opt-in (ELB_WINO_CTA2=1): measured on B200 they are not faster than single
+    // CTAs (VGG conv3_2 GEMM 0.417 ms either way, int8 0.152 vs 0.120 ms), because the kernel is
+    // bound by the hi/lo splitter warps and the epilogue, not by the bytes of B.
+    const char *on2 = getenv("ELB_WINO_CTA2");
+    w->cta2 = g.m_tiles >= 4 && w->BN % 32 == 0 && on2 && atoi(on2) > 0;
+    if (w->cta2) {
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(2 * (sms / 2));
+      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
+      cudaLaunchAttribute at{};
+      at.id = cudaLaunchAttributeClusterDimension;
+      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+      cfg.attrs = &at;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, wino_gemm_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = sms / 2;
+      }
+      w->max_clusters = n;
+    }
+  }
   info.launches_per_call = 3 * ((d.n + w->imgs_per_chunk - 1) / w->imgs_per_chunk);
   return ELB_OK;
 }
@@ -868,13 +991,15 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
             const int o = nt * BN + r;
             if (o >= w->OCP) continue;
             const float *src = &u[(static_cast<size_t>(a) * w->OCP + o) * w->ICP + ks * 16];
-            float *stage = dst + ((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * (32 * BN);
+            // pairs: a stage is stored as two half images of BN/2 rows, one per CTA
+            const int BNH = w->cta2 ? BN / 2 : BN, hf = r / BNH, rr = r % BNH;
+            float *stage = dst + ((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * (32 * BN) + static_cast<size_t>(hf) * 32 * BNH;
             for (int c = 0; c < 16; ++c) {
               const float hi = tf32_rna(src[c]);
               volatile float lo = src[c] - hi;
               const int j = c >> 2, e = c & 3;
-              stage[(static_cast<size_t>(j) * BN + r) * 4 + e] = hi;
-              stage[(static_cast<size_t>(4 + j) * BN + r) * 4 + e] = lo;
+              stage[(static_cast<size_t>(j) * BNH + rr) * 4 + e] = hi;
+              stage[(static_cast<size_t>(4 + j) * BNH + rr) * 4 + e] = lo;
             }
           }
   } else {
@@ -897,8 +1022,9 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
           }
           sq += static_cast<float>(q);
           const int cb = i >> 4, ks = cb >> 3, j = cb & 7;
-          img[(((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * 8 + j) * (16 * BN) + r * 16 + (i & 15)] =
-              static_cast<uint8_t>(q);
+          const int BNH = w->cta2 ? BN / 2 : BN, hf = r / BNH, rr = r % BNH;
+          img[((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * (128 * BN) + static_cast<size_t>(hf) * 128 * BNH +
+              (static_cast<size_t>(j) * BNH + rr) * 16 + (i & 15)] = static_cast<uint8_t>(q);
         }
         volatile float sw = m / 127.0f;
         volatile float sc = sw * d.tinput_scale;
@@ -970,9 +1096,24 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.m_pitch = w->g.m_tiles;           // pitch of the operand image (full chunk)
     gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
     gp.OCB = g.OCB; gp.Tpad = w->g.Tpad; gp.T = g.T; gp.kind = w->kind;
-    const int total = 36 * gp.m_tiles * gp.n_tiles;
-    wino_gemm_kernel<<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
-    W_TRY(cudaGetLastError());
+    if (w->cta2) {
+      const int pairs = 36 * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(2 * (pairs < w->max_clusters ? pairs : w->max_clusters));
+      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
+      cfg.stream = s;
+      cudaLaunchAttribute at{};
+      at.id = cudaLaunchAttributeClusterDimension;
+      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+      cfg.attrs = &at;
+      cfg.numAttrs = 1;
+      W_TRY(cudaLaunchKernelEx(&cfg, wino_gemm_kernel<true>, gp));
+    } else {
+      const int total = 36 * gp.m_tiles * gp.n_tiles;
+      wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+      W_TRY(cudaGetLastError());
+    }
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[2], s));
     // 3. output transform
     WinoOutParams op{};
@@ -1126,7 +1267,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
     void *p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(wino_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    e = cudaFuncSetAttribute(wino_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
     if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
   }
@@ -1179,7 +1320,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   gp.m_tiles = g.m_tiles; gp.m_pitch = g.m_tiles; gp.n_tiles = n_tiles; gp.k_stages = g.k_stages; gp.BN = BN;
   gp.OCB = g.OCB; gp.Tpad = g.Tpad; gp.T = g.T; gp.kind = KIND_F32;
   const int total = 36 * gp.m_tiles * gp.n_tiles;
-  wino_gemm_kernel<<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
   WinoOutParams op{};
   op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;
   op.out_type = OUT_F32; op.with_bias = d.with_bias; op.with_relu = d.with_relu; op.with_sum = d.with_ip_sum;
