@@ -263,7 +263,7 @@ def vgg_weights(idx, ic, oc):
 
 class VggStack:
     """The 13 convolutions of VGG-16 as 13 plans of the library, run back to back on device tensors;
-    the 2x2 pooling between stages is the harness keeping every second row and column."""
+    the 2x2 pooling between stages keeps every second row and column (the library's subsample kernel)."""
 
     def __init__(self, n, int8, device, scales=None):
         import torch
@@ -271,12 +271,18 @@ class VggStack:
         E = importlib.import_module("deep-learning-math-kernel-research_b200")
         self.E, self.n, self.int8 = E, n, int8
         self.layers, self.ops, self.names = [], 0, []
+        self.pool_launches = 0
         k = 0
+        last = None
         for item in VGG16:
             if item == "pool":
-                self.layers.append("pool")
+                oc, hw = last
+                odt = torch.uint8 if int8 else torch.float32
+                self.layers.append(("pool", torch.zeros((n, (oc + 15) // 16, hw // 2, hw // 2, 16), dtype=odt, device="cuda"),
+                                    (oc, hw)))
                 continue
             ic, oc, hw = item
+            last = (oc, hw)
             isc, osc = (scales[k], scales[k + 1]) if int8 else (1.0, 1.0)
             case = vgg_layer_case(k, ic, oc, hw, n, int8, isc, osc)
             d = G.make_desc(case, device=device)
@@ -297,8 +303,13 @@ class VggStack:
         """Enqueue the whole stack on `stream` (a torch stream that is current); returns the last output."""
         i = 0
         for layer in self.layers:
-            if layer == "pool":
-                x = x[:, :, ::2, ::2, :].contiguous()
+            if layer[0] == "pool":
+                _, pooled, (oc, hw) = layer
+                rc = self.E.subsample(pooled, x, self.n, oc, hw, hw, 2, 2, stream=stream.cuda_stream)
+                if rc != 0:
+                    raise SystemExit(f"bench.py: subsample failed rc={rc}: {self.E.last_error()}")
+                self.pool_launches += 1
+                x = pooled
                 continue
             d, out, _ = layer
             if events is not None:
@@ -313,11 +324,11 @@ class VggStack:
         return x
 
     def launches(self):
-        return sum(l[0].launch_count() for l in self.layers if l != "pool")
+        return sum(l[0].launch_count() for l in self.layers if l[0] != "pool") + self.pool_launches
 
     def close(self):
         for l in self.layers:
-            if l != "pool":
+            if l[0] != "pool":
                 l[0].close()
 
 
@@ -343,7 +354,7 @@ def vgg_calibrate(device):
     scales = [1.0 / 255.0]
     s = torch.cuda.current_stream()
     for layer in st.layers:
-        if layer == "pool":
+        if layer[0] == "pool":
             x = x[:, :, ::2, ::2, :].contiguous()
             continue
         d, out, _ = layer
@@ -444,14 +455,15 @@ def run_stack(args, wl, rank, world, local_rank):
     value = aggregate_throughput(ops, ms_step, world)
     peaks, peak_kind = measured_peaks()
     act_bytes = x_np.nbytes + sum(l[1].numel() * l[1].element_size() + (0 if i == 0 else 0)
-                                  for i, l in enumerate(st.layers) if l != "pool")
+                                  for i, l in enumerate(st.layers) if l[0] != "pool")
     # every layer reads its input and writes its output once: inputs are the previous outputs
     # (a quarter of them after a pooling stage)
     alg_bytes = 0
     prev = x_np.nbytes
     for l in st.layers:
-        if l == "pool":
+        if l[0] == "pool":
             prev //= 4
+            alg_bytes += 2 * prev       # the subsample kernel reads a quarter of the pixels and writes them
             continue
         ob = l[1].numel() * l[1].element_size()
         alg_bytes += prev + ob
@@ -464,7 +476,7 @@ def run_stack(args, wl, rank, world, local_rank):
                        "parallelism": f"minibatch split, {world} x replicated weights, {n} images per GPU",
                        "cache": "one step streams more than 1 GB of activations through the 126 MB L2",
                        "layers": [{"name": nm, "ms": round(ms, 4), "tops": round(l[2].cal_ops() / ms / 1e9, 2)}
-                                  for nm, ms, l in zip(st.names, layer_ms, [q for q in st.layers if q != "pool"])],
+                                  for nm, ms, l in zip(st.names, layer_ms, [q for q in st.layers if q[0] != "pool"])],
                        **({"u8_scales": [round(v, 6) for v in scales]} if int8 else {})},
             "clocks": sampler.summary(),
             "e2e": {"value": aggregate_throughput(ops, e2e_ms / e2e_steps, world), "unit": wl["unit"],

@@ -113,6 +113,8 @@ def _load():
         "elb_device_supported": (i32, [i32]),
         "elb_reorder_nchw_to_nChw16c": (i32, [vp, vp, i32, i32, i32, i32, i32, vp]),
         "elb_reorder_nChw16c_to_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, vp]),
+        "elb_reorder": (i32, [vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
+        "elb_subsample_nChw16c": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
         "elb_selftest_bounded_wait": (i32, [i32, C.c_ulonglong]),
     }
     for name, (res, args) in sig.items():
@@ -125,7 +127,7 @@ lib = _load()
 EXPORTED_SYMBOLS = ["elb_conv_sizes", "elb_conv_create", "elb_conv_info", "elb_conv_execute", "elb_conv_enqueue",
                     "elb_conv_prepare", "elb_conv_set_accumulator_dump", "elb_conv_device_status",
                     "elb_conv_launch_count", "elb_conv_set_stage_events", "elb_conv_destroy", "elb_last_error", "elb_device_supported",
-                    "elb_reorder_nchw_to_nChw16c", "elb_reorder_nChw16c_to_nchw"]
+                    "elb_reorder_nchw_to_nChw16c", "elb_reorder_nChw16c_to_nchw", "elb_reorder", "elb_subsample_nChw16c"]
 
 
 def last_error() -> str:
@@ -267,3 +269,28 @@ def elx_conv(desc: eld_conv_t, output, input, weights, bias) -> int:
     if desc.xc is None:
         raise RuntimeError("elx_conv: descriptor is not set up")
     return lib.elb_conv_execute(desc.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias))
+
+
+def _elem_bytes(x) -> int:
+    if hasattr(x, "element_size"):
+        return x.element_size()
+    return x.dtype.itemsize
+
+
+def reorder(dst, dst_format: int, src, src_format: int, *dims, stream=None) -> int:
+    """``euler::reorder<T, dst_format, src_format>(dst, src, dims...)`` (include/euler_reorder.hpp:9-64)
+    for DEVICE tensors: dims are (n, c, h, w), (o, i, h, w) or (g, o, i, h, w) as in the reference.
+    The call is asynchronous on ``stream`` (default stream when None)."""
+    if len(dims) == 4:
+        g, (a, b, h, w) = 1, dims
+    elif len(dims) == 5:
+        g, a, b, h, w = dims
+    else:
+        raise ValueError("reorder takes 4 or 5 extents")
+    return lib.elb_reorder(_ptr(dst), dst_format, _ptr(src), src_format, g, a, b, h, w, _elem_bytes(src), _ptr(stream))
+
+
+def subsample(dst, src, n: int, c: int, h: int, w: int, step_h: int = 2, step_w: int = 2, stream=None) -> int:
+    """Keep every step_h-th row and step_w-th column of a device nChw16c tensor (the glue between two
+    layers of a stack; the reference's harness chains layers on the host, tests/elt_conv.cpp:399-410)."""
+    return lib.elb_subsample_nChw16c(_ptr(dst), _ptr(src), n, c, h, w, step_h, step_w, _elem_bytes(src), _ptr(stream))

@@ -760,6 +760,29 @@ int elb_reorder_nChw16c_to_nchw(void *dst, const void *src, int n, int c, int h,
   return ELB_OK;
 }
 
+int elb_reorder(void *dst, int dst_format, const void *src, int src_format, int g, int a, int b, int h, int w,
+                int elem_bytes, void *cuda_stream) {
+  if (!dst || !src) return fail(ELB_GENERAL_ERROR, "bad reorder argument");
+  bool supported = false;
+  cudaError_t e = launch_reorder(dst, dst_format, src, src_format, g, a, b, h, w, elem_bytes,
+                                 static_cast<cudaStream_t>(cuda_stream), supported);
+  if (!supported) return fail(ELB_UNIMPLEMENTED, "reorder from format %d to format %d (element size %d) is not implemented",
+                              src_format, dst_format, elem_bytes);
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "reorder launch failed: %s", cudaGetErrorString(e));
+  return ELB_OK;
+}
+
+int elb_subsample_nChw16c(void *dst, const void *src, int n, int c, int h, int w, int step_h, int step_w,
+                          int elem_bytes, void *cuda_stream) {
+  if (!dst || !src || (elem_bytes != 1 && elem_bytes != 4) || n < 1 || c < 1 || h < 1 || w < 1 || step_h < 1 ||
+      step_w < 1)
+    return fail(ELB_GENERAL_ERROR, "bad subsample argument");
+  cudaError_t e = launch_subsample_blocked(dst, src, n, c, h, w, step_h, step_w, elem_bytes,
+                                           static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "subsample launch failed: %s", cudaGetErrorString(e));
+  return ELB_OK;
+}
+
 // Test hook (not part of the reference surface): runs the bounded-wait self test and returns the
 // status word the kernel wrote (ST_WAIT_TIMEOUT_TEST = 104 when the wait gave up as designed).
 ELB_API int elb_selftest_bounded_wait(int device, unsigned long long limit_ns) {

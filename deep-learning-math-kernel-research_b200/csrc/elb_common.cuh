@@ -166,4 +166,11 @@ cudaError_t launch_reorder_to_blocked(void *dst, const void *src, int n, int c, 
 cudaError_t launch_reorder_from_blocked(void *dst, const void *src, int n, int c, int h, int w, int eb,
                                         cudaStream_t s);
 
+// Any reorder<T, dst, src> of the reference; supported = false when the pair is not one of them.
+cudaError_t launch_reorder(void *dst, int dst_fmt, const void *src, int src_fmt, int g, int a, int b, int h,
+                           int w, int eb, cudaStream_t s, bool &supported);
+// dst[n][C/16][ceil(h/sh)][ceil(w/sw)][16] = src[n][C/16][y*sh][x*sw][16]
+cudaError_t launch_subsample_blocked(void *dst, const void *src, int n, int c, int h, int w, int sh, int sw, int eb,
+                                     cudaStream_t s);
+
 }  // namespace elb

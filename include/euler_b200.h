@@ -165,6 +165,23 @@ ELB_API int elb_reorder_nchw_to_nChw16c(void *dst, const void *src, int n, int c
 ELB_API int elb_reorder_nChw16c_to_nchw(void *dst, const void *src, int n, int c, int h, int w,
                                         int elem_bytes, void *cuda_stream);
 
+/* Any layout conversion the reference exports, on the device -- replaces the twelve
+ * reorder<T, dst, src> specialisations (src/elx_reorder.cpp:11-207): nchw <-> nhwc, nchw <-> nChw16c,
+ * oihw <-> hwio, oihw <-> OIhw16i16o, goihw <-> ghwio, goihw <-> gOIhw16i16o -- and the remaining
+ * pairs inside each family (nhwc <-> nChw16c, hwio <-> OIhw16i16o, ghwio <-> gOIhw16i16o).
+ * dst_format / src_format are ELB_NCHW ... ELB_GOIHW16I16O; (g, a, b, h, w) are the logical extents
+ * (activations: g ignored, a = n, b = c; weights: a = o, b = i; g only for the g* formats).
+ * Lanes of a blocked destination past o / i / c are written as zero, as the reference does.
+ * elem_bytes is 1 or 4; pointers are device pointers; returns ELB_UNIMPLEMENTED for other pairs. */
+ELB_API int elb_reorder(void *dst, int dst_format, const void *src, int src_format, int g, int a, int b,
+                        int h, int w, int elem_bytes, void *cuda_stream);
+
+/* Spatial subsample of an nChw16c tensor on the device: dst[n][C/16][ceil(h/step_h)][ceil(w/step_w)][16]
+ * = src[n][C/16][y*step_h][x*step_w][16].  The glue between two layers of a stack that the reference's
+ * harness leaves to the host (tests/elt_conv.cpp:399-410 feeds a layer's output to the next layer). */
+ELB_API int elb_subsample_nChw16c(void *dst, const void *src, int n, int c, int h, int w, int step_h,
+                                  int step_w, int elem_bytes, void *cuda_stream);
+
 /* FP32 Winograd F(4x4,3x3) convolution that allocates nothing -- no counterpart in the reference.
  *
  * For callers that may not allocate device memory at the point where they run a convolution (a
