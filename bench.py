@@ -55,6 +55,10 @@ WORKLOADS = {
                      "tensor, sum scale 1.0) u8 out nChw16c; the reference's KxK path ignores the sum flag"),
     "c4": dict(metric="effective_conv_tops_int8_winograd", unit="TOP/s", dtype="u8",
                desc="INT8 Winograd F(4x4,3x3) N=128 C=K=512 28x28 s1 p1 f32 out nChw16c"),
+    "c1t4": dict(metric="effective_conv_tflops_fp32_winograd_f2x2", unit="TFLOP/s", dtype="tf32x3(fp32)",
+                 desc="FP32 Winograd F(2x2,3x3) (tile_size 4) VGG-16 conv3_2 N=64 C=K=256 56x56 s1 p1 bias+ReLU nChw16c"),
+    "c4t4": dict(metric="effective_conv_tops_int8_winograd_f2x2", unit="TOP/s", dtype="u8",
+                 desc="INT8 Winograd F(2x2,3x3) (tile_size 4) N=128 C=K=512 28x28 s1 p1 f32 out nChw16c"),
     "dw": dict(metric="effective_conv_tops_int8_depthwise", unit="TOP/s", dtype="u8",
                desc="INT8 depthwise 3x3 MobileNet-v1 Conv2d_3 N=64 C=128 56x56 s1 p1 bias+ReLU u8 out nChw16c T=14"),
     "c5": dict(metric="effective_conv_tflops_fp32_winograd_vgg16_stack", unit="TFLOP/s", dtype="tf32x3(fp32)",
@@ -207,11 +211,12 @@ def roofline_of(workload, case, d, alg_bytes, ms_step, stage_ms, peaks, peak_kin
     tiles = R.wino_tiles(case)
     in_b = case.n * icp * case.ih * case.iw * (4 if case.types == "fp32" else 1)
     out_b = case.n * ocp * case.oh * case.ow * (4 if case.out_dtype.__name__ == "float32" else 1)
-    v_b = 36 * tiles * icp * (4 if case.types == "fp32" else 1)
-    m_b = 36 * tiles * ocp * 4
+    aa = R.wino_edge(case) ** 2
+    v_b = aa * tiles * icp * (4 if case.types == "fp32" else 1)
+    m_b = aa * tiles * ocp * 4
     names = ["wino_input_kernel", "wino_gemm_kernel", "wino_output_kernel"]
     kernels = [{"kernel": names[0], "ms": stage_ms[0], "bytes": in_b + v_b},
-               {"kernel": names[1], "ms": stage_ms[1], "bytes": v_b + m_b, "flops": 2 * 36 * tiles * icp * ocp},
+               {"kernel": names[1], "ms": stage_ms[1], "bytes": v_b + m_b, "flops": 2 * aa * tiles * icp * ocp},
                {"kernel": names[2], "ms": stage_ms[2], "bytes": m_b + out_b}]
     for k in kernels:
         k["gbs"] = k["bytes"] / (k["ms"] * 1e-3) / 1e9

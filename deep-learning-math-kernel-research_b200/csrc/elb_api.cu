@@ -203,7 +203,7 @@ int choose_kernel(const elb_conv_desc_t &d, int algorithm, int tile, const char 
   if (d.g != 1 && !depthwise) { *why = "grouped convolution"; return ELB_KERNEL_NONE; }
   if (algorithm == ELB_CONV_WINOGRAD) {
     if (d.stride_h != 1 || d.kh != 3 || d.kw != 3 || d.g != 1) { *why = "Winograd needs 3x3 stride 1"; return ELB_KERNEL_NONE; }
-    if (tile != 6) { *why = "only tile_size 6, F(4x4,3x3), is implemented"; return ELB_KERNEL_NONE; }
+    if (tile != 6 && tile != 4) { *why = "only tile_size 6, F(4x4,3x3), and 4, F(2x2,3x3), are implemented"; return ELB_KERNEL_NONE; }
     if (d.fmt_weights != ELB_OIHW16I16O) { *why = "weights must be OIhw16i16o"; return ELB_KERNEL_NONE; }
     if (is_fp32_user(d)) return ELB_KERNEL_WINO_F32_UMMA;
     if (is_int8_user(d)) return ELB_KERNEL_WINO_I8_UMMA;

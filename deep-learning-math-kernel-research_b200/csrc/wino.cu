@@ -98,6 +98,7 @@ __device__ __forceinline__ void at6(const float (&f)[6], float (&p)[4]) {
 }
 
 struct WinoGeom {
+  int A;          // input tile edge: 6 = F(4x4,3x3), 4 = F(2x2,3x3); output tile edge A - 2
   int N, CB, OCB, IH, IW, OH, OW, ht, wt, pad_t, pad_l;
   int T;          // tiles in this chunk = images * ht * wt
   int m_tiles;    // ceil(T / 128)
@@ -332,6 +333,107 @@ __global__ void __launch_bounds__(TRANS_THREADS, 512 / TRANS_THREADS) wino_input
   }
 }
 
+
+// ------------------------------------------------------------------------------ F(2x2,3x3), tile_size 4
+// Same data flow with 16 transform positions, 4x4 input tiles anchored every 2 pixels and 2x2
+// output tiles.  The matrices hold only 0, +-1 (and powers of two on the weight side), so the
+// transforms are sums; they are written in the reference's order
+// (src/kernel/elk_conv_wino_2x2_3x3_input.hxx:103-149, ..._output.hxx:89-97).
+__device__ __forceinline__ void bt4(const float (&f)[4], float (&o)[4]) {
+  o[0] = __fsub_rn(f[0], f[2]);
+  o[1] = __fsub_rn(f[2], f[1]);
+  o[2] = __fadd_rn(f[1], f[2]);
+  o[3] = __fsub_rn(f[3], f[1]);
+}
+
+// One thread = one 4x4 tile x 4 consecutive channels (64 values).  IN_U8: quantises to u8 like the
+// F(4x4,3x3) kernel; |V| <= 4 * 255, so the magic-number rounding is exact whenever the host found
+// 1020 * |mrepS| + |tz| < 2^22 (FAST), else the general conversion is kept.
+template <bool IN_U8, bool FAST>
+__global__ void __launch_bounds__(128) wino4_input_kernel(const __grid_constant__ WinoInParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * 32 + (threadIdx.x >> 2);
+  const int cb = blockIdx.y;
+  if (t >= g.Tpad) return;
+  const int mt = t >> 7, row = t & 127;
+  const bool live = t < g.T;
+  int n = 0, th = 0, tw = 0;
+  if (live) {
+    n = t / (g.ht * g.wt);
+    const int r = t - n * g.ht * g.wt;
+    th = r / g.wt;
+    tw = r - th * g.wt;
+  }
+  const int ih0 = 2 * th - g.pad_t, iw0 = 2 * tw - g.pad_l;
+  float d[4][4][4];
+#pragma unroll
+  for (int h = 0; h < 4; ++h)
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int ih = ih0 + h, iw = iw0 + w;
+      const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+      const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
+      if (IN_U8) {
+        const uint32_t raw = ok ? __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(p.in) + pix * 16) + quad) : 0u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          d[h][w][c] = __fsub_rn(__uint_as_float(__byte_perm(raw, 0x4B000000u, 0x7650 + c)), 8388608.0f);
+      } else {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ok) v = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16) + quad);
+        d[h][w][0] = v.x; d[h][w][1] = v.y; d[h][w][2] = v.z; d[h][w][3] = v.w;
+      }
+    }
+  float v[4][4][4];   // v[i][j][channel]
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float gg[4][4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {       // along w
+      const float f[4] = {d[h][0][c], d[h][1][c], d[h][2][c], d[h][3][c]};
+      bt4(f, gg[h]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {       // along h
+      const float f[4] = {gg[0][j], gg[1][j], gg[2][j], gg[3][j]};
+      float o[4];
+      bt4(f, o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i][j][c] = o[i];
+    }
+    // the reference sums the last element in another order (elk_conv_wino_2x2_3x3_input.hxx:146)
+    v[3][3][c] = __fadd_rn(__fsub_rn(__fsub_rn(d[1][1][c], d[1][3][c]), d[3][1][c]), d[3][3][c]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int a = i * 4 + j;
+      if (IN_U8) {
+        uint32_t b[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float f = __fmaf_rn(v[i][j][c], p.mrepS, p.tz);
+          b[c] = min(__float_as_uint(__fadd_rn(f, 12582912.0f)) - 0x4B400000u, 255u);
+          if (!FAST) {
+            if (!(fabsf(f) < 4194304.0f)) {
+              const float q = rintf(f);
+              b[c] = (q < 0.0f || q > 255.0f || q != q) ? 255u : static_cast<uint32_t>(q);
+            }
+          }
+        }
+        const uint32_t w = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+        const size_t off = ((((static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4;
+        *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) + off) = live ? w : 0u;
+      } else {
+        const size_t stage = (static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + cb;
+        float *base = static_cast<float *>(p.a_img) + stage * (A_RAW_BYTES / 4);
+        *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = make_float4(v[i][j][0], v[i][j][1], v[i][j][2], v[i][j][3]);
+      }
+    }
+}
+
 // ------------------------------------------------------------------------------ batched GEMM
 struct WinoGemmParams {
   const uint8_t *a_img;     // [36][m_tiles][k_stages][A_STAGE_BYTES]
@@ -343,6 +445,7 @@ struct WinoGemmParams {
   int *status;
   long long *trace;         // optional per-CTA timeline (SM cycle counter), 64 slots per CTA (debug)
   int m_tiles, m_pitch, n_tiles, k_stages, BN, OCB, Tpad, T, kind;
+  int positions;            // A*A independent GEMMs: 36 for F(4x4,3x3), 16 for F(2x2,3x3)
 };
 // CTA2 = true: the kernel runs as clusters of two CTAs.  A pair multiplies TWO 128-tile row blocks
 // (one per CTA) by the BN transformed weights with one tcgen05.mma.cta_group::2 per K step; each
@@ -380,7 +483,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   const uint32_t b_stage_bytes = 128u * BNL;
   const int m_units = CTA2 ? (p.m_tiles + 1) / 2 : p.m_tiles;    // row blocks (pairs of them) per position and n tile
   const int tiles_per_a = m_units * p.n_tiles;
-  const int total_tiles = 36 * tiles_per_a;
+  const int total_tiles = p.positions * tiles_per_a;
   const int first = CTA2 ? blockIdx.x >> 1 : blockIdx.x, step = CTA2 ? gridDim.x >> 1 : gridDim.x;
   constexpr uint32_t TMEM_COLS = 512;     // two accumulator buffers of up to 256 columns
 
@@ -816,6 +919,101 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid
   }
 }
 
+
+// F(2x2,3x3) output transform: one thread = one tile x 4 channels.  Sums in the reference's order
+// (src/kernel/elk_conv_wino_2x2_3x3_output.hxx:89-97); the epilogue is the one above except that
+// u8 / s8 results are rounded toward minus infinity (:145-153), where every other tile size
+// rounds to nearest even.
+__global__ void __launch_bounds__(128) wino4_output_kernel(const __grid_constant__ WinoOutParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * 32 + (threadIdx.x >> 2);
+  const int ocb = blockIdx.y;
+  if (t >= g.T) return;
+  const int n = t / (g.ht * g.wt);
+  const int r = t - n * g.ht * g.wt;
+  const int th = r / g.wt, tw = r - th * g.wt;
+  float4 raw[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      raw[i][j] = __ldg(reinterpret_cast<const float4 *>(
+          p.m_in + (((static_cast<size_t>(i * 4 + j) * g.OCB + ocb) * 4 + quad) * g.Tpad + t) * 4));
+  float y[2][2][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float m[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        m[i][j] = c == 0 ? raw[i][j].x : c == 1 ? raw[i][j].y : c == 2 ? raw[i][j].z : raw[i][j].w;
+    const float c0 = __fadd_rn(__fadd_rn(m[1][0], m[1][1]), m[1][2]);
+    const float c1 = __fadd_rn(__fadd_rn(m[2][0], m[2][1]), m[2][2]);
+    const float c2 = __fsub_rn(__fadd_rn(m[1][2], m[1][3]), m[1][1]);
+    const float c3 = __fsub_rn(__fadd_rn(m[2][2], m[2][3]), m[2][1]);
+    y[0][0][c] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(m[0][0], m[0][1]), m[0][2]), c0), c1);
+    y[1][0][c] = __fadd_rn(__fadd_rn(__fadd_rn(__fsub_rn(c1, c0), m[3][0]), m[3][1]), m[3][2]);
+    y[0][1][c] = __fadd_rn(__fadd_rn(__fadd_rn(__fsub_rn(m[0][2], m[0][1]), m[0][3]), c2), c3);
+    y[1][1][c] = __fadd_rn(__fadd_rn(__fsub_rn(__fsub_rn(c3, c2), m[3][1]), m[3][2]), m[3][3]);
+  }
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.with_bias && p.bias) bias4 = *reinterpret_cast<const float4 *>(p.bias + ocb * 16 + quad * 4);
+  const float bb[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
+  const int elt = p.out_type == OUT_F32 ? 4 : 1;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int oh = 2 * th + i, ow = 2 * tw + j;
+      if (oh >= g.OH || ow >= g.OW) continue;
+      const size_t pix = ((static_cast<size_t>(n) * g.OCB + ocb) * g.OH + oh) * g.OW + ow;
+      uint8_t *dst = static_cast<uint8_t *>(p.out) + (pix * 16 + quad * 4) * elt;
+      float f[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        f[c] = y[i][j][c];
+        if (p.with_bias) f[c] = __fadd_rn(f[c], bb[c]);
+        if (p.out_type != OUT_F32) f[c] = __fmaf_rn(f[c], p.orepS, p.oz);
+      }
+      if (p.with_sum) {
+        if (p.out_type == OUT_F32) {
+          const float4 pv = *reinterpret_cast<const float4 *>(dst);
+          f[0] = __fadd_rn(f[0], pv.x); f[1] = __fadd_rn(f[1], pv.y);
+          f[2] = __fadd_rn(f[2], pv.z); f[3] = __fadd_rn(f[3], pv.w);
+        } else {
+          const uint32_t pv = *reinterpret_cast<const uint32_t *>(dst);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t b = (pv >> (8 * c)) & 0xFFu;
+            f[c] = __fadd_rn(f[c], p.out_type == OUT_U8 ? static_cast<float>(b)
+                                                        : static_cast<float>(static_cast<int>(static_cast<int8_t>(b))));
+          }
+        }
+      }
+      if (p.with_relu) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) f[c] = fmaxf(f[c], 0.0f);
+      }
+      if (p.out_type == OUT_F32) {
+        *reinterpret_cast<float4 *>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+      } else {
+        uint32_t w = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float q = floorf(f[c]);
+          uint32_t b;
+          // u8: the unsigned conversion of a negative value saturates to 255
+          if (p.out_type == OUT_U8) b = (q >= 0.0f && q <= 255.0f) ? static_cast<uint32_t>(q) : 255u;
+          else b = static_cast<uint32_t>(static_cast<int>(fminf(fmaxf(q, -128.0f), 127.0f))) & 0xFFu;
+          w |= b << (8 * c);
+        }
+        *reinterpret_cast<uint32_t *>(dst) = w;
+      }
+    }
+}
+
 // ------------------------------------------------------------------------------ host side
 inline float tf32_rna(float x) {            // what cvt.rna.tf32.f32 returns for finite x
   uint32_t u;
@@ -847,15 +1045,47 @@ inline void g3(float f0, float f1, float f2, float o[6]) {
   o[5] = f2;
 }
 
-// U[a][oc][ic] = G g G^T, kh direction first (the reference's order), zero for padded channels.
-std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, int ICP) {
-  std::vector<float> u(static_cast<size_t>(36) * OCP * ICP, 0.0f);
+// F(2x2,3x3): G rows (1,0,0), (.5,-.5,.5), (.5,.5,.5), (0,0,1); kw direction first, the sums in the
+// reference's order, the power-of-two factors applied last (exact)
+// (src/kernel/elk_conv_wino_2x2_3x3_weights.hxx:73-107).
+inline void weights_tile4(const float (&g)[3][3], float (&u)[4][4]) {
+  const float cs[4] = {1.0f, 0.5f, 0.5f, 1.0f};
+  float r[3][4];
+  for (int x = 0; x < 3; ++x) {
+    volatile float d = g[x][0] - g[x][1];
+    volatile float a = g[x][0] + g[x][1];
+    volatile float s1 = d + g[x][2];
+    volatile float s2 = a + g[x][2];
+    r[x][0] = g[x][0]; r[x][1] = s1; r[x][2] = s2; r[x][3] = g[x][2];
+  }
+  for (int j = 0; j < 4; ++j) {
+    volatile float d = r[0][j] - r[1][j];
+    volatile float a = r[0][j] + r[1][j];
+    volatile float s1 = d + r[2][j];
+    volatile float s2 = a + r[2][j];
+    u[0][j] = cs[j] * r[0][j];
+    u[1][j] = cs[j] * 0.5f * s1;
+    u[2][j] = cs[j] * 0.5f * s2;
+    u[3][j] = cs[j] * r[2][j];
+  }
+}
+
+// U[a][oc][ic] = G g G^T in the reference's order, zero for padded channels; a = hA*A + wA.
+std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, int ICP, int A) {
+  std::vector<float> u(static_cast<size_t>(A) * A * OCP * ICP, 0.0f);
   const int I2 = ICP / 16;
   for (int o = 0; o < oc; ++o)
     for (int i = 0; i < ic; ++i) {
       float g[3][3], m[6][3], r[6];
       for (int kh = 0; kh < 3; ++kh)
         for (int kw = 0; kw < 3; ++kw) g[kh][kw] = w[host::w_index(I2, 3, 3, o, i, kh, kw)];
+      if (A == 4) {
+        float u4[4][4];
+        weights_tile4(g, u4);
+        for (int a = 0; a < 4; ++a)
+          for (int b = 0; b < 4; ++b) u[(static_cast<size_t>(a * 4 + b) * OCP + o) * ICP + i] = u4[a][b];
+        continue;
+      }
       for (int kw = 0; kw < 3; ++kw) {
         g3(g[0][kw], g[1][kw], g[2][kw], r);
         for (int a = 0; a < 6; ++a) m[a][kw] = r[a];
@@ -886,6 +1116,7 @@ struct WinoImpl {
 
 int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, std::string &err) {
   if (d.pad_t != 1 || d.pad_l != 1) { err = "Winograd needs pad 1"; return ELB_UNIMPLEMENTED; }
+  if (info.tile_size != 6 && info.tile_size != 4) { err = "Winograd tile_size must be 6 or 4"; return ELB_UNIMPLEMENTED; }
   WinoImpl *w = new WinoImpl();
   pl.impl = w;
   w->kind = info.kernel == ELB_KERNEL_WINO_I8_UMMA ? KIND_I8 : KIND_F32;
@@ -899,7 +1130,9 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   WinoGeom &g = w->g;
   g.CB = w->ICP / V; g.OCB = w->OCP / V;
   g.IH = d.ih; g.IW = d.iw; g.OH = d.oh; g.OW = d.ow;
-  g.ht = (d.oh + 3) / 4; g.wt = (d.ow + 3) / 4;
+  g.A = info.tile_size;
+  const int OT = g.A - 2, AA = g.A * g.A;
+  g.ht = (d.oh + OT - 1) / OT; g.wt = (d.ow + OT - 1) / OT;
   g.pad_t = d.pad_t; g.pad_l = d.pad_l;
   g.k_stages = w->kind == KIND_F32 ? g.CB : (g.CB + 7) / 8;
   w->n_tiles = (w->OCP + MAX_BN - 1) / MAX_BN;
@@ -907,7 +1140,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   // chunk of whole images whose transform-domain buffers fit the budget
   const size_t tiles_img = static_cast<size_t>(g.ht) * g.wt;
   const size_t a_gbytes = w->kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;    // one stage of A in global memory
-  const size_t per_tile = static_cast<size_t>(36) * (static_cast<size_t>(g.k_stages) * a_gbytes / BM + static_cast<size_t>(w->OCP) * 4);
+  const size_t per_tile = static_cast<size_t>(AA) * (static_cast<size_t>(g.k_stages) * a_gbytes / BM + static_cast<size_t>(w->OCP) * 4);
   size_t imgs = WORKSPACE_BUDGET / (per_tile * tiles_img);
   if (imgs < 1) imgs = 1;
   if (imgs > static_cast<size_t>(d.n)) imgs = d.n;
@@ -916,9 +1149,9 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   g.T = static_cast<int>(imgs * tiles_img);
   g.m_tiles = (g.T + BM - 1) / BM;
   g.Tpad = g.m_tiles * BM;
-  w->a_bytes = static_cast<size_t>(36) * g.m_tiles * g.k_stages * a_gbytes;
-  w->b_bytes = static_cast<size_t>(36) * w->n_tiles * g.k_stages * 128 * w->BN;
-  w->m_bytes = static_cast<size_t>(36) * g.OCB * g.Tpad * 16 * 4;
+  w->a_bytes = static_cast<size_t>(AA) * g.m_tiles * g.k_stages * a_gbytes;
+  w->b_bytes = static_cast<size_t>(AA) * w->n_tiles * g.k_stages * 128 * w->BN;
+  w->m_bytes = static_cast<size_t>(AA) * g.OCB * g.Tpad * 16 * 4;
   w->in_img_bytes = static_cast<size_t>(w->ICP) * d.ih * d.iw * (d.dt_input == ELB_F32 ? 4 : 1);
   w->out_type = d.dt_output == ELB_F32 ? OUT_F32 : d.dt_output == ELB_U8 ? OUT_U8 : OUT_S8;
   w->out_img_bytes = static_cast<size_t>(w->OCP) * d.oh * d.ow * (w->out_type == OUT_F32 ? 4 : 1);
@@ -984,13 +1217,13 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
     if (!bias) { err = "bias is null but with_bias is set"; return ELB_GENERAL_ERROR; }
     W_TRY(cudaMemcpy(hb.data(), bias, static_cast<size_t>(w->OCP) * 4, cudaMemcpyDefault));
   }
-  std::vector<float> u = transform_weights(hw.data(), d.oc, d.ic, w->OCP, w->ICP);
-  const int BN = w->BN, KS = g.k_stages;
+  std::vector<float> u = transform_weights(hw.data(), d.oc, d.ic, w->OCP, w->ICP, g.A);
+  const int BN = w->BN, KS = g.k_stages, AA = g.A * g.A;
   std::vector<uint8_t> img(w->b_bytes, 0);
   if (w->kind == KIND_F32) {
     // [a][nt][ks = channel block][plane][chunk j = 4 channels][BN rows][4 floats]
     float *dst = reinterpret_cast<float *>(img.data());
-    for (int a = 0; a < 36; ++a)
+    for (int a = 0; a < AA; ++a)
       for (int nt = 0; nt < w->n_tiles; ++nt)
         for (int ks = 0; ks < KS; ++ks)
           for (int r = 0; r < BN; ++r) {
@@ -1011,8 +1244,8 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
   } else {
     // per (a, oc): abs-max over ic, q = rne((U*127)/absmax), scale = (absmax/127)*tS,
     // shift = -(sum q * scale) * ceil(tz)      (src/elx_conv_wino_trans_weights.cpp:437-535)
-    std::vector<float> scale(static_cast<size_t>(36) * w->OCP, 0.0f), shift(scale.size(), 0.0f);
-    for (int a = 0; a < 36; ++a)
+    std::vector<float> scale(static_cast<size_t>(AA) * w->OCP, 0.0f), shift(scale.size(), 0.0f);
+    for (int a = 0; a < AA; ++a)
       for (int o = 0; o < w->OCP; ++o) {
         const float *src = &u[(static_cast<size_t>(a) * w->OCP + o) * w->ICP];
         float m = 0.0f;
@@ -1084,7 +1317,13 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     dim3 gi((m_tiles_run * BM + TRANS_TILES - 1) / TRANS_TILES, g.CB);
     const bool timed = pl.stage_ev[0] != nullptr && n0 == first;
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[0], s));
-    if (w->kind == KIND_I8) {
+    if (g.A == 4) {
+      dim3 g4((m_tiles_run * BM + 31) / 32, g.CB);
+      const bool fast = 1020.0f * std::fabs(w->mrepS) + std::fabs(w->tz) < 4194304.0f;
+      if (w->kind != KIND_I8) wino4_input_kernel<false, true><<<g4, 128, 0, s>>>(ip);
+      else if (fast) wino4_input_kernel<true, true><<<g4, 128, 0, s>>>(ip);
+      else wino4_input_kernel<true, false><<<g4, 128, 0, s>>>(ip);
+    } else if (w->kind == KIND_I8) {
       // largest |V| for u8 inputs: 255 * (largest absolute row sum of B^T = 5.28125)^2
       const bool fast = 255.0f * 27.8916f * std::fabs(w->mrepS) + std::fabs(w->tz) < 4194304.0f;
       if (fast) wino_input_u8_kernel<true><<<gi, TRANS_THREADS, 0, s>>>(ip);
@@ -1107,8 +1346,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.m_pitch = w->g.m_tiles;           // pitch of the operand image (full chunk)
     gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
     gp.OCB = g.OCB; gp.Tpad = w->g.Tpad; gp.T = g.T; gp.kind = w->kind;
+    gp.positions = g.A * g.A;
     if (w->cta2) {
-      const int pairs = 36 * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
+      const int pairs = gp.positions * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
       cudaLaunchConfig_t cfg{};
       cfg.gridDim = dim3(2 * (pairs < w->max_clusters ? pairs : w->max_clusters));
       cfg.blockDim = dim3(GEMM_THREADS);
@@ -1121,7 +1361,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
       cfg.numAttrs = 1;
       W_TRY(cudaLaunchKernelEx(&cfg, wino_gemm_kernel<true>, gp));
     } else {
-      const int total = 36 * gp.m_tiles * gp.n_tiles;
+      const int total = gp.positions * gp.m_tiles * gp.n_tiles;
       wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
       W_TRY(cudaGetLastError());
     }
@@ -1136,7 +1376,8 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     op.out_type = w->out_type; op.with_bias = w->with_bias; op.with_relu = w->with_relu; op.with_sum = w->with_sum;
     op.orepS = w->orepS; op.oz = w->oz;
     dim3 go((g.T + TRANS_TILES - 1) / TRANS_TILES, g.OCB);
-    wino_output_kernel<<<go, TRANS_THREADS, 0, s>>>(op);
+    if (g.A == 4) wino4_output_kernel<<<dim3((g.T + 31) / 32, g.OCB), 128, 0, s>>>(op);
+    else wino_output_kernel<<<go, TRANS_THREADS, 0, s>>>(op);
     W_TRY(cudaGetLastError());
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[3], s));
     launches += 3;
@@ -1291,6 +1532,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   WinoGeom g{};
   g.N = d.n; g.CB = ICP / V; g.OCB = OCP / V;
   g.IH = d.ih; g.IW = d.iw; g.OH = d.oh; g.OW = d.ow;
+  g.A = 6;
   g.ht = (d.oh + 3) / 4; g.wt = (d.ow + 3) / 4;
   g.pad_t = 1; g.pad_l = 1;
   g.k_stages = g.CB;
@@ -1330,6 +1572,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   gp.status = status;
   gp.m_tiles = g.m_tiles; gp.m_pitch = g.m_tiles; gp.n_tiles = n_tiles; gp.k_stages = g.k_stages; gp.BN = BN;
   gp.OCB = g.OCB; gp.Tpad = g.Tpad; gp.T = g.T; gp.kind = KIND_F32;
+  gp.positions = 36;
   const int total = 36 * gp.m_tiles * gp.n_tiles;
   wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
   WinoOutParams op{};

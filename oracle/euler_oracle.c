@@ -43,7 +43,13 @@ typedef struct orc_conv {
   float sum_scale, sum_z;
   float tin_scale, tin_z;    /* wino_tinput_quant */
   int32_t fused_epilogue;    /* 1: acc*scale+shift is one fma (what g++ -mfma emits) */
+  int32_t tile;              /* Winograd tile_size A: 6 (or 0) = F(4x4,3x3), 4 = F(2x2,3x3) */
 } orc_conv_t;
+
+/* Winograd geometry: A = input tile edge, A - 2 = output tile edge */
+static inline int wino_A(const orc_conv_t *p) { return p->tile == 4 ? 4 : 6; }
+static inline int wino_ht(const orc_conv_t *p) { int o = wino_A(p) - 2; return (p->oh + o - 1) / o; }
+static inline int wino_wt(const orc_conv_t *p) { int o = wino_A(p) - 2; return (p->ow + o - 1) / o; }
 
 /* round to nearest even, the mode of _MM_FROUND_TO_NEAREST_INT */
 static inline float rne(float x) { return nearbyintf(x); }
@@ -316,9 +322,74 @@ static inline void wino_at6(const float f[6], float p[4]) {
   }
 }
 
-/* tweights out: [36][OC][IC] fp32 (a = hA*6 + wA).  Padded channels are zero. */
+
+/* ------------------------------------------------------------------------------------------
+ * Winograd F(2x2,3x3) (reference tile_size = 4).  Only additions and multiplications by powers
+ * of two, so the only rounding is in the adds; their order is the reference's.
+ *
+ * Input (src/kernel/elk_conv_wino_2x2_3x3_input.hxx:103-149): B^T rows (1,0,-1,0), (0,-1,1,0),
+ * (0,1,1,0), (0,-1,0,1), w direction first.  The last element is summed in a different order there.
+ * ------------------------------------------------------------------------------------------ */
+static inline void wino_bt4(const float f[4], float o[4]) {
+  o[0] = f[0] - f[2];
+  o[1] = f[2] - f[1];
+  o[2] = f[1] + f[2];
+  o[3] = f[3] - f[1];
+}
+static void wino_input_tile4(float d[6][6], float v[6][6]) {
+  float g[4][4];
+  for (int h = 0; h < 4; ++h) wino_bt4(d[h], g[h]);
+  for (int j = 0; j < 4; ++j) {
+    float col[4] = {g[0][j], g[1][j], g[2][j], g[3][j]}, o[4];
+    wino_bt4(col, o);
+    for (int i = 0; i < 4; ++i) v[i][j] = o[i];
+  }
+  v[3][3] = ((d[1][1] - d[1][3]) - d[3][1]) + d[3][3];      /* :146 */
+}
+/* Weights (src/kernel/elk_conv_wino_2x2_3x3_weights.hxx:73-107): G rows (1,0,0), (.5,-.5,.5),
+ * (.5,.5,.5), (0,0,1); w direction first. */
+static void wino_weights_tile4(float g[3][3], float u[6][6]) {
+  static const float cs[4] = {1.0f, 0.5f, 0.5f, 1.0f};
+  float r[3][4];
+  for (int x = 0; x < 3; ++x) {
+    r[x][0] = g[x][0];
+    r[x][1] = (g[x][0] - g[x][1]) + g[x][2];
+    r[x][2] = (g[x][0] + g[x][1]) + g[x][2];
+    r[x][3] = g[x][2];
+  }
+  for (int j = 0; j < 4; ++j) {
+    u[0][j] = cs[j] * r[0][j];
+    u[1][j] = (cs[j] * 0.5f) * ((r[0][j] - r[1][j]) + r[2][j]);
+    u[2][j] = (cs[j] * 0.5f) * ((r[0][j] + r[1][j]) + r[2][j]);
+    u[3][j] = cs[j] * r[2][j];
+  }
+}
+/* Output (src/kernel/elk_conv_wino_2x2_3x3_output.hxx:89-97), t[hA][wA] -> y[2][2] */
+static void wino_output_tile4(float t[6][6], float y[4][4]) {
+  float c0 = (t[1][0] + t[1][1]) + t[1][2];
+  float c1 = (t[2][0] + t[2][1]) + t[2][2];
+  float c2 = (t[1][2] + t[1][3]) - t[1][1];
+  float c3 = (t[2][2] + t[2][3]) - t[2][1];
+  y[0][0] = (((t[0][0] + t[0][1]) + t[0][2]) + c0) + c1;
+  y[1][0] = (((c1 - c0) + t[3][0]) + t[3][1]) + t[3][2];
+  y[0][1] = (((t[0][2] - t[0][1]) + t[0][3]) + c2) + c3;
+  y[1][1] = (((c3 - c2) - t[3][1]) + t[3][2]) + t[3][3];
+}
+static void wino_output_tile6(float t[6][6], float y[4][4]) {
+  float m[4][6];
+  for (int j = 0; j < 6; ++j) {
+    float f[6], q[4];
+    for (int i = 0; i < 6; ++i) f[i] = t[i][j];
+    wino_at6(f, q);
+    for (int i = 0; i < 4; ++i) m[i][j] = q[i];
+  }
+  for (int i = 0; i < 4; ++i) wino_at6(m[i], y[i]);
+}
+
+/* tweights out: [A*A][OC][IC] fp32 (a = hA*A + wA).  Padded channels are zero. */
 void orc_wino_trans_weights(const orc_conv_t *p, const float *w, float *tw) {
   int IC = ALIGNUP(p->ic, V), OC = ALIGNUP(p->oc, V);
+  const int A = wino_A(p);
 #pragma omp parallel for schedule(static)
   for (int o = 0; o < OC; ++o)
     for (int i = 0; i < IC; ++i) {
@@ -326,18 +397,19 @@ void orc_wino_trans_weights(const orc_conv_t *p, const float *w, float *tw) {
       for (int kh = 0; kh < 3; ++kh)
         for (int kw = 0; kw < 3; ++kw)
           g[kh][kw] = (o < p->oc && i < p->ic) ? w[w_index(p, o, i, kh, kw)] : 0.0f;
-      wino_weights_tile(g, u);
-      for (int a = 0; a < 36; ++a) tw[((size_t)a * OC + o) * IC + i] = u[a / 6][a % 6];
+      if (A == 4) wino_weights_tile4(g, u); else wino_weights_tile(g, u);
+      for (int a = 0; a < A * A; ++a) tw[((size_t)a * OC + o) * IC + i] = u[a / A][a % A];
     }
 }
 
-/* tinput out: [36][T][IC] fp32 with T = n*ht*wt tiles, tile index t = (n*ht + th)*wt + tw.
+/* tinput out: [A*A][T][IC] fp32 with T = n*ht*wt tiles, tile index t = (n*ht + th)*wt + tw.
  * Tiles are anchored at (4*th - pad_t, 4*tw - pad_l); taps outside the image read as 0
  * (src/elx_conv_wino_trans_input.hpp:207-260).  in_is_u8: raw u8 values are converted to float
  * WITHOUT de-scaling (elk_conv_wino_4x4_3x3_input.hxx:40-47). */
 void orc_wino_trans_input(const orc_conv_t *p, const void *in, int in_is_u8, float *tin) {
   int IC = ALIGNUP(p->ic, V);
-  int ht = (p->oh + 3) / 4, wt = (p->ow + 3) / 4;
+  const int A = wino_A(p), OT = A - 2;
+  int ht = wino_ht(p), wt = wino_wt(p);
   size_t T = (size_t)p->n * ht * wt;
 #pragma omp parallel for collapse(2) schedule(static)
   for (int n = 0; n < p->n; ++n)
@@ -345,9 +417,9 @@ void orc_wino_trans_input(const orc_conv_t *p, const void *in, int in_is_u8, flo
       for (int th = 0; th < ht; ++th)
         for (int tw = 0; tw < wt; ++tw) {
           float d[6][6], v[6][6];
-          for (int h = 0; h < 6; ++h)
-            for (int w = 0; w < 6; ++w) {
-              int ih = 4 * th - p->pad_t + h, iw = 4 * tw - p->pad_l + w;
+          for (int h = 0; h < A; ++h)
+            for (int w = 0; w < A; ++w) {
+              int ih = OT * th - p->pad_t + h, iw = OT * tw - p->pad_l + w;
               float x = 0.0f;
               if (ih >= 0 && ih < p->ih && iw >= 0 && iw < p->iw && c < p->ic) {
                 size_t idx = in_index(p, n, c, ih, iw);
@@ -357,9 +429,9 @@ void orc_wino_trans_input(const orc_conv_t *p, const void *in, int in_is_u8, flo
             }
           /* is_border: first tile row/column (padding) or last (the tile overhangs the image) */
           int border = th == 0 || tw == 0 || th == ht - 1 || tw == wt - 1;
-          wino_input_tile(d, v, border);
+          if (A == 4) wino_input_tile4(d, v); else wino_input_tile(d, v, border);
           size_t t = ((size_t)n * ht + th) * wt + tw;
-          for (int a = 0; a < 36; ++a) tin[((size_t)a * T + t) * IC + c] = v[a / 6][a % 6];
+          for (int a = 0; a < A * A; ++a) tin[((size_t)a * T + t) * IC + c] = v[a / A][a % A];
         }
 }
 
@@ -367,10 +439,11 @@ void orc_wino_trans_input(const orc_conv_t *p, const void *in, int in_is_u8, flo
  * (src/kernel/elk_gemm.hxx:380-393). */
 void orc_wino_gemm_f32(const orc_conv_t *p, const float *tin, const float *tw, float *tout) {
   int IC = ALIGNUP(p->ic, V), OC = ALIGNUP(p->oc, V);
-  int ht = (p->oh + 3) / 4, wt = (p->ow + 3) / 4;
+  int ht = wino_ht(p), wt = wino_wt(p);
+  const int AA = wino_A(p) * wino_A(p);
   size_t T = (size_t)p->n * ht * wt;
 #pragma omp parallel for collapse(2) schedule(static)
-  for (int a = 0; a < 36; ++a)
+  for (int a = 0; a < AA; ++a)
     for (size_t t = 0; t < T; ++t) {
       const float *vi = tin + ((size_t)a * T + t) * IC;
       for (int o = 0; o < OC; ++o) {
@@ -388,7 +461,8 @@ void orc_wino_gemm_f32(const orc_conv_t *p, const float *tin, const float *tw, f
 void orc_wino_trans_output(const orc_conv_t *p, const float *tout, const float *bias, void *out,
                            const void *prev) {
   int OC = ALIGNUP(p->oc, V);
-  int ht = (p->oh + 3) / 4, wt = (p->ow + 3) / 4;
+  const int A = wino_A(p), OT = A - 2;
+  int ht = wino_ht(p), wt = wino_wt(p);
   size_t T = (size_t)p->n * ht * wt;
   float orepS = p->out_type == ORC_F32 ? 1.0f : 1.0f / p->out_scale;
 #pragma omp parallel for collapse(2) schedule(static)
@@ -397,21 +471,16 @@ void orc_wino_trans_output(const orc_conv_t *p, const float *tout, const float *
       for (int th = 0; th < ht; ++th)
         for (int tw = 0; tw < wt; ++tw) {
           size_t t = ((size_t)n * ht + th) * wt + tw;
-          float m[4][6];
-          for (int j = 0; j < 6; ++j) {
-            float f[6], q[4];
-            for (int i = 0; i < 6; ++i) f[i] = tout[((size_t)(i * 6 + j) * T + t) * OC + o];
-            wino_at6(f, q);
-            for (int i = 0; i < 4; ++i) m[i][j] = q[i];
-          }
-          for (int i = 0; i < 4; ++i) {
-            float y[4];
-            wino_at6(m[i], y);
-            for (int j = 0; j < 4; ++j) {
-              int oh = 4 * th + i, ow = 4 * tw + j;
+          float tt[6][6], yy[4][4];
+          for (int i = 0; i < A; ++i)
+            for (int j = 0; j < A; ++j) tt[i][j] = tout[((size_t)(i * A + j) * T + t) * OC + o];
+          if (A == 4) wino_output_tile4(tt, yy); else wino_output_tile6(tt, yy);
+          for (int i = 0; i < OT; ++i) {
+            for (int j = 0; j < OT; ++j) {
+              int oh = OT * th + i, ow = OT * tw + j;
               if (oh >= p->oh || ow >= p->ow) continue;
               size_t idx = out_index(p, n, o, oh, ow);
-              float f = y[j];
+              float f = yy[i][j];
               if (p->with_bias && bias) f += bias[o];
               if (p->out_type != ORC_F32) f = fmaf(f, orepS, p->out_z);
               if (p->with_sum && prev) {
@@ -420,7 +489,17 @@ void orc_wino_trans_output(const orc_conv_t *p, const float *tout, const float *
                                            : (float)((const int8_t *)prev)[idx];
               }
               if (p->with_relu) f = f > 0.0f ? f : 0.0f;
-              if (p->out_type == ORC_U8) {
+              if (A == 4 && p->out_type != ORC_F32) {
+                /* the F(2x2,3x3) kernel alone converts with round-toward-minus-infinity
+                 * (elk_conv_wino_2x2_3x3_output.hxx:145-153); saturation as below */
+                float rf = floorf(f);
+                if (p->out_type == ORC_U8) {
+                  uint32_t u = (rf >= 0.0f && rf < 4294967296.0f) ? (uint32_t)rf : 0xFFFFFFFFu;
+                  ((uint8_t *)out)[idx] = (uint8_t)(u > 255u ? 255u : u);
+                } else {
+                  ((int8_t *)out)[idx] = (int8_t)(rf > 127.0f ? 127.0f : rf < -128.0f ? -128.0f : rf);
+                }
+              } else if (p->out_type == ORC_U8) {
                 /* cvt_roundps_epu32 then unsigned saturation: negative -> 0 is NOT what happens:
                  * vcvtps2udq of a negative value yields 0xFFFFFFFF, which saturates to 255. */
                 float rf = rne(f);
@@ -439,11 +518,12 @@ void orc_wino_trans_output(const orc_conv_t *p, const float *tout, const float *
 int orc_wino_f32_conv(const orc_conv_t *p, const float *in, const float *w, const float *bias,
                       float *out, const float *prev) {
   int IC = ALIGNUP(p->ic, V), OC = ALIGNUP(p->oc, V);
-  int ht = (p->oh + 3) / 4, wt = (p->ow + 3) / 4;
+  int ht = wino_ht(p), wt = wino_wt(p);
+  const int AA = wino_A(p) * wino_A(p);
   size_t T = (size_t)p->n * ht * wt;
-  float *tw = (float *)malloc(sizeof(float) * 36 * OC * IC);
-  float *tin = (float *)malloc(sizeof(float) * 36 * T * IC);
-  float *tout = (float *)malloc(sizeof(float) * 36 * T * OC);
+  float *tw = (float *)malloc(sizeof(float) * AA * OC * IC);
+  float *tin = (float *)malloc(sizeof(float) * AA * T * IC);
+  float *tout = (float *)malloc(sizeof(float) * AA * T * OC);
   if (!tw || !tin || !tout) { free(tw); free(tin); free(tout); return -1; }
   orc_wino_trans_weights(p, w, tw);
   orc_wino_trans_input(p, in, 0, tin);
@@ -468,22 +548,23 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
                        void *out, const void *prev, uint8_t *dump_tin, int8_t *dump_tw,
                        int32_t *dump_acc, float *dump_tout) {
   int IC = ALIGNUP(p->ic, V), OC = ALIGNUP(p->oc, V);
-  int ht = (p->oh + 3) / 4, wt = (p->ow + 3) / 4;
+  int ht = wino_ht(p), wt = wino_wt(p);
+  const int AA = wino_A(p) * wino_A(p);
   size_t T = (size_t)p->n * ht * wt;
-  float *twf = (float *)malloc(sizeof(float) * 36 * OC * IC);
-  float *tinf = (float *)malloc(sizeof(float) * 36 * T * IC);
-  uint8_t *tin = (uint8_t *)malloc((size_t)36 * T * IC);
-  int8_t *tw = (int8_t *)malloc((size_t)36 * OC * IC);
-  float *scale = (float *)malloc(sizeof(float) * 36 * OC);
-  float *shift = (float *)malloc(sizeof(float) * 36 * OC);
-  float *tout = (float *)malloc(sizeof(float) * 36 * T * OC);
+  float *twf = (float *)malloc(sizeof(float) * AA * OC * IC);
+  float *tinf = (float *)malloc(sizeof(float) * AA * T * IC);
+  uint8_t *tin = (uint8_t *)malloc((size_t)AA * T * IC);
+  int8_t *tw = (int8_t *)malloc((size_t)AA * OC * IC);
+  float *scale = (float *)malloc(sizeof(float) * AA * OC);
+  float *shift = (float *)malloc(sizeof(float) * AA * OC);
+  float *tout = (float *)malloc(sizeof(float) * AA * T * OC);
   if (!twf || !tinf || !tin || !tw || !scale || !shift || !tout) return -1;
 
   float tz = ceilf(p->tin_z);
   float mrepS = p->in_scale * (1.0f / p->tin_scale);
 
   orc_wino_trans_weights(p, w, twf);
-  for (int a = 0; a < 36; ++a)
+  for (int a = 0; a < AA; ++a)
     for (int o = 0; o < OC; ++o) {
       const float *u = twf + ((size_t)a * OC + o) * IC;
       float m = 0.0f;
@@ -502,7 +583,7 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
 
   orc_wino_trans_input(p, in, 1, tinf);
 #pragma omp parallel for schedule(static)
-  for (size_t k = 0; k < (size_t)36 * T * IC; ++k) {
+  for (size_t k = 0; k < (size_t)AA * T * IC; ++k) {
     /* cvt_roundps_epu32 + cvtusepi32_epi8: a value that rounds below zero converts to 0xFFFFFFFF
      * and therefore saturates to 255, not to 0 (src/elx_conv_wino_trans_input.cpp:643-648) */
     float f = rne(fmaf(tinf[k], mrepS, tz));
@@ -510,7 +591,7 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
   }
 
 #pragma omp parallel for collapse(2) schedule(static)
-  for (int a = 0; a < 36; ++a)
+  for (int a = 0; a < AA; ++a)
     for (size_t t = 0; t < T; ++t) {
       const uint8_t *vi = tin + ((size_t)a * T + t) * IC;
       for (int o = 0; o < OC; ++o) {
@@ -522,9 +603,9 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
         tout[k] = fmaf((float)acc, scale[a * OC + o], shift[a * OC + o]);
       }
     }
-  if (dump_tin) memcpy(dump_tin, tin, (size_t)36 * T * IC);
-  if (dump_tw) memcpy(dump_tw, tw, (size_t)36 * OC * IC);
-  if (dump_tout) memcpy(dump_tout, tout, sizeof(float) * 36 * T * OC);
+  if (dump_tin) memcpy(dump_tin, tin, (size_t)AA * T * IC);
+  if (dump_tw) memcpy(dump_tw, tw, (size_t)AA * OC * IC);
+  if (dump_tout) memcpy(dump_tout, tout, sizeof(float) * AA * T * OC);
   orc_conv_t po = *p;
   po.out_z = ceilf(p->out_z);        /* src/elx_int8_conv_wino.cpp:276 */
   orc_wino_trans_output(&po, tout, bias, out, prev);
@@ -536,13 +617,14 @@ int orc_int8_wino_conv(const orc_conv_t *p, const uint8_t *in, const float *w, c
  * numbers the reference's test derives wino_tinput_quant from (tests/elt_conv_utils.cpp:238-255). */
 int orc_wino_tinput_range(const orc_conv_t *p, const uint8_t *in, float *mn, float *mx) {
   int IC = ALIGNUP(p->ic, V);
-  int ht = (p->oh + 3) / 4, wt = (p->ow + 3) / 4;
+  int ht = wino_ht(p), wt = wino_wt(p);
+  const int AA = wino_A(p) * wino_A(p);
   size_t T = (size_t)p->n * ht * wt;
-  float *tinf = (float *)malloc(sizeof(float) * 36 * T * IC);
+  float *tinf = (float *)malloc(sizeof(float) * AA * T * IC);
   if (!tinf) return -1;
   orc_wino_trans_input(p, in, 1, tinf);
   float lo = FLT_MAX, hi = -FLT_MAX;
-  for (size_t k = 0; k < (size_t)36 * T * IC; ++k) {
+  for (size_t k = 0; k < (size_t)AA * T * IC; ++k) {
     float v = tinf[k] * p->in_scale;
     if (v < lo) lo = v;
     if (v > hi) hi = v;

@@ -40,6 +40,12 @@ def cases():
         C("g_wino_f32_sum", 1, 16, 32, 8, 8, types="fp32", algo="wino", tile=6, bias=True, sum=True),
         C("g_wino_i8_f32", 1, 32, 32, 8, 8, types="u8f32f32f32", algo="wino", tile=6),
         C("g_wino_i8_u8", 1, 32, 16, 8, 8, types="u8f32u8f32", algo="wino", tile=6, relu=True, bias=True, oscale=2.0),
+        # F(2x2,3x3) = tile_size 4 (its u8 / s8 stores round toward minus infinity)
+        C("g_wino4_f32", 1, 32, 32, 12, 12, types="fp32", algo="wino", tile=4, relu=True, bias=True),
+        C("g_wino4_f32_partial_sum", 1, 16, 32, 9, 7, types="fp32", algo="wino", tile=4, bias=True, sum=True),
+        C("g_wino4_i8_f32", 1, 32, 32, 8, 8, types="u8f32f32f32", algo="wino", tile=4),
+        C("g_wino4_i8_u8", 1, 32, 16, 9, 8, types="u8f32u8f32", algo="wino", tile=4, relu=True, bias=True, oscale=0.05),
+        C("g_wino4_i8_s8", 1, 48, 32, 6, 6, types="u8f32s8f32", algo="wino", tile=4, bias=True, oscale=0.1),
         # int8 depthwise 3x3 (g = channels, goihw weights); flt_t is the reference's row chunk T, which
         # decides which u8 pixels are floored and which are rounded to nearest
         C("g_dw_s1_u8_t14", 1, 32, 32, 28, 28, g=32, algo="direct", knobs=dict(flt_t=14), **i8),

@@ -146,6 +146,10 @@ def baseline_case(cid: str, n: int | None = None) -> ConvCase:
     if cid == "c4":
         return ConvCase("c4_int8_wino", n or 128, 512, 512, 28, 28, types="u8f32f32f32", algo="wino",
                         tile=6, knobs=dict(xopt=0xa161, blk_i=32, blk_o=1, flt_o=2, flt_t=11, pat_o=16))
+    if cid == "c1t4":   # the c1 layer with tile_size 4 = F(2x2,3x3)
+        return dataclasses.replace(baseline_case("c1", n), name="c1t4_fp32_wino_f2x2_vgg_conv3_2", tile=4)
+    if cid == "c4t4":   # the c4 layer with tile_size 4
+        return dataclasses.replace(baseline_case("c4", n), name="c4t4_int8_wino_f2x2", tile=4)
     if cid == "dw":   # MobileNet-v1 Conv2d_3_depthwise shape; chunk T = 14 as in the reference's tuned script
         return ConvCase("dw_int8_mobilenet_conv3", n or 64, 128, 128, 56, 56, g=128, types="u8f32u8f32",
                         algo="direct", relu=True, bias=True, knobs=dict(xopt=0xc160, flt_t=14))
@@ -214,7 +218,7 @@ class OrcConv(C.Structure):
                  "stride_w", "with_relu", "with_bias", "with_sum", "out_type")] + \
                [(k, C.c_float) for k in
                 ("relu_lo", "relu_hi", "in_scale", "in_z", "out_scale", "out_z", "sum_scale", "sum_z",
-                 "tin_scale", "tin_z")] + [("fused_epilogue", C.c_int32)]
+                 "tin_scale", "tin_z")] + [("fused_epilogue", C.c_int32), ("tile", C.c_int32)]
 
 
 _ORACLE = None
@@ -240,7 +244,7 @@ def orc_params(case: ConvCase, fused: bool = True) -> OrcConv:
     return OrcConv(case.n, case.ic, case.oc, case.ih, case.iw, case.oh, case.ow, case.kh, case.kw,
                    case.pad, case.pad, case.stride, case.stride, int(case.relu), int(case.bias),
                    int(case.sum), ot, 0.0, FLT_MAX, case.iscale, case.iz, case.oscale, case.oz,
-                   case.sscale, case.sz, case.tscale or 1.0, case.tz or 0.0, int(fused))
+                   case.sscale, case.sz, case.tscale or 1.0, case.tz or 0.0, int(fused), int(case.tile))
 
 
 def _p(a):
@@ -296,8 +300,14 @@ def oracle_direct_f64(case: ConvCase, t: dict):
     return out
 
 
+def wino_edge(case: ConvCase) -> int:
+    """Input tile edge A of the case's Winograd tile_size (6 unless the case asks for 4)."""
+    return 4 if case.tile == 4 else 6
+
+
 def wino_tiles(case: ConvCase) -> int:
-    return case.n * ((case.oh + 3) // 4) * ((case.ow + 3) // 4)
+    o = wino_edge(case) - 2
+    return case.n * (-(-case.oh // o)) * (-(-case.ow // o))
 
 
 def oracle_int8_wino(case: ConvCase, t: dict, dumps: bool = False):
@@ -308,8 +318,9 @@ def oracle_int8_wino(case: ConvCase, t: dict, dumps: bool = False):
     T, IC, OC = wino_tiles(case), alignup(case.ic), alignup(case.oc)
     d = {}
     if dumps:
-        d = dict(tin=np.zeros((36, T, IC), np.uint8), tw=np.zeros((36, OC, IC), np.int8),
-                 acc=np.zeros((36, T, OC), np.int32), tout=np.zeros((36, T, OC), np.float32))
+        aa = wino_edge(case) ** 2
+        d = dict(tin=np.zeros((aa, T, IC), np.uint8), tw=np.zeros((aa, OC, IC), np.int8),
+                 acc=np.zeros((aa, T, OC), np.int32), tout=np.zeros((aa, T, OC), np.float32))
     rc = lib.orc_int8_wino_conv(C.byref(p), _p(t["input"]), _p(t["weights"]), _p(t["bias"]), _p(out), _p(prev),
                                 _p(d.get("tin")), _p(d.get("tw")), _p(d.get("acc")), _p(d.get("tout")))
     assert rc == 0

@@ -24,7 +24,7 @@ def test_oracle_matches_reference_fixture(name):
 def test_fixture_set_covers_every_path():
     names = GU.golden_names()
     assert len(names) >= 12
-    for key in ("i8_1x1", "i8_3x3_s1", "i8_3x3_s2", "wino_f32", "wino_i8", "c2_shape", "c3_shape", "sum", "dw_s1",
+    for key in ("i8_1x1", "i8_3x3_s1", "i8_3x3_s2", "wino_f32", "wino_i8", "wino4_f32", "wino4_i8", "c2_shape", "c3_shape", "sum", "dw_s1",
                 "dw_s2"):
         assert any(key in n for n in names), key
 

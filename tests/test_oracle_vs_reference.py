@@ -69,6 +69,31 @@ def test_int8_winograd_close():
     assert R.rel_l2(R.oracle_int8_wino(case, t), ref) < 2e-6
 
 
+@pytest.mark.parametrize("dims", [(2, 32, 32, 14, 14), (1, 16, 48, 13, 11), (1, 48, 16, 7, 9)])
+def test_fp32_winograd_f2x2_close(dims):
+    """tile_size 4 = F(2x2,3x3) (src/kernel/elk_conv_wino_2x2_3x3_*.hxx)."""
+    case = R.ConvCase("ovr_wino4", *dims, types="fp32", algo="wino", tile=4, relu=True, bias=True)
+    t = R.make_tensors(case)
+    ref, _ = R.run_reference(case, t)
+    assert R.rel_l2(R.oracle_wino_f32(case, t), ref) < 2e-6
+
+
+@pytest.mark.parametrize("types,kw", [("u8f32f32f32", {}), ("u8f32u8f32", dict(relu=True, bias=True, oscale=0.05)),
+                                      ("u8f32s8f32", dict(bias=True, oscale=0.1))])
+def test_int8_winograd_f2x2(types, kw):
+    """INT8 F(2x2,3x3); its u8 / s8 stores round toward minus infinity (elk_conv_wino_2x2_3x3_output.hxx:145-153)."""
+    case = R.ConvCase("ovr_i8wino4", 2, 32, 32, 12, 12, types=types, algo="wino", tile=4, **kw)
+    t = R.make_tensors(case)
+    case = R.calibrate_tinput(case, t)
+    ref, _ = R.run_reference(case, t)
+    got = R.oracle_int8_wino(case, t)
+    if types == "u8f32f32f32":
+        assert R.rel_l2(got, ref) < 2e-6
+    else:
+        d = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+        assert d.max() == 0, (d.max(), (d != 0).mean())
+
+
 DW = dict(algo="direct", bias=True)
 
 

@@ -1,5 +1,5 @@
-"""GPU parity of the Winograd F(4x4,3x3) path (fp32 with the 3xTF32 tensor-core GEMM, and int8)
-against the CPU restatement, through the C-ABI.
+"""GPU parity of the Winograd paths -- F(4x4,3x3) (tile_size 6) and F(2x2,3x3) (tile_size 4), fp32
+with the 3xTF32 tensor-core GEMM and int8 -- against the CPU restatement, through the C-ABI.
 
 fp32 tolerance: relative L2 error <= 1e-5 against the restated fp32 Winograd result (the bar the
 benchmark definition sets), and additionally against an fp64 direct convolution.
@@ -21,7 +21,8 @@ F32_TOL = 1e-5
 def _f32(name, n, ic, oc, ih, iw, **kw):
     kw.setdefault("relu", True)
     kw.setdefault("bias", True)
-    return R.ConvCase(name, n, ic, oc, ih, iw, types="fp32", algo="wino", tile=6, **kw)
+    kw.setdefault("tile", 6)
+    return R.ConvCase(name, n, ic, oc, ih, iw, types="fp32", algo="wino", **kw)
 
 
 F32_CASES = [
@@ -34,6 +35,13 @@ F32_CASES = [
     _f32("wino_oc512", 1, 64, 512, 8, 8),                       # two N tiles of 256
     _f32("wino_oc320", 1, 32, 320, 8, 8),                       # N tiles of 160
     _f32("wino_tiny", 1, 16, 16, 4, 4),
+    # F(2x2,3x3)
+    _f32("wino4_small", 2, 32, 32, 14, 14, tile=4),
+    _f32("wino4_partial_tiles", 1, 16, 48, 13, 11, tile=4),     # odd oh, ow: clipped 2x2 tiles
+    _f32("wino4_vgg_conv5", 2, 512, 512, 14, 14, tile=4),
+    _f32("wino4_sum_pad_lanes", 2, 24, 40, 9, 9, tile=4, sum=True),
+    _f32("wino4_plain_oc320", 1, 32, 320, 8, 8, tile=4, relu=False, bias=False),
+    _f32("wino4_tiny", 1, 16, 16, 2, 2, tile=4),
 ]
 
 
@@ -55,7 +63,7 @@ def test_fp32_winograd_matches_oracle(pkg, case):
             e2 = R.from_nChw16c(exact, oc)
             assert R.rel_l2(g2, e2) <= 2e-5
         # padded output channels carry bias-free zeros (relu(0 + 0))
-        if case.oc % 16:
+        if case.oc % 16 and not case.sum:
             assert np.all(R.from_nChw16c(got, R.alignup(case.oc))[:, case.oc:] == 0)
     finally:
         d.close()
@@ -73,7 +81,8 @@ def test_fp32_winograd_host_buffers_and_repeat(pkg):
 
 def _i8(name, n, ic, oc, ih, iw, **kw):
     kw.setdefault("types", "u8f32f32f32")
-    return R.ConvCase(name, n, ic, oc, ih, iw, algo="wino", tile=6, **kw)
+    kw.setdefault("tile", 6)
+    return R.ConvCase(name, n, ic, oc, ih, iw, algo="wino", **kw)
 
 
 I8_CASES = [
@@ -82,6 +91,13 @@ I8_CASES = [
     _i8("i8wino_partial", 1, 48, 16, 7, 10, relu=True, bias=True),
     _i8("i8wino_k_tail", 1, 144, 32, 8, 8),                      # 9 channel blocks: partial K stage
     _i8("i8wino_u8out", 2, 64, 64, 8, 8, types="u8f32u8f32", relu=True, bias=True, oscale=2.0),
+    # F(2x2,3x3): u8 / s8 stores round toward minus infinity
+    _i8("i8wino4_small", 2, 32, 32, 12, 12, tile=4),
+    _i8("i8wino4_partial_k_tail", 1, 144, 48, 7, 9, tile=4, relu=True, bias=True),
+    _i8("i8wino4_u8out", 2, 64, 64, 8, 8, tile=4, types="u8f32u8f32", relu=True, bias=True, oscale=0.05),
+    _i8("i8wino4_u8out_norelu_oz", 1, 32, 32, 10, 10, tile=4, types="u8f32u8f32", bias=True, oscale=0.1, oz=100.0),
+    _i8("i8wino4_s8out_sum", 1, 32, 64, 8, 8, tile=4, types="u8f32s8f32", bias=True, oscale=0.1, sum=True),
+    _i8("i8wino4_resnet_conv4", 2, 256, 256, 14, 14, tile=4, types="u8f32u8f32", relu=True, bias=True, oscale=0.05),
 ]
 
 
@@ -92,7 +108,7 @@ def test_int8_winograd_matches_oracle(pkg, case):
     case = R.calibrate_tinput(case, t)
     want, dumps = R.oracle_int8_wino(case, t, dumps=True)
     T, OCP = R.wino_tiles(case), R.alignup(case.oc)
-    got, d, acc = G.run_gpu(case, t, want_acc=True, acc_shape=(36, T, OCP))
+    got, d, acc = G.run_gpu(case, t, want_acc=True, acc_shape=(R.wino_edge(case) ** 2, T, OCP))
     try:
         assert d.kernel == "wino_i8_umma"
         assert d.device_status() == 0
@@ -104,6 +120,9 @@ def test_int8_winograd_matches_oracle(pkg, case):
             # requantised output: the fp32 output transform may differ in the last bit, which can
             # flip a rounding; allow 1 LSB on a tiny fraction
             diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
-            assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+            if case.tile == 4:      # sums only, in the reference's order: bit-exact
+                assert diff.max() == 0, f"{int((diff != 0).sum())} of {diff.size} outputs differ"
+            else:
+                assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
     finally:
         d.close()
