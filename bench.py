@@ -59,6 +59,10 @@ WORKLOADS = {
                  desc="FP32 Winograd F(2x2,3x3) (tile_size 4) VGG-16 conv3_2 N=64 C=K=256 56x56 s1 p1 bias+ReLU nChw16c"),
     "c4t4": dict(metric="effective_conv_tops_int8_winograd_f2x2", unit="TOP/s", dtype="u8",
                  desc="INT8 Winograd F(2x2,3x3) (tile_size 4) N=128 C=K=512 28x28 s1 p1 f32 out nChw16c"),
+    "c2f": dict(metric="effective_conv_tflops_fp32_direct_1x1", unit="TFLOP/s", dtype="tf32x3(fp32)",
+                desc="FP32 direct 1x1 ResNet-50 res4 reduce N=64 C=1024 K=256 14x14 bias+ReLU nChw16c"),
+    "c3f": dict(metric="effective_conv_tflops_fp32_direct", unit="TFLOP/s", dtype="tf32x3(fp32)",
+                desc="FP32 direct 3x3 stride 2 pad 1 N=64 C=128 K=256 56x56->28x28 bias+ReLU nChw16c"),
     "dw": dict(metric="effective_conv_tops_int8_depthwise", unit="TOP/s", dtype="u8",
                desc="INT8 depthwise 3x3 MobileNet-v1 Conv2d_3 N=64 C=128 56x56 s1 p1 bias+ReLU u8 out nChw16c T=14"),
     "c5": dict(metric="effective_conv_tflops_fp32_winograd_vgg16_stack", unit="TFLOP/s", dtype="tf32x3(fp32)",
@@ -212,9 +216,13 @@ def roofline_of(workload, case, d, alg_bytes, ms_step, stage_ms, peaks, peak_kin
     in_b = case.n * icp * case.ih * case.iw * (4 if case.types == "fp32" else 1)
     out_b = case.n * ocp * case.oh * case.ow * (4 if case.out_dtype.__name__ == "float32" else 1)
     aa = R.wino_edge(case) ** 2
+    names = ["wino_input_kernel", "wino_gemm_kernel", "wino_output_kernel"]
+    if d.kernel == "f32_direct_umma":
+        # implicit GEMM: one row per output pixel, K = taps * input channels, one "position"
+        names = ["f32_gather_kernel", "wino_gemm_kernel", "f32_epilogue_kernel"]
+        tiles, aa, icp = case.n * case.oh * case.ow, 1, icp * case.kh * case.kw
     v_b = aa * tiles * icp * (4 if case.types == "fp32" else 1)
     m_b = aa * tiles * ocp * 4
-    names = ["wino_input_kernel", "wino_gemm_kernel", "wino_output_kernel"]
     kernels = [{"kernel": names[0], "ms": stage_ms[0], "bytes": in_b + v_b},
                {"kernel": names[1], "ms": stage_ms[1], "bytes": v_b + m_b, "flops": 2 * aa * tiles * icp * ocp},
                {"kernel": names[2], "ms": stage_ms[2], "bytes": m_b + out_b}]
@@ -704,7 +712,7 @@ def main():
     # ---- Winograd: time each of the three kernels of a step live (events on the launching stream
     # between the kernels, over buffer sets the previous steps pushed out of L2)
     stage_ms = None
-    if case.algo == "wino":
+    if case.algo == "wino" or d.kernel == "f32_direct_umma":
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         for e in evs:
             e.record(stream)          # creates the underlying cudaEvent_t

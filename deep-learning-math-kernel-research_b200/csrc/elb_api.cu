@@ -211,8 +211,13 @@ int choose_kernel(const elb_conv_desc_t &d, int algorithm, int tile, const char 
     return ELB_KERNEL_NONE;
   }
   if (algorithm == ELB_CONV_DIRECT_1X1 || algorithm == ELB_CONV_DIRECT) {
-    if (!is_int8_user(d)) { *why = "direct convolution is implemented for u8 inputs only"; return ELB_KERNEL_NONE; }
     if (algorithm == ELB_CONV_DIRECT_1X1 && (d.kh != 1 || d.kw != 1)) { *why = "1x1 algorithm on a non-1x1 filter"; return ELB_KERNEL_NONE; }
+    if (is_fp32_user(d)) {
+      if (d.g != 1) { *why = "fp32 grouped / depthwise convolution"; return ELB_KERNEL_NONE; }
+      if (d.fmt_weights != ELB_OIHW16I16O) { *why = "weights must be OIhw16i16o"; return ELB_KERNEL_NONE; }
+      return ELB_KERNEL_F32_DIRECT_UMMA;
+    }
+    if (!is_int8_user(d)) { *why = "direct convolution is implemented for fp32 and for u8 inputs"; return ELB_KERNEL_NONE; }
     if (depthwise) {
       if (d.kh != 3 || d.kw != 3 || d.dt_output == ELB_F32) { *why = "depthwise needs 3x3 and u8/s8 output"; return ELB_KERNEL_NONE; }
       if (d.fmt_weights != ELB_GOIHW) { *why = "depthwise weights must be goihw"; return ELB_KERNEL_NONE; }
@@ -467,6 +472,7 @@ int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
     case ELB_KERNEL_I8_CONV_UMMA:
     case ELB_KERNEL_I8_SIMT: rc = prepare_i8_direct(pl, weights, bias); break;
     case ELB_KERNEL_WINO_F32_UMMA:
+    case ELB_KERNEL_F32_DIRECT_UMMA:
     case ELB_KERNEL_WINO_I8_UMMA: {
       std::string err;
       rc = wino_prepare(pl.wino, pl.d, pl.info, weights, bias, err);
@@ -500,6 +506,7 @@ int do_enqueue_range(elb_conv &pl, void *out, const void *in, int n0, int cnt, c
       return rc;
     }
     case ELB_KERNEL_WINO_F32_UMMA:
+    case ELB_KERNEL_F32_DIRECT_UMMA:
     case ELB_KERNEL_WINO_I8_UMMA: {
       std::string err;
       int nl = 0;

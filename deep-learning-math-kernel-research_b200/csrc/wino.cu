@@ -98,7 +98,9 @@ __device__ __forceinline__ void at6(const float (&f)[6], float (&p)[4]) {
 }
 
 struct WinoGeom {
-  int A;          // input tile edge: 6 = F(4x4,3x3), 4 = F(2x2,3x3); output tile edge A - 2
+  int A;          // input tile edge: 6 = F(4x4,3x3), 4 = F(2x2,3x3); output tile edge A - 2.
+                  // 1 = fp32 direct convolution: one "position", a GEMM row per output pixel
+  int KH, KW, stride, taps;   // direct convolution only
   int N, CB, OCB, IH, IW, OH, OW, ht, wt, pad_t, pad_l;
   int T;          // tiles in this chunk = images * ht * wt
   int m_tiles;    // ceil(T / 128)
@@ -432,6 +434,46 @@ __global__ void __launch_bounds__(128) wino4_input_kernel(const __grid_constant_
         *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = make_float4(v[i][j][0], v[i][j][1], v[i][j][2], v[i][j][3]);
       }
     }
+}
+
+
+// ------------------------------------------------------------------------------ fp32 direct / 1x1
+// The fp32 direct convolutions (reference: elx_conv_direct_1x1_t and elx_conv_direct_t,
+// src/elx_conv_direct_1x1.cpp, src/elx_conv_direct.cpp, kernels src/kernel/elk_gemm.hxx and
+// src/kernel/elk_conv.hxx) run as ONE implicit GEMM on the same 3xTF32 tensor-core kernel as the
+// Winograd path: rows = output pixels (n, oh, ow), K = (kh, kw, ic) in chunks of 16 channels,
+// columns = output channels.
+//   f32_gather_kernel   writes the operand image [m tile][K stage = (tap, channel block)][4 chunks]
+//                       [128 rows][4 floats]: the input pixel each row reads for that tap, zero
+//                       where the tap falls into the padding;
+//   wino_gemm_kernel    with one position;
+//   f32_epilogue_kernel result + bias (+ the stored output for the in-place sum), clamped to
+//                       relu_bound when ReLU is on (elk_gemm.hxx:230-235), written as nChw16c.
+// One thread moves the 4 channels (16 bytes) of one row.
+__global__ void __launch_bounds__(128) f32_gather_kernel(const __grid_constant__ WinoInParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * 32 + (threadIdx.x >> 2);
+  const int ks = blockIdx.y;                 // tap * CB + cb
+  if (t >= g.Tpad) return;
+  const int tap = ks / g.CB, cb = ks - tap * g.CB;
+  const int kh = tap / g.KW, kw = tap - kh * g.KW;
+  const int mt = t >> 7, row = t & 127;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (t < g.T) {
+    const int hw = g.OH * g.OW;
+    const int n = t / hw;
+    const int r = t - n * hw;
+    const int oh = r / g.OW, ow = r - oh * g.OW;
+    const int ih = oh * g.stride - g.pad_t + kh, iw = ow * g.stride - g.pad_l + kw;
+    if (ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW) {
+      const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + ih) * g.IW + iw;
+      v = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16) + quad);
+    }
+  }
+  const size_t stage = static_cast<size_t>(mt) * g.k_stages + ks;
+  float *base = static_cast<float *>(p.a_img) + stage * (A_RAW_BYTES / 4);
+  *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = v;
 }
 
 // ------------------------------------------------------------------------------ batched GEMM
@@ -815,6 +857,7 @@ struct WinoOutParams {
   WinoGeom g;
   int out_type, with_bias, with_relu, with_sum;
   float orepS, oz;
+  float relu_lo, relu_hi;   // fp32 direct convolution only (the Winograd output transform uses a literal 0)
 };
 
 __global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid_constant__ WinoOutParams p) {
@@ -1014,6 +1057,36 @@ __global__ void __launch_bounds__(128) wino4_output_kernel(const __grid_constant
     }
 }
 
+
+// fp32 direct convolution: GEMM result [OCB*4 channel quads][Tpad][4] -> nChw16c with the fused
+// epilogue.  Row t of the GEMM is output pixel (n, oh, ow) in nChw16c order.
+__global__ void __launch_bounds__(128) f32_epilogue_kernel(const __grid_constant__ WinoOutParams p) {
+  const WinoGeom &g = p.g;
+  const int quad = threadIdx.x & 3;
+  const int t = blockIdx.x * 32 + (threadIdx.x >> 2);
+  const int ocb = blockIdx.y;
+  if (t >= g.T) return;
+  const int hw = g.OH * g.OW;
+  const int n = t / hw;
+  const int r = t - n * hw;
+  float4 v = __ldg(reinterpret_cast<const float4 *>(p.m_in + ((static_cast<size_t>(ocb) * 4 + quad) * g.Tpad + t) * 4));
+  if (p.with_bias && p.bias) {
+    const float4 b = *reinterpret_cast<const float4 *>(p.bias + ocb * 16 + quad * 4);
+    v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+  }
+  float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) +
+                                           ((static_cast<size_t>(n) * g.OCB + ocb) * hw + r) * 16) + quad;
+  if (p.with_sum) {
+    const float4 pv = *dst;
+    v.x = __fadd_rn(v.x, pv.x); v.y = __fadd_rn(v.y, pv.y); v.z = __fadd_rn(v.z, pv.z); v.w = __fadd_rn(v.w, pv.w);
+  }
+  if (p.with_relu) {
+    v.x = fminf(fmaxf(v.x, p.relu_lo), p.relu_hi); v.y = fminf(fmaxf(v.y, p.relu_lo), p.relu_hi);
+    v.z = fminf(fmaxf(v.z, p.relu_lo), p.relu_hi); v.w = fminf(fmaxf(v.w, p.relu_lo), p.relu_hi);
+  }
+  *dst = v;
+}
+
 // ------------------------------------------------------------------------------ host side
 inline float tf32_rna(float x) {            // what cvt.rna.tf32.f32 returns for finite x
   uint32_t u;
@@ -1107,6 +1180,8 @@ struct WinoImpl {
   int ICP = 0, OCP = 0, BN = 0, n_tiles = 0;
   int out_type = OUT_F32, with_bias = 0, with_relu = 0, with_sum = 0;
   float orepS = 1.f, oz = 0.f, mrepS = 1.f, tz = 0.f;
+  float relu_lo = 0.f, relu_hi = 3.402823466e38f;
+  bool direct = false;     // fp32 direct convolution on the GEMM kernel (g.A == 1)
   size_t in_img_bytes = 0, out_img_bytes = 0;
   size_t a_bytes = 0, b_bytes = 0, m_bytes = 0;
   bool cta2 = false;       // GEMM on pairs of CTAs (weight rows split over the pair)
@@ -1115,10 +1190,15 @@ struct WinoImpl {
 };
 
 int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, std::string &err) {
-  if (d.pad_t != 1 || d.pad_l != 1) { err = "Winograd needs pad 1"; return ELB_UNIMPLEMENTED; }
-  if (info.tile_size != 6 && info.tile_size != 4) { err = "Winograd tile_size must be 6 or 4"; return ELB_UNIMPLEMENTED; }
+  const bool direct = info.kernel == ELB_KERNEL_F32_DIRECT_UMMA;
+  if (!direct) {
+    if (d.pad_t != 1 || d.pad_l != 1) { err = "Winograd needs pad 1"; return ELB_UNIMPLEMENTED; }
+    if (info.tile_size != 6 && info.tile_size != 4) { err = "Winograd tile_size must be 6 or 4"; return ELB_UNIMPLEMENTED; }
+  }
   WinoImpl *w = new WinoImpl();
   pl.impl = w;
+  w->direct = direct;
+  w->relu_lo = d.relu_lower; w->relu_hi = d.relu_upper;
   w->kind = info.kernel == ELB_KERNEL_WINO_I8_UMMA ? KIND_I8 : KIND_F32;
   if (w->kind == KIND_I8) {
     if (d.sampling_kind != ELB_CALIBRATED) { err = "int8 Winograd: only CALIBRATED sampling is implemented"; return ELB_UNIMPLEMENTED; }
@@ -1130,11 +1210,12 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   WinoGeom &g = w->g;
   g.CB = w->ICP / V; g.OCB = w->OCP / V;
   g.IH = d.ih; g.IW = d.iw; g.OH = d.oh; g.OW = d.ow;
-  g.A = info.tile_size;
-  const int OT = g.A - 2, AA = g.A * g.A;
-  g.ht = (d.oh + OT - 1) / OT; g.wt = (d.ow + OT - 1) / OT;
+  g.A = direct ? 1 : info.tile_size;
+  const int OT = direct ? 1 : g.A - 2, AA = g.A * g.A;
+  g.ht = (d.oh + OT - 1) / OT; g.wt = (d.ow + OT - 1) / OT;      // direct: one GEMM row per output pixel
   g.pad_t = d.pad_t; g.pad_l = d.pad_l;
-  g.k_stages = w->kind == KIND_F32 ? g.CB : (g.CB + 7) / 8;
+  g.KH = d.kh; g.KW = d.kw; g.stride = d.stride_h; g.taps = direct ? d.kh * d.kw : 1;
+  g.k_stages = w->kind == KIND_F32 ? g.CB * g.taps : (g.CB + 7) / 8;
   w->n_tiles = (w->OCP + MAX_BN - 1) / MAX_BN;
   w->BN = host::alignup((w->OCP + w->n_tiles - 1) / w->n_tiles, 16);
   // chunk of whole images whose transform-domain buffers fit the budget
@@ -1217,8 +1298,20 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
     if (!bias) { err = "bias is null but with_bias is set"; return ELB_GENERAL_ERROR; }
     W_TRY(cudaMemcpy(hb.data(), bias, static_cast<size_t>(w->OCP) * 4, cudaMemcpyDefault));
   }
-  std::vector<float> u = transform_weights(hw.data(), d.oc, d.ic, w->OCP, w->ICP, g.A);
+  std::vector<float> u;
+  if (w->direct) {
+    // U[oc][tap][ic]: K runs over (kh, kw) taps, then the input channels
+    u.assign(static_cast<size_t>(w->OCP) * g.taps * w->ICP, 0.0f);
+    for (int o = 0; o < d.oc; ++o)
+      for (int tap = 0; tap < g.taps; ++tap)
+        for (int i = 0; i < d.ic; ++i)
+          u[(static_cast<size_t>(o) * g.taps + tap) * w->ICP + i] =
+              hw[host::w_index(w->ICP / 16, d.kh, d.kw, o, i, tap / d.kw, tap % d.kw)];
+  } else {
+    u = transform_weights(hw.data(), d.oc, d.ic, w->OCP, w->ICP, g.A);
+  }
   const int BN = w->BN, KS = g.k_stages, AA = g.A * g.A;
+  const size_t KTOT = static_cast<size_t>(g.taps) * w->ICP;      // K extent of one position
   std::vector<uint8_t> img(w->b_bytes, 0);
   if (w->kind == KIND_F32) {
     // [a][nt][ks = channel block][plane][chunk j = 4 channels][BN rows][4 floats]
@@ -1229,7 +1322,7 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
           for (int r = 0; r < BN; ++r) {
             const int o = nt * BN + r;
             if (o >= w->OCP) continue;
-            const float *src = &u[(static_cast<size_t>(a) * w->OCP + o) * w->ICP + ks * 16];
+            const float *src = &u[(static_cast<size_t>(a) * w->OCP + o) * KTOT + static_cast<size_t>(ks) * 16];
             // pairs: a stage is stored as two half images of BN/2 rows, one per CTA
             const int BNH = w->cta2 ? BN / 2 : BN, hf = r / BNH, rr = r % BNH;
             float *stage = dst + ((static_cast<size_t>(a) * w->n_tiles + nt) * KS + ks) * (32 * BN) + static_cast<size_t>(hf) * 32 * BNH;
@@ -1317,7 +1410,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     dim3 gi((m_tiles_run * BM + TRANS_TILES - 1) / TRANS_TILES, g.CB);
     const bool timed = pl.stage_ev[0] != nullptr && n0 == first;
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[0], s));
-    if (g.A == 4) {
+    if (w->direct) {
+      f32_gather_kernel<<<dim3((m_tiles_run * BM + 31) / 32, g.k_stages), 128, 0, s>>>(ip);
+    } else if (g.A == 4) {
       dim3 g4((m_tiles_run * BM + 31) / 32, g.CB);
       const bool fast = 1020.0f * std::fabs(w->mrepS) + std::fabs(w->tz) < 4194304.0f;
       if (w->kind != KIND_I8) wino4_input_kernel<false, true><<<g4, 128, 0, s>>>(ip);
@@ -1375,8 +1470,10 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     op.g.Tpad = w->g.Tpad;
     op.out_type = w->out_type; op.with_bias = w->with_bias; op.with_relu = w->with_relu; op.with_sum = w->with_sum;
     op.orepS = w->orepS; op.oz = w->oz;
+    op.relu_lo = w->relu_lo; op.relu_hi = w->relu_hi;
     dim3 go((g.T + TRANS_TILES - 1) / TRANS_TILES, g.OCB);
-    if (g.A == 4) wino4_output_kernel<<<dim3((g.T + 31) / 32, g.OCB), 128, 0, s>>>(op);
+    if (w->direct) f32_epilogue_kernel<<<dim3((g.T + 31) / 32, g.OCB), 128, 0, s>>>(op);
+    else if (g.A == 4) wino4_output_kernel<<<dim3((g.T + 31) / 32, g.OCB), 128, 0, s>>>(op);
     else wino_output_kernel<<<go, TRANS_THREADS, 0, s>>>(op);
     W_TRY(cudaGetLastError());
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[3], s));

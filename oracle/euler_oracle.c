@@ -658,7 +658,13 @@ int orc_direct_f64_conv(const orc_conv_t *p, const float *in, const float *w, co
                   acc += (double)in[in_index(p, n, i, ih, iw)] * (double)w[w_index(p, o, i, kh, kw)];
               }
             }
-          if (p->with_relu && acc < 0.0) acc = 0.0;
+          /* in-place sum: the fp32 direct kernels start from the stored output instead of zero
+           * (AT_CLEAR_OUTPUT off, src/kernel/elk_gemm.hxx:330-372, src/kernel/elk_conv.hxx) */
+          if (p->with_sum) acc += (double)out[out_index(p, n, o, oh, ow)];
+          if (p->with_relu) {      /* relu_bound is honoured on this path (elk_gemm.hxx:230-235) */
+            if (acc < (double)p->relu_lo) acc = (double)p->relu_lo;
+            if (acc > (double)p->relu_hi) acc = (double)p->relu_hi;
+          }
           out[out_index(p, n, o, oh, ow)] = (float)acc;
         }
   return 0;

@@ -46,6 +46,12 @@ def cases():
         C("g_wino4_i8_f32", 1, 32, 32, 8, 8, types="u8f32f32f32", algo="wino", tile=4),
         C("g_wino4_i8_u8", 1, 32, 16, 9, 8, types="u8f32u8f32", algo="wino", tile=4, relu=True, bias=True, oscale=0.05),
         C("g_wino4_i8_s8", 1, 48, 32, 6, 6, types="u8f32s8f32", algo="wino", tile=4, bias=True, oscale=0.1),
+        # fp32 direct convolutions (1x1 and KxK); the in-place sum IS honoured on these paths
+        C("g_f32_1x1", 1, 64, 32, 7, 7, kh=1, kw=1, pad=0, types="fp32", algo="1x1", relu=True, bias=True),
+        C("g_f32_1x1_s2_sum", 1, 32, 32, 8, 8, kh=1, kw=1, pad=0, stride=2, types="fp32", algo="1x1", bias=True, sum=True),
+        C("g_f32_3x3_s2", 1, 32, 32, 14, 14, stride=2, types="fp32", algo="direct", relu=True, bias=True),
+        C("g_f32_3x3_sum", 1, 32, 16, 9, 9, types="fp32", algo="direct", relu=True, bias=True, sum=True),
+        C("g_f32_7x7_s2", 1, 32, 32, 14, 14, kh=7, kw=7, pad=3, stride=2, types="fp32", algo="direct", relu=True, bias=True),
         # int8 depthwise 3x3 (g = channels, goihw weights); flt_t is the reference's row chunk T, which
         # decides which u8 pixels are floored and which are rounded to nearest
         C("g_dw_s1_u8_t14", 1, 32, 32, 28, 28, g=32, algo="direct", knobs=dict(flt_t=14), **i8),

@@ -38,7 +38,7 @@ def check_against_golden(case, got, want):
             assert diff.max() <= 1 and (diff != 0).mean() < 5e-3, f"{int((diff != 0).sum())} outputs differ"
         else:
             assert np.array_equal(got, want), f"{int((got != want).sum())} of {got.size} outputs differ"
-    elif case.algo == "wino":
+    elif case.algo == "wino" or case.types == "fp32":
         err = R.rel_l2(got, want)
         assert err <= 1e-5, f"rel-L2 {err:.3e}"
     else:

@@ -146,6 +146,12 @@ def baseline_case(cid: str, n: int | None = None) -> ConvCase:
     if cid == "c4":
         return ConvCase("c4_int8_wino", n or 128, 512, 512, 28, 28, types="u8f32f32f32", algo="wino",
                         tile=6, knobs=dict(xopt=0xa161, blk_i=32, blk_o=1, flt_o=2, flt_t=11, pat_o=16))
+    if cid == "c2f":    # the c2 layer (ResNet-50 res4 1x1 reduce) in fp32
+        return ConvCase("c2f_fp32_1x1_resnet50_res4", n or 64, 1024, 256, 14, 14, kh=1, kw=1, pad=0, types="fp32",
+                        algo="1x1", relu=True, bias=True, knobs=dict(blk_i=64, blk_o=1, flt_o=1, flt_t=7))
+    if cid == "c3f":    # the c3 layer (3x3 stride 2) in fp32
+        return ConvCase("c3f_fp32_3x3_s2", n or 64, 128, 256, 56, 56, stride=2, types="fp32", algo="direct",
+                        relu=True, bias=True, knobs=dict(blk_i=8, blk_o=1, flt_o=1, flt_t=7))
     if cid == "c1t4":   # the c1 layer with tile_size 4 = F(2x2,3x3)
         return dataclasses.replace(baseline_case("c1", n), name="c1t4_fp32_wino_f2x2_vgg_conv3_2", tile=4)
     if cid == "c4t4":   # the c4 layer with tile_size 4
@@ -294,6 +300,8 @@ def oracle_wino_f32(case: ConvCase, t: dict):
 def oracle_direct_f64(case: ConvCase, t: dict):
     lib = oracle_lib()
     out = np.zeros(out_shape(case), dtype=np.float32)
+    if case.sum:
+        out[...] = t["residual"]      # in-place sum: the output tensor holds the residual on entry
     p = orc_params(case)
     rc = lib.orc_direct_f64_conv(C.byref(p), _p(t["input"]), _p(t["weights"]), _p(t["bias"]), _p(out))
     assert rc == 0

@@ -10,7 +10,9 @@ import refutil as R
 @pytest.mark.parametrize("name", GU.golden_names())
 def test_oracle_matches_reference_fixture(name):
     case, t, want = GU.load_golden(name)
-    if case.types == "fp32":
+    if case.types == "fp32" and case.algo != "wino":
+        got = R.oracle_direct_f64(case, t)
+    elif case.types == "fp32":
         got = R.oracle_wino_f32(case, t)
     elif case.algo == "wino":
         got = R.oracle_int8_wino(case, t)
@@ -24,7 +26,7 @@ def test_oracle_matches_reference_fixture(name):
 def test_fixture_set_covers_every_path():
     names = GU.golden_names()
     assert len(names) >= 12
-    for key in ("i8_1x1", "i8_3x3_s1", "i8_3x3_s2", "wino_f32", "wino_i8", "wino4_f32", "wino4_i8", "c2_shape", "c3_shape", "sum", "dw_s1",
+    for key in ("i8_1x1", "i8_3x3_s1", "i8_3x3_s2", "wino_f32", "wino_i8", "wino4_f32", "wino4_i8", "f32_1x1", "f32_3x3", "c2_shape", "c3_shape", "sum", "dw_s1",
                 "dw_s2"):
         assert any(key in n for n in names), key
 

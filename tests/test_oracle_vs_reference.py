@@ -94,6 +94,24 @@ def test_int8_winograd_f2x2(types, kw):
         assert d.max() == 0, (d.max(), (d != 0).mean())
 
 
+@pytest.mark.parametrize("name,kw", [
+    ("1x1", dict(kh=1, kw=1, pad=0, algo="1x1")), ("1x1_s2", dict(kh=1, kw=1, pad=0, stride=2, algo="1x1")),
+    ("3x3", dict(algo="direct")), ("3x3_s2", dict(stride=2, algo="direct")), ("3x3_p0", dict(pad=0, algo="direct")),
+    ("5x5", dict(kh=5, kw=5, pad=2, algo="direct")), ("7x7_s2", dict(kh=7, kw=7, pad=3, stride=2, algo="direct")),
+    ("1x1_sum", dict(kh=1, kw=1, pad=0, algo="1x1", sum=True)), ("3x3_sum", dict(algo="direct", sum=True)),
+    ("1x1_sum_plain", dict(kh=1, kw=1, pad=0, algo="1x1", sum=True, bias=False, relu=False)),
+])
+def test_fp32_direct_close(name, kw):
+    """fp32 1x1 / KxK direct: result, bias, in-place sum (honoured here) and ReLU order."""
+    kw = dict(kw)
+    kw.setdefault("relu", True)
+    kw.setdefault("bias", True)
+    case = _with_knobs(R.ConvCase("ovr_f32_" + name, 2, 32, 32, 14, 14, types="fp32", **kw))
+    t = R.make_tensors(case)
+    ref, _ = R.run_reference(case, t)
+    assert R.rel_l2(R.oracle_direct_f64(case, t), ref) < 2e-6
+
+
 DW = dict(algo="direct", bias=True)
 
 
