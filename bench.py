@@ -226,12 +226,17 @@ def roofline_of(workload, case, d, alg_bytes, ms_step, stage_ms, peaks, peak_kin
     kernels = [{"kernel": names[0], "ms": stage_ms[0], "bytes": in_b + v_b},
                {"kernel": names[1], "ms": stage_ms[1], "bytes": v_b + m_b, "flops": 2 * aa * tiles * icp * ocp},
                {"kernel": names[2], "ms": stage_ms[2], "bytes": m_b + out_b}]
+    if launches_per_step == 1:
+        # fp32 1x1 stride 1: the GEMM kernel alone reads the input and writes the output
+        kernels = [{"kernel": names[1], "ms": ms_step, "bytes": in_b + out_b + ocp * icp * 4,
+                    "flops": 2 * aa * tiles * icp * ocp}]
+        stage_ms = [ms_step]
     for k in kernels:
         k["gbs"] = k["bytes"] / (k["ms"] * 1e-3) / 1e9
         k["frac_hbm"] = k["gbs"] / peaks["hbm_gbs"]
-    dom = max(range(3), key=lambda i: stage_ms[i])
+    dom = max(range(len(kernels)), key=lambda i: stage_ms[i])
     k = kernels[dom]
-    if dom == 1 and case.types == "fp32":
+    if "flops" in k and case.types == "fp32":
         tf = k["flops"] / (k["ms"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops"] / 2 / 3
         rl = {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,

@@ -166,6 +166,23 @@ cudaError_t launch_reorder_to_blocked(void *dst, const void *src, int n, int c, 
 cudaError_t launch_reorder_from_blocked(void *dst, const void *src, int n, int c, int h, int w, int eb,
                                         cudaStream_t s);
 
+// cuTensorMapEncodeTiled, resolved through the runtime (no link-time dependency on libcuda)
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+inline PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_encodeTiled>(p);
+  }
+  return fn;
+}
+
 // Any reorder<T, dst, src> of the reference; supported = false when the pair is not one of them.
 cudaError_t launch_reorder(void *dst, int dst_fmt, const void *src, int src_fmt, int g, int a, int b, int h,
                            int w, int eb, cudaStream_t s, bool &supported);

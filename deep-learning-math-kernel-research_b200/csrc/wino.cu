@@ -28,6 +28,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "elb_common.cuh"
@@ -478,6 +479,9 @@ __global__ void __launch_bounds__(128) f32_gather_kernel(const __grid_constant__
 
 // ------------------------------------------------------------------------------ batched GEMM
 struct WinoGemmParams {
+  // flat mode (fp32 1x1 stride 1 without padding): 3-D map over the nChw16c input -- 16 floats of a
+  // pixel, the pixels of a plane, (image, channel block) planes -- read in boxes of 4 floats x 128 pixels
+  alignas(64) CUtensorMap tmap_a;
   const uint8_t *a_img;     // [36][m_tiles][k_stages][A_STAGE_BYTES]
   const uint8_t *b_img;     // [36][n_tiles][k_stages][128*BN bytes]
   float *m_out;             // [36][OCB*4 channel quads][Tpad][4] fp32
@@ -488,6 +492,14 @@ struct WinoGemmParams {
   long long *trace;         // optional per-CTA timeline (SM cycle counter), 64 slots per CTA (debug)
   int m_tiles, m_pitch, n_tiles, k_stages, BN, OCB, Tpad, T, kind;
   int positions;            // A*A independent GEMMs: 36 for F(4x4,3x3), 16 for F(2x2,3x3)
+  // flat mode: the whole convolution in this kernel.  Row block mt = (image, block of 128 pixels);
+  // A is fetched from the user's tensor by tiled copies, the epilogue adds bias (+ stored output),
+  // clamps and writes nChw16c.
+  int flat, HW, tiles_img, CB;
+  const float *bias;
+  float *out;
+  int with_bias, with_relu, with_sum;
+  float relu_lo, relu_hi;
 };
 // CTA2 = true: the kernel runs as clusters of two CTAs.  A pair multiplies TWO 128-tile row blocks
 // (one per CTA) by the BN transformed weights with one tcgen05.mma.cta_group::2 per K step; each
@@ -562,10 +574,45 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     // next), and the two producer warps take turns on the passes, so the whole four-stage ring is
     // being refilled at any time.
     const uint32_t pw = warp == 0 ? 0u : 1u;
-    const int grp = lane >> 1, gl = lane & 1;      // lanes 0..3 work: stage-in-pass, A / B
     uint32_t it = 0, gpass = 0;
     bool ok = true;
-    for (int tile = first; tile < total_tiles && ok; tile += step) {
+    if (p.flat) {
+      // flat mode: lanes 0..3 / 8..11 fetch the four 16-byte channel chunks of a stage (boxes of
+      // 4 floats x 128 pixels, rows past the end of the plane arrive as zeros), lanes 4 / 12 the weights
+      const int grp = lane >> 3, gl = lane & 7;
+      if (lane == 0) tma_prefetch_desc(&p.tmap_a);
+      for (int tile = first; tile < total_tiles && ok; tile += step) {
+        const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+        const int n = mt / p.tiles_img, ptile = mt - n * p.tiles_img;
+        const uint8_t *b_src = p.b_img + static_cast<size_t>(nt) * p.k_stages * b_stage_bytes;
+        for (int ks0 = 0; ks0 < p.k_stages; ks0 += 2, it += 2, ++gpass) {
+          if ((gpass & 1u) != pw) continue;
+          const int ks = ks0 + grp;
+          const bool active = lane < 16 && gl < 5 && ks < p.k_stages;
+          const uint32_t my_it = it + grp;
+          const int s = my_it % GEMM_STAGES;
+          const uint32_t ph = (my_it / GEMM_STAGES) & 1u;
+          int w_ok = 1;
+          if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
+          if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+          uint8_t *stage = smem + s * STAGE_BYTES;
+          if (active) {
+            while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
+            }
+            if (gl == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(A_RAW_BYTES) + b_stage_bytes);
+          }
+          __syncwarp();
+          if (active) {
+            if (gl < 4) tma_tile_3d(stage + gl * 2048, &p.tmap_a, 4 * gl, ptile * BM, n * p.CB + ks, &full[s]);
+            else tma_bulk_g2s(stage + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_stage_bytes, b_stage_bytes, &full[s]);
+          }
+          __syncwarp();
+        }
+        if (p.k_stages & 1) --it;
+      }
+    }
+    const int grp = lane >> 1, gl = lane & 1;      // lanes 0..3 work: stage-in-pass, A / B
+    for (int tile = first; tile < total_tiles && ok && !p.flat; tile += step) {
       const int a = tile / tiles_per_a;
       const int r = tile - a * tiles_per_a;
       const int nt = r / m_units, mu = r - nt * m_units;
@@ -762,9 +809,36 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         }
         __syncwarp();
       }
+      // flat mode: this thread's row is pixel flat_pix of image flat_n
+      const int flat_n = p.flat ? mt / p.tiles_img : 0;
+      const int flat_pix = p.flat ? (mt - flat_n * p.tiles_img) * BM + row : 0;
       auto emit = [&](int k, const uint32_t (&rr)[16]) {      // k-th 16-column block of this warp
         const int blk = half + 2 * k;
         const int ocb = nt * (BN / 16) + blk;
+        if (p.flat) {
+          if (flat_pix < p.HW && ocb < p.OCB) {
+            float4 *o = reinterpret_cast<float4 *>(p.out + ((static_cast<size_t>(flat_n) * p.OCB + ocb) * p.HW + flat_pix) * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float4 v = make_float4(__uint_as_float(rr[4 * i]), __uint_as_float(rr[4 * i + 1]),
+                                     __uint_as_float(rr[4 * i + 2]), __uint_as_float(rr[4 * i + 3]));
+              if (p.with_bias) {
+                const float4 bb = __ldg(reinterpret_cast<const float4 *>(p.bias + ocb * 16) + i);
+                v.x = __fadd_rn(v.x, bb.x); v.y = __fadd_rn(v.y, bb.y); v.z = __fadd_rn(v.z, bb.z); v.w = __fadd_rn(v.w, bb.w);
+              }
+              if (p.with_sum) {
+                const float4 pv = o[i];
+                v.x = __fadd_rn(v.x, pv.x); v.y = __fadd_rn(v.y, pv.y); v.z = __fadd_rn(v.z, pv.z); v.w = __fadd_rn(v.w, pv.w);
+              }
+              if (p.with_relu) {
+                v.x = fminf(fmaxf(v.x, p.relu_lo), p.relu_hi); v.y = fminf(fmaxf(v.y, p.relu_lo), p.relu_hi);
+                v.z = fminf(fmaxf(v.z, p.relu_lo), p.relu_hi); v.w = fminf(fmaxf(v.w, p.relu_lo), p.relu_hi);
+              }
+              o[i] = v;
+            }
+          }
+          return;
+        }
         if (live && ocb < p.OCB) {
           float f[16];
           if (p.kind == KIND_F32) {
@@ -1182,6 +1256,7 @@ struct WinoImpl {
   float orepS = 1.f, oz = 0.f, mrepS = 1.f, tz = 0.f;
   float relu_lo = 0.f, relu_hi = 3.402823466e38f;
   bool direct = false;     // fp32 direct convolution on the GEMM kernel (g.A == 1)
+  bool flat = false;       // ... 1x1 stride 1 without padding: the GEMM kernel alone, reading the user's tensor
   size_t in_img_bytes = 0, out_img_bytes = 0;
   size_t a_bytes = 0, b_bytes = 0, m_bytes = 0;
   bool cta2 = false;       // GEMM on pairs of CTAs (weight rows split over the pair)
@@ -1198,6 +1273,9 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   WinoImpl *w = new WinoImpl();
   pl.impl = w;
   w->direct = direct;
+  // 1x1, stride 1, no padding: the operand rows are the input pixels themselves
+  w->flat = direct && d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_l == 0 &&
+            d.oh == d.ih && d.ow == d.iw && !(getenv("ELB_F32_NO_FLAT") && atoi(getenv("ELB_F32_NO_FLAT")) > 0);
   w->relu_lo = d.relu_lower; w->relu_hi = d.relu_upper;
   w->kind = info.kernel == ELB_KERNEL_WINO_I8_UMMA ? KIND_I8 : KIND_F32;
   if (w->kind == KIND_I8) {
@@ -1224,7 +1302,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   const size_t per_tile = static_cast<size_t>(AA) * (static_cast<size_t>(g.k_stages) * a_gbytes / BM + static_cast<size_t>(w->OCP) * 4);
   size_t imgs = WORKSPACE_BUDGET / (per_tile * tiles_img);
   if (imgs < 1) imgs = 1;
-  if (imgs > static_cast<size_t>(d.n)) imgs = d.n;
+  if (imgs > static_cast<size_t>(d.n) || w->flat) imgs = d.n;       // flat mode needs no transform-domain buffers
   w->imgs_per_chunk = static_cast<int>(imgs);
   g.N = w->imgs_per_chunk;
   g.T = static_cast<int>(imgs * tiles_img);
@@ -1233,6 +1311,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   w->a_bytes = static_cast<size_t>(AA) * g.m_tiles * g.k_stages * a_gbytes;
   w->b_bytes = static_cast<size_t>(AA) * w->n_tiles * g.k_stages * 128 * w->BN;
   w->m_bytes = static_cast<size_t>(AA) * g.OCB * g.Tpad * 16 * 4;
+  if (w->flat) { w->a_bytes = 256; w->m_bytes = 256; }
   w->in_img_bytes = static_cast<size_t>(w->ICP) * d.ih * d.iw * (d.dt_input == ELB_F32 ? 4 : 1);
   w->out_type = d.dt_output == ELB_F32 ? OUT_F32 : d.dt_output == ELB_U8 ? OUT_U8 : OUT_S8;
   w->out_img_bytes = static_cast<size_t>(w->OCP) * d.oh * d.ow * (w->out_type == OUT_F32 ? 4 : 1);
@@ -1255,7 +1334,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
     // CTAs (VGG conv3_2 GEMM 0.417 ms either way, int8 0.152 vs 0.120 ms), because the kernel is
     // bound by the hi/lo splitter warps and the epilogue, not by the bytes of B.
     const char *on2 = getenv("ELB_WINO_CTA2");
-    w->cta2 = g.m_tiles >= 4 && w->BN % 32 == 0 && on2 && atoi(on2) > 0;
+    w->cta2 = g.m_tiles >= 4 && w->BN % 32 == 0 && on2 && atoi(on2) > 0 && !w->flat;
     if (w->cta2) {
       int dev = 0, sms = 0;
       cudaGetDevice(&dev);
@@ -1277,7 +1356,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
       w->max_clusters = n;
     }
   }
-  info.launches_per_call = 3 * ((d.n + w->imgs_per_chunk - 1) / w->imgs_per_chunk);
+  info.launches_per_call = w->flat ? 1 : 3 * ((d.n + w->imgs_per_chunk - 1) / w->imgs_per_chunk);
   return ELB_OK;
 }
 
@@ -1391,6 +1470,44 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     return ELB_GENERAL_ERROR;
   }
   if (first < 0 || count <= 0 || first + count > w->N) { err = "image range outside the batch"; return ELB_GENERAL_ERROR; }
+  if (w->flat) {
+    // the whole convolution in the GEMM kernel: A straight from the user's tensor, fused epilogue
+    const WinoGeom &g = w->g;
+    const int HW = g.OH * g.OW, tiles_img = (HW + BM - 1) / BM;
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (!enc) { err = "cuTensorMapEncodeTiled is not available from the driver"; return ELB_GENERAL_ERROR; }
+    WinoGemmParams gp{};
+    const float *src = static_cast<const float *>(in) + static_cast<size_t>(first) * (w->in_img_bytes / 4);
+    cuuint64_t dims[3] = {16, static_cast<cuuint64_t>(HW), static_cast<cuuint64_t>(count) * g.CB};
+    cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(HW) * 64};
+    cuuint32_t box[3] = {4, BM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult cr = enc(&gp.tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(src), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) { err = "cuTensorMapEncodeTiled failed (" + std::to_string(static_cast<int>(cr)) + ")"; return ELB_GENERAL_ERROR; }
+    gp.b_img = static_cast<const uint8_t *>(w->d_b);
+    gp.status = status;
+    gp.trace = static_cast<long long *>(pl.trace);
+    gp.m_tiles = count * tiles_img;
+    gp.m_pitch = gp.m_tiles;
+    gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
+    gp.OCB = g.OCB; gp.Tpad = 0; gp.T = count * HW; gp.kind = KIND_F32;
+    gp.positions = 1;
+    gp.flat = 1; gp.HW = HW; gp.tiles_img = tiles_img; gp.CB = g.CB;
+    gp.bias = static_cast<const float *>(w->d_bias);
+    gp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
+    gp.with_bias = w->with_bias; gp.with_relu = w->with_relu; gp.with_sum = w->with_sum;
+    gp.relu_lo = w->relu_lo; gp.relu_hi = w->relu_hi;
+    const bool timed = pl.stage_ev[0] != nullptr;
+    if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[0], s)); W_TRY(cudaEventRecord(pl.stage_ev[1], s)); }
+    const int total = gp.m_tiles * gp.n_tiles;
+    wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    W_TRY(cudaGetLastError());
+    if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[2], s)); W_TRY(cudaEventRecord(pl.stage_ev[3], s)); }
+    launches = 1;
+    return ELB_OK;
+  }
   for (int n0 = first; n0 < first + count; n0 += w->imgs_per_chunk) {
     WinoGeom g = w->g;
     const int imgs = std::min(w->imgs_per_chunk, first + count - n0);

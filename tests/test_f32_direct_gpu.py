@@ -79,3 +79,30 @@ def test_relu_bound_is_honoured(pkg):
     assert out.max() == 6.0 and out.min() == 0.0
     assert R.rel_l2(out, want) <= F32_TOL
     d.close()
+
+
+def test_1x1_through_the_gather_path(pkg, monkeypatch):
+    """The general three-kernel path on a shape the single-kernel 1x1 path would take."""
+    import gpuutil as G
+    monkeypatch.setenv("ELB_F32_NO_FLAT", "1")
+    case = _c("f32_1x1_gathered", 2, 96, 48, 10, 13, kh=1, kw=1, pad=0, sum=True)
+    t = R.make_tensors(case)
+    want = R.oracle_direct_f64(case, t)
+    got, d = G.run_gpu(case, t)
+    try:
+        assert d.launch_count() == 3
+        assert R.rel_l2(got, want) <= F32_TOL
+    finally:
+        d.close()
+
+
+def test_1x1_single_kernel_launch_count(pkg):
+    import gpuutil as G
+    case = CASES[0]
+    t = R.make_tensors(case)
+    got, d = G.run_gpu(case, t)
+    try:
+        assert d.launch_count() == 1
+        assert R.rel_l2(got, R.oracle_direct_f64(case, t)) <= F32_TOL
+    finally:
+        d.close()
