@@ -56,8 +56,16 @@ def test_int8_depthwise_through_euler_hpp(pkg):
     assert np.array_equal(out, R.oracle_int8_depthwise(case, t))
 
 
+def test_fp32_direct_through_euler_hpp(pkg):
+    case = R.ConvCase("dropin_f32_3x3s2", 2, 64, 32, 14, 14, stride=2, types="fp32", algo="direct", relu=True, bias=True)
+    t = R.make_tensors(case)
+    out, info = _run(case, t)
+    assert info["rc"] == 0
+    assert R.rel_l2(out, R.oracle_direct_f64(case, t)) <= 1e-5
+
+
 def test_unsupported_descriptor_returns_code_instead_of_aborting(pkg):
-    case = R.ConvCase("dropin_rej", 1, 32, 32, 8, 8, types="fp32", algo="direct")     # fp32 direct: not on this path
+    case = R.ConvCase("dropin_rej", 1, 32, 32, 8, 8, types="fp32", algo="wino", tile=7)    # F(5x5,3x3): not built
     t = R.make_tensors(case)
     if not R.DROPIN_DRIVER.exists():
         pytest.skip("driver not built")

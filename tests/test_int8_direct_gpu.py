@@ -54,9 +54,9 @@ BOX_CASES = [
 ]
 
 
-def _check(case, kernel_expected=None, host_buffers=False):
+def _check(case, kernel_expected=None, host_buffers=False, tensors=None):
     import gpuutil as G
-    t = R.make_tensors(case)
+    t = tensors if tensors is not None else R.make_tensors(case)
     want, want_acc = R.oracle_int8_conv(case, t, want_acc=True)
     got, d, acc = G.run_gpu(case, t, want_acc=True, host_buffers=host_buffers)
     try:
@@ -81,6 +81,29 @@ def test_int8_1x1_umma_matches_oracle(pkg, case):
 @pytest.mark.parametrize("case", BOX_CASES, ids=lambda c: c.name)
 def test_int8_kxk_umma_matches_oracle(pkg, case):
     _check(case, "i8_conv_umma")
+
+
+@pytest.mark.parametrize("case", [
+    _case("big_acc_1x1_f32", 2, 512, 64, 8, 8, kh=1, kw=1, pad=0, algo="1x1", types="u8f32f32f32"),
+    _case("big_acc_1x1_u8", 2, 512, 64, 8, 8, kh=1, kw=1, pad=0, algo="1x1", oscale=40.0),
+    _case("big_acc_1x1_s8_sum", 1, 512, 32, 8, 8, kh=1, kw=1, pad=0, algo="1x1", types="u8f32s8f32", relu=False,
+          oscale=300.0, sum=True, sscale=0.5),
+    _case("big_acc_3x3_u8", 1, 128, 32, 10, 10, algo="direct", oscale=60.0),
+], ids=lambda c: c.name)
+def test_accumulators_beyond_2_pow_22(pkg, case):
+    """Half of the pixels are 255 and half of the output channels have all-positive (or all-negative)
+    weights, so |accumulator| reaches 255 * 64 * K > 2^22: the epilogue's exact int -> float shortcut
+    does not apply there and the conversion instruction must take over, mixed with in-range values."""
+    t = R.make_tensors(case)
+    x = t["input"]
+    x[:, :, ::2] = 255
+    o2, i2 = R.alignup(case.oc) // 16, R.alignup(case.ic) // 16
+    w = t["weights"][:o2 * i2 * case.kh * case.kw * 256].reshape(o2, i2, case.kh, case.kw, 16, 16)   # a view: [.., 16 i][16 o]
+    w[..., 0:4] = np.abs(w[..., 0:4])
+    w[..., 4:8] = -np.abs(w[..., 4:8])
+    want, want_acc = R.oracle_int8_conv(case, t, want_acc=True)
+    assert np.abs(want_acc).max() > (1 << 22) and (np.abs(want_acc) < (1 << 22)).mean() > 0.2
+    _check(case, tensors=t)
 
 
 @pytest.mark.parametrize("case", [FLAT_CASES[1], FLAT_CASES[3], BOX_CASES[0], BOX_CASES[3]], ids=lambda c: c.name)
