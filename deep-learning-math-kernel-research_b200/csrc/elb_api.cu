@@ -332,6 +332,12 @@ int setup_i8_direct(elb_conv &pl) {
     {
       const char *norot = getenv("ELB_I8_NO_ROTATE_K");            // tuning experiments only
       p.rotate_k = (norot && atoi(norot) > 0) ? 0 : 1;
+      // Stages per producer pass: one stage per pass refills a slot as soon as it is free, which
+      // shortens short launches (1x1 benchmark layer 13.2 -> 12.7 us, 3x3 stride 2 36.2 -> 34.5 us);
+      // two per pass double the issue rate, which long persistent launches need (INT8 VGG stack
+      // 1.05 ms against 1.21 ms with one).  ELB_I8_SPP overrides (tuning experiments only).
+      const char *spp = getenv("ELB_I8_SPP");
+      p.spp = spp ? (atoi(spp) == 1 ? 1 : 2) : ((long long)p.m_tiles * p.n_tiles <= 4LL * pl.num_sms ? 1 : 2);
     }
     // Pairs of SMs (int8_conv2.cu: each CTA fetches half of the weight panel) are opt-in with
     // ELB_I8_CTA2=1: measured on B200 they are slower than the single-CTA kernel (1x1 benchmark layer

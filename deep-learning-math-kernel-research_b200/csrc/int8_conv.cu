@@ -182,10 +182,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         // tap: box_c divides CB, so a copy never straddles two taps) and lane 8 the weight panel.
         // Chunks past the end of K are not fetched: their weights are zero, whatever the slot holds.
         const int grp = lane >> 4, gl = lane & 15;
-        for (int ki0 = 0; ki0 < p.k_stages; ki0 += 2, it += 2, ++gpass) {
+        const int spp = p.spp == 1 ? 1 : 2;          // stages per pass
+        for (int ki0 = 0; ki0 < p.k_stages; ki0 += spp, it += spp, ++gpass) {
           if ((gpass & 1u) != pw) continue;          // the other producer warp's pass
           const int ki = ki0 + grp;
-          const bool active = ki < p.k_stages;
+          const bool active = grp < spp && ki < p.k_stages;
           const uint32_t my_it = it + grp;
           const int s = my_it % STAGES;
           const uint32_t ph = (my_it / STAGES) & 1u;
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           __syncwarp();
           if (gl == 0 && active && my_it < 16) ELB_TRACE(2 + my_it);
         }
-        if (p.k_stages & 1) --it;      // the last pass of an odd K loop served one stage only
+        if (spp == 2 && (p.k_stages & 1)) --it;      // the last pass of an odd K loop served one stage only
       }
     }
   } else if (warp == 1) {

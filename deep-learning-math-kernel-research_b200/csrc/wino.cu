@@ -43,6 +43,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int GEMM_STAGES_1 = 4;             // pipeline stages: one CTA per tile (16 KB A + 32 KB B each)
 constexpr int GEMM_STAGES_2 = 6;             // pairs of CTAs (16 KB A + 16 KB of B each)
+constexpr int GEMM_MAX_STAGES = 8;           // barrier slots; fp32 with A in tensor memory runs 5..8 smaller stages
 constexpr int EPI_CONST_BYTES = 16384;       // int8: per-epilogue-warp copies of the tile's scale / shift slice
 constexpr int A_STAGE_BYTES = 16384;          // in shared memory. fp32: hi + lo planes x 4 chunks x 2 KB; int8: 8 chunks x 2 KB
 constexpr int A_RAW_BYTES = 8192;             // fp32 only: one stage of V as it lies in global memory (4 chunks x 2 KB)
@@ -496,6 +497,9 @@ struct WinoGemmParams {
   // A is fetched from the user's tensor by tiled copies, the epilogue adds bias (+ stored output),
   // clamps and writes nChw16c.
   int flat, HW, tiles_img, CB;
+  int rotate_k;             // tiles start their K loop at different stages (spreads the weight reads over L2)
+  int spp;                  // pipeline stages a producer warp fills per pass (1 or 2); the two warps alternate passes
+  int a_tmem;               // fp32, single CTAs: A planes in tensor memory and ONE accumulator buffer (see the kernel)
   const float *bias;
   float *out;
   int with_bias, with_relu, with_sum;
@@ -519,10 +523,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // IN PLACE into its hi plane there and its lo plane behind it), then the epilogue constants
   uint8_t *consts_area = smem + GEMM_STAGES * STAGE_BYTES;
   uint64_t *full = reinterpret_cast<uint64_t *>(consts_area + EPI_CONST_BYTES);
-  uint64_t *empty = full + GEMM_STAGES;
-  uint64_t *cfull = empty + GEMM_STAGES;       // fp32: hi / lo planes of stage s are written
-  uint64_t *pfull = cfull + GEMM_STAGES;       // pairs, leader only: the peer's stage s is ready
-  uint64_t *tfull = pfull + GEMM_STAGES;
+  uint64_t *empty = full + GEMM_MAX_STAGES;
+  uint64_t *cfull = empty + GEMM_MAX_STAGES;       // fp32: hi / lo planes of stage s are written
+  uint64_t *pfull = cfull + GEMM_MAX_STAGES;       // pairs, leader only: the peer's stage s is ready
+  uint64_t *tfull = pfull + GEMM_MAX_STAGES;
   uint64_t *tempty = tfull + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -540,9 +544,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   const int total_tiles = p.positions * tiles_per_a;
   const int first = CTA2 ? blockIdx.x >> 1 : blockIdx.x, step = CTA2 ? gridDim.x >> 1 : gridDim.x;
   constexpr uint32_t TMEM_COLS = 512;     // two accumulator buffers of up to 256 columns
+  // fp32 on single CTAs: ONE accumulator buffer (columns 0..255) and, behind it, a ring of A-operand
+  // slots in tensor memory, one per shared-memory stage: 16 columns of tf32 hi + 16 of lo
+  constexpr uint32_t A_TMEM_COL0 = MAX_BN;
+  const bool a_in_tmem = !CTA2 && p.kind == KIND_F32 && p.a_tmem != 0;
+  // Ring geometry.  With A in tensor memory a stage holds the raw 8 KB of A and the BN weight rows
+  // only, so the ring (which may also use the area of the int8 epilogue constants) gets deeper:
+  // 5 stages at BN = 256, up to 8 (the tensor-memory slots left beside the accumulator) below.
+  const int stage_bytes = a_in_tmem ? A_RAW_BYTES + 128 * BN : STAGE_BYTES;
+  const int b_off = a_in_tmem ? A_RAW_BYTES : A_STAGE_BYTES;
+  const int nstages = a_in_tmem ? min(GEMM_MAX_STAGES, (GEMM_STAGES * STAGE_BYTES + EPI_CONST_BYTES) / stage_bytes) : GEMM_STAGES;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < GEMM_STAGES; ++s) {
+    for (int s = 0; s < GEMM_MAX_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       mbar_init(&cfull[s], GEMM_CONV_WARPS);
@@ -574,6 +588,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     // next), and the two producer warps take turns on the passes, so the whole four-stage ring is
     // being refilled at any time.
     const uint32_t pw = warp == 0 ? 0u : 1u;
+    const int spp = p.spp == 1 ? 1 : 2;
     uint32_t it = 0, gpass = 0;
     bool ok = true;
     if (p.flat) {
@@ -585,17 +600,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
         const int n = mt / p.tiles_img, ptile = mt - n * p.tiles_img;
         const uint8_t *b_src = p.b_img + static_cast<size_t>(nt) * p.k_stages * b_stage_bytes;
-        for (int ks0 = 0; ks0 < p.k_stages; ks0 += 2, it += 2, ++gpass) {
+        // CTAs that run side by side multiply by the same weights: each tile starts its K loop at a
+        // different stage so that they do not all ask the same L2 lines at the same moment
+        const int rot = p.rotate_k ? tile % p.k_stages : 0;
+        for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass) {
           if ((gpass & 1u) != pw) continue;
           const int ks = ks0 + grp;
-          const bool active = lane < 16 && gl < 5 && ks < p.k_stages;
+          const int ksr = ks + rot < p.k_stages ? ks + rot : ks + rot - p.k_stages;     // rotated K stage
+          const bool active = grp < spp && gl < 5 && ks < p.k_stages;
           const uint32_t my_it = it + grp;
-          const int s = my_it % GEMM_STAGES;
-          const uint32_t ph = (my_it / GEMM_STAGES) & 1u;
+          const int s = my_it % nstages;
+          const uint32_t ph = (my_it / nstages) & 1u;
           int w_ok = 1;
           if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
           if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
-          uint8_t *stage = smem + s * STAGE_BYTES;
+          uint8_t *stage = smem + s * stage_bytes;
           if (active) {
             while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
             }
@@ -603,12 +622,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           }
           __syncwarp();
           if (active) {
-            if (gl < 4) tma_tile_3d(stage + gl * 2048, &p.tmap_a, 4 * gl, ptile * BM, n * p.CB + ks, &full[s]);
-            else tma_bulk_g2s(stage + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_stage_bytes, b_stage_bytes, &full[s]);
+            if (gl < 4) tma_tile_3d(stage + gl * 2048, &p.tmap_a, 4 * gl, ptile * BM, n * p.CB + ksr, &full[s]);
+            else tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_stage_bytes, b_stage_bytes, &full[s]);
           }
           __syncwarp();
         }
-        if (p.k_stages & 1) --it;
+        if (spp == 2 && (p.k_stages & 1)) --it;
       }
     }
     const int grp = lane >> 1, gl = lane & 1;      // lanes 0..3 work: stage-in-pass, A / B
@@ -625,20 +644,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * (CTA2 ? 2 : 1) * b_stage_bytes +
                              (CTA2 ? rank * b_stage_bytes : 0);
       const size_t b_pitch = static_cast<size_t>(CTA2 ? 2 : 1) * b_stage_bytes;
+      const int rot = p.rotate_k ? tile % p.k_stages : 0;      // see the flat-mode loop above
       if (pw == 0 && lane == 0 && it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
-      for (int ks0 = 0; ks0 < p.k_stages; ks0 += 2, it += 2, ++gpass) {
+      for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass) {
         if ((gpass & 1u) != pw) continue;            // the other producer warp's pass
         const int ks = ks0 + grp;
-        const bool active = lane < 4 && ks < p.k_stages;
+        const int ksr = ks + rot < p.k_stages ? ks + rot : ks + rot - p.k_stages;
+        const bool active = grp < spp && ks < p.k_stages;
         const uint32_t my_it = it + grp;
-        const int s = my_it % GEMM_STAGES;
-        const uint32_t ph = (my_it / GEMM_STAGES) & 1u;
+        const int s = my_it % nstages;
+        const uint32_t ph = (my_it / nstages) & 1u;
         // empty[s] is committed by the MMAs of the stage's previous use, which also implies that the
         // splitter warps are done with raw slot s
         int w_ok = 1;
         if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
         if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
-        uint8_t *stage = smem + s * STAGE_BYTES;
+        uint8_t *stage = smem + s * stage_bytes;
         if (active) {
           while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
           }        // every issuing lane observes the completed phase itself
@@ -648,14 +669,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         if (active) {
           if (gl == 0) {
             if (live)
-              tma_bulk_g2s(stage, a_src + static_cast<size_t>(ks) * a_gbytes, a_gbytes, &full[s]);
+              tma_bulk_g2s(stage, a_src + static_cast<size_t>(ksr) * a_gbytes, a_gbytes, &full[s]);
           } else {
-            tma_bulk_g2s(stage + A_STAGE_BYTES, b_src + static_cast<size_t>(ks) * b_pitch, b_stage_bytes, &full[s]);
+            tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_pitch, b_stage_bytes, &full[s]);
           }
         }
         __syncwarp();
       }
-      if (p.k_stages & 1) --it;        // the last pass of an odd K loop served one stage only
+      if (spp == 2 && (p.k_stages & 1)) --it;        // the last pass of an odd K loop served one stage only
     }
   } else if (warp == 1) {
     // -------- MMA issuer (pairs: in the leader CTA only; the peer's lane forwards stage readiness)
@@ -664,8 +685,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       bool ok = true;
       for (int tile = first; tile < total_tiles && ok; tile += step) {
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = it % GEMM_STAGES;
-          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          const int s = it % nstages;
+          const uint32_t ph = (it / nstages) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag) ||
               (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag))) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           mbar_arrive_cluster(mapa_u32(&pfull[s], 0));
@@ -678,21 +699,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       uint32_t it = 0, tcount = 0;
       bool ok = true;
       for (int tile = first; tile < total_tiles && ok; tile += step, ++tcount) {
-        const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
+        const uint32_t b = a_in_tmem ? 0u : (tcount & 1u), tph = a_in_tmem ? (tcount & 1u) : ((tcount >> 1) & 1u);
         if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
         tc_fence_after_sync();
         if (tcount < 8) WG_TRACE(8 + tcount);
         const uint32_t d_tmem = tmem_base + b * MAX_BN;
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = it % GEMM_STAGES;
-          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          const int s = it % nstages;
+          const uint32_t ph = (it / nstages) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (CTA2 && !mbar_wait(&pfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           tc_fence_after_sync();
           if (ks == 0 && tcount < 8) WG_TRACE(16 + tcount);
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+          const uint32_t a_addr = smem_u32(smem + s * stage_bytes);
+          const uint32_t b_addr = a_addr + b_off;
           if (p.kind == KIND_F32) {
             // planes: A hi at +0, lo at +8 KB; B hi at +0, lo at +4 chunks.  K step = 2 chunks.
 #pragma unroll
@@ -701,7 +722,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
               const uint64_t alo = umma_desc_kmajor(a_addr + 8192 + k2 * 4096, 2048, 128);
               const uint64_t bhi = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
               const uint64_t blo = umma_desc_kmajor(b_addr + 4 * b_lbo + k2 * 2 * b_lbo, b_lbo, 128);
-              if (CTA2) {
+              if (a_in_tmem) {
+                // A planes in tensor memory: hi at columns [0,16) of the stage's slot, lo at [16,32)
+                const uint32_t t_hi = tmem_base + A_TMEM_COL0 + s * 32 + k2 * 8, t_lo = t_hi + 16;
+                umma_tf32_ts(d_tmem, t_lo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
+                umma_tf32_ts(d_tmem, t_hi, blo, idesc, 1u);
+                umma_tf32_ts(d_tmem, t_hi, bhi, idesc, 1u);
+              } else if (CTA2) {
                 umma_tf32_2cta(d_tmem, alo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
                 umma_tf32_2cta(d_tmem, ahi, blo, idesc, 1u);
                 umma_tf32_2cta(d_tmem, ahi, bhi, idesc, 1u);
@@ -742,11 +769,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       for (int tile = first; tile < total_tiles && ok; tile += step) {
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           if (static_cast<int>(it % GEMM_CONV_GROUPS) != cgrp) continue;       // the other group's stage
-          const int s = it % GEMM_STAGES;
-          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          const int s = it % nstages;
+          const uint32_t ph = (it / nstages) & 1u;
           if (!mbar_wait_warp(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (tid_c == 0 && it < 8) WG_TRACE(48 + 2 * it);
-          float4 *hi = reinterpret_cast<float4 *>(smem + s * STAGE_BYTES);     // holds the raw fp32 values on arrival
+          if (a_in_tmem) {
+            // single CTAs: the planes go to TENSOR memory, row r of the stage = lane r, so the MMAs
+            // read A without touching shared memory (three MMAs per K step re-reading A and B from
+            // shared memory, next to the incoming copies, saturated its port).  Warp w may only
+            // address lanes 32*(w%4)..: the four splitter warps cover the four quarters.
+            const int quarter = warp & 3, srow = quarter * 32 + lane;
+            const float4 *raw4 = reinterpret_cast<const float4 *>(smem + s * stage_bytes);
+            uint32_t h[16], l[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 v = raw4[j * BM + srow];
+              const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t hb;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[c]));
+                h[4 * j + c] = hb;
+                l[4 * j + c] = __float_as_uint(__fsub_rn(x[c], __uint_as_float(hb)));
+              }
+            }
+            const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + A_TMEM_COL0 + s * 32;
+            tmem_st16(t_slot, h);
+            tmem_st16(t_slot + 16, l);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&cfull[s]);
+            if (tid_c == 0 && it < 8) WG_TRACE(49 + 2 * it);
+            continue;
+          }
+          float4 *hi = reinterpret_cast<float4 *>(smem + s * stage_bytes);     // holds the raw fp32 values on arrival
           const float4 *raw = hi;
           float4 *lo = hi + A_RAW_BYTES / 16;
 #pragma unroll
@@ -786,7 +843,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const int nt = r / m_units, mu = r - nt * m_units;
       const int mt = CTA2 ? 2 * mu + static_cast<int>(rank) : mu;
       const bool live = mt < p.m_tiles;
-      const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
+      const uint32_t b = a_in_tmem ? 0u : (tcount & 1u), tph = a_in_tmem ? (tcount & 1u) : ((tcount >> 1) & 1u);
       const int t = mt * BM + row;
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
       tc_fence_after_sync();
@@ -917,8 +974,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   }
 }
 
-constexpr int GEMM_SMEM_BYTES_1 = GEMM_STAGES_1 * (A_STAGE_BYTES + B_STAGE_MAX) + EPI_CONST_BYTES + (4 * GEMM_STAGES_1 + 4) * 8 + 16 + 128;
-constexpr int GEMM_SMEM_BYTES_2 = GEMM_STAGES_2 * (A_STAGE_BYTES + B_STAGE_MAX / 2) + EPI_CONST_BYTES + (4 * GEMM_STAGES_2 + 4) * 8 + 16 + 128;
+constexpr int GEMM_SMEM_BYTES_1 = GEMM_STAGES_1 * (A_STAGE_BYTES + B_STAGE_MAX) + EPI_CONST_BYTES + (4 * GEMM_MAX_STAGES + 4) * 8 + 16 + 128;
+constexpr int GEMM_SMEM_BYTES_2 = GEMM_STAGES_2 * (A_STAGE_BYTES + B_STAGE_MAX / 2) + EPI_CONST_BYTES + (4 * GEMM_MAX_STAGES + 4) * 8 + 16 + 128;
 constexpr int GEMM_SMEM_BYTES = GEMM_SMEM_BYTES_1 > GEMM_SMEM_BYTES_2 ? GEMM_SMEM_BYTES_1 : GEMM_SMEM_BYTES_2;
 static_assert(GEMM_SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 static_assert(GEMM_EPI_WARPS * 2 * MAX_BN * 4 <= EPI_CONST_BYTES, "epilogue constants must fit their area");
@@ -1245,6 +1302,32 @@ std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, in
   return u;
 }
 
+// Tuning switches of the GEMM kernel (environment overrides are for experiments only).
+// fp32: A in tensor memory costs the second accumulator buffer (the epilogue no longer overlaps the
+// next tile's MMAs) but relieves the shared-memory port and deepens the ring.  Measured on B200,
+// per layer of the VGG-16 stack (32 images): it loses where the K loop is short and the epilogue
+// therefore weighs most (64 / 128 input channels: 1.29 -> 1.52 ms, 0.42 -> 0.49 ms), is even at 128
+// channels x 8 stages, and wins from 256 input channels up (conv4_2 0.308 -> 0.283 ms, conv5_x
+// 0.108 -> 0.097 ms) and whenever a CTA runs a single tile (1x1 benchmark layer 68.9 -> 55.9 us).
+inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms) {
+  if (const char *e = getenv("ELB_F32_A_TMEM")) return atoi(e) > 0 ? 1 : 0;
+  return kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms) ? 1 : 0;
+}
+// K rotation spreads the weight reads of CTAs running side by side over L2; measured without effect
+// on this kernel (the weights of one position are 0.5 MB and stay hot), so it is off.
+inline int tune_rotate_k() {
+  if (const char *e = getenv("ELB_WINO_ROTATE_K")) return atoi(e) > 0 ? 1 : 0;
+  return 0;
+}
+// Stages per producer pass.  One stage per pass refills a slot as soon as it is free (a pass of two
+// waits for both); two per pass doubles the issue rate.  fp32 needs a stage every ~800 cycles at
+// best and gains from the shorter wait on every layer of the VGG-16 stack (conv3_2 0.368 -> 0.351 ms),
+// int8 Winograd does not care.
+inline int tune_spp(int kind) {
+  if (const char *e = getenv("ELB_WINO_SPP")) return atoi(e) == 1 ? 1 : 2;
+  return kind == KIND_F32 ? 1 : 2;
+}
+
 }  // namespace
 
 struct WinoImpl {
@@ -1495,6 +1578,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.OCB = g.OCB; gp.Tpad = 0; gp.T = count * HW; gp.kind = KIND_F32;
     gp.positions = 1;
     gp.flat = 1; gp.HW = HW; gp.tiles_img = tiles_img; gp.CB = g.CB;
+    gp.spp = tune_spp(KIND_F32);
+    gp.rotate_k = tune_rotate_k();
+    gp.a_tmem = tune_a_tmem(KIND_F32, gp.k_stages, static_cast<long long>(gp.m_tiles) * gp.n_tiles, num_sms);
     gp.bias = static_cast<const float *>(w->d_bias);
     gp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
     gp.with_bias = w->with_bias; gp.with_relu = w->with_relu; gp.with_sum = w->with_sum;
@@ -1559,6 +1645,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
     gp.OCB = g.OCB; gp.Tpad = w->g.Tpad; gp.T = g.T; gp.kind = w->kind;
     gp.positions = g.A * g.A;
+    gp.spp = tune_spp(w->kind);
+    gp.rotate_k = tune_rotate_k();
+    gp.a_tmem = tune_a_tmem(w->kind, gp.k_stages, static_cast<long long>(gp.positions) * gp.m_tiles * gp.n_tiles, num_sms);
     if (w->cta2) {
       const int pairs = gp.positions * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
       cudaLaunchConfig_t cfg{};
@@ -1787,7 +1876,9 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   gp.m_tiles = g.m_tiles; gp.m_pitch = g.m_tiles; gp.n_tiles = n_tiles; gp.k_stages = g.k_stages; gp.BN = BN;
   gp.OCB = g.OCB; gp.Tpad = g.Tpad; gp.T = g.T; gp.kind = KIND_F32;
   gp.positions = 36;
+  gp.spp = 1;
   const int total = 36 * gp.m_tiles * gp.n_tiles;
+  gp.a_tmem = (gp.k_stages >= 16 || total <= num_sms) ? 1 : 0;
   wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
   WinoOutParams op{};
   op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;
