@@ -332,12 +332,21 @@ int setup_i8_direct(elb_conv &pl) {
     {
       const char *norot = getenv("ELB_I8_NO_ROTATE_K");            // tuning experiments only
       p.rotate_k = (norot && atoi(norot) > 0) ? 0 : 1;
-      // Stages per producer pass: one stage per pass refills a slot as soon as it is free, which
-      // shortens short launches (1x1 benchmark layer 13.2 -> 12.7 us, 3x3 stride 2 36.2 -> 34.5 us);
-      // two per pass double the issue rate, which long persistent launches need (INT8 VGG stack
-      // 1.05 ms against 1.21 ms with one).  ELB_I8_SPP overrides (tuning experiments only).
-      const char *spp = getenv("ELB_I8_SPP");
-      p.spp = spp ? (atoi(spp) == 1 ? 1 : 2) : ((long long)p.m_tiles * p.n_tiles <= 4LL * pl.num_sms ? 1 : 2);
+      // Producer warps and stages per pass.  A copy instruction occupies its warp for hundreds of
+      // cycles, so the issue rate is set by how many warps issue and how many stages each serves per
+      // pass; one stage per pass refills a slot as soon as it is free (a pass of two waits for both).
+      // Measured on B200: short launches are fastest with 2 warps x 1 stage (1x1 benchmark layer
+      // 13.2 -> 12.7 us, 3x3 stride 2 36.2 -> 34.5 us); long K loops (16 stages and more) of 128 or
+      // 256 output channels with 4 warps x 1 stage (VGG conv4_2 0.091 -> 0.080 ms, conv3_2 0.081 ->
+      // 0.074 ms); long launches of short K loops with 2 warps x 2 stages.  warps x stages must not
+      // exceed the ring depth: a warp further ahead could not tell its slot's phase by parity.
+      // ELB_I8_SPP / ELB_I8_NPROD override (tuning experiments only).
+      const bool short_launch = (long long)p.m_tiles * p.n_tiles <= 4LL * pl.num_sms;
+      p.nprod = (pl.i8cfg.BN >= 128 && p.k_stages >= 16) ? 4 : 2;
+      p.spp = (p.nprod == 4 || short_launch) ? 1 : 2;
+      if (const char *e = getenv("ELB_I8_NPROD")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) p.nprod = v; }
+      if (const char *e = getenv("ELB_I8_SPP")) p.spp = atoi(e) == 1 ? 1 : 2;
+      while (p.nprod * p.spp > pl.i8cfg.STAGES) { if (p.spp > 1) p.spp = 1; else p.nprod /= 2; }
     }
     // Pairs of SMs (int8_conv2.cu: each CTA fetches half of the weight panel) are opt-in with
     // ELB_I8_CTA2=1: measured on B200 they are slower than the single-CTA kernel (1x1 benchmark layer

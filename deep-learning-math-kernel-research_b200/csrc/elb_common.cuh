@@ -138,6 +138,7 @@ struct I8ConvParams {
   int BW, BH, tiles_w, tiles_h;      // BOX mode tile = BH x BW output pixels (BH*BW = 128)
   int merged_rows;                   // BOX mode, stride 1: 4-D tensor map over 8-byte elements
   int spp;                           // BOX mode: pipeline stages a producer warp fills per pass (1 or 2)
+  int nprod;                         // BOX mode: producer warps taking turns on the passes (1, 2 or 4)
   int rotate_k;                      // tiles start their K loop at different stages (spreads the weight reads over L2)
 };
 

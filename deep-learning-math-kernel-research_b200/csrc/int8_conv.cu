@@ -44,7 +44,8 @@ constexpr int BM = 128;
 // two int<->float conversions per output, not by the number of warps.)
 constexpr int NUM_EPI_WARPS = I8_EPI_WARPS;
 constexpr int EPI_PER_QUARTER = NUM_EPI_WARPS / 4;
-constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32 + 32;    // + a second producer warp (the last warp)
+constexpr int MAX_PRODUCERS = 4;                                                // warp 0 and the last three warps
+constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32 + 32 * (MAX_PRODUCERS - 1);
 constexpr int PRODUCER2_WARP = 2 + NUM_EPI_WARPS;
 constexpr int MAX_OC_SMEM = 2048;    // per-channel constants cached in shared memory
 
@@ -118,13 +119,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   if (threadIdx.x == 0) ELB_TRACE(1);
   int fail_code = 0;
 
-  if (warp == 0 || (warp == PRODUCER2_WARP && MODE == I8_MODE_BOX)) {
+  if (warp == 0 || warp >= PRODUCER2_WARP) {
     // ------------------------------------------------------------------ producer(s)
     // BOX mode runs two producer warps that take turns on the passes (two stages each) of the K
     // loop, so that four stages are being issued at any time; see the comment in the loop.
-    const uint32_t pw = warp == 0 ? 0u : 1u;
+    const uint32_t pw = warp == 0 ? 0u : static_cast<uint32_t>(warp - PRODUCER2_WARP + 1);
+    const uint32_t nprod = MODE == I8_MODE_BOX ? static_cast<uint32_t>(p.nprod) : 1u;      // 1, 2 or 4 warps take turns
     uint32_t it = 0, gpass = 0;
-    bool ok = true;
+    bool ok = pw < nprod;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
       // tile geometry
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         const int grp = lane >> 4, gl = lane & 15;
         const int spp = p.spp == 1 ? 1 : 2;          // stages per pass
         for (int ki0 = 0; ki0 < p.k_stages; ki0 += spp, it += spp, ++gpass) {
-          if ((gpass & 1u) != pw) continue;          // the other producer warp's pass
+          if ((gpass & (nprod - 1u)) != pw) continue;          // another producer warp's pass
           const int ki = ki0 + grp;
           const bool active = grp < spp && ki < p.k_stages;
           const uint32_t my_it = it + grp;
@@ -466,10 +468,10 @@ I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
     if (v == 64 || v == 128 || v == 256) c.BN = v;
   }
   c.KC = 8;
-  c.STAGES = c.BN == 256 ? 4 : 6;
+  c.STAGES = c.BN == 256 ? 4 : c.BN == 128 ? 6 : 8;     // as many as shared memory holds: the ring is latency-bound
   (void)cb; (void)taps;
   c.smem_bytes = c.BN == 256 ? SmemLayout<256, 8, 4>::TOTAL
-               : c.BN == 128 ? SmemLayout<128, 8, 6>::TOTAL : SmemLayout<64, 8, 6>::TOTAL;
+               : c.BN == 128 ? SmemLayout<128, 8, 6>::TOTAL : SmemLayout<64, 8, 8>::TOTAL;
   return c;
 }
 
@@ -478,11 +480,11 @@ static cudaError_t dispatch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &c
   if (cfg.mode == I8_MODE_FLAT) {
     if (cfg.BN == 256) return launch_cfg<256, 8, 4, I8_MODE_FLAT>(p, num_sms, s, attr_only);
     if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);
-    return launch_cfg<64, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);
+    return launch_cfg<64, 8, 8, I8_MODE_FLAT>(p, num_sms, s, attr_only);
   }
   if (cfg.BN == 256) return launch_cfg<256, 8, 4, I8_MODE_BOX>(p, num_sms, s, attr_only);
   if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_BOX>(p, num_sms, s, attr_only);
-  return launch_cfg<64, 8, 6, I8_MODE_BOX>(p, num_sms, s, attr_only);
+  return launch_cfg<64, 8, 8, I8_MODE_BOX>(p, num_sms, s, attr_only);
 }
 
 cudaError_t init_i8_umma(const I8UmmaConfig &cfg) {
