@@ -183,11 +183,12 @@ def cpu_reference_run(case, t, steps, warmup, budget_s=12.0):
 # DRAM bytes (read + written) of ONE launch of each workload's dominant kernel, from the ncu
 # captures summarised under profiles/ (launch lists of the full-size workloads).
 NCU_TRAFFIC = {
-    "c1": {"wino_input_kernel": 205.6e6 + 404.6e6, "wino_gemm_kernel": 481.4e6 + 410.6e6,
+    "c1": {"wino_input_kernel": 205.6e6 + 404.6e6, "wino_gemm_kernel": 481.5e6 + 411.2e6,
            "wino_output_kernel": 462.5e6 + 174.2e6},
     "c2": {"i8_gemm_umma": 13.15e6},
     "c3": {"i8_conv_umma": 26.03e6},
     "c3s": {"i8_conv_umma": 38.88e6},
+    "c2f": {"wino_gemm_kernel": 53.5e6},
     "dw": {"i8_depthwise": 25.71e6 + 0.01e6},
     "c4": {"wino_input_kernel": 51.4e6 + 57.0e6, "wino_gemm_kernel": 114.8e6 + 357.9e6,
            "wino_output_kernel": 462.5e6 + 175.3e6},
