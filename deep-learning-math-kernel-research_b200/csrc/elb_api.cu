@@ -138,10 +138,17 @@ struct elb_conv {
   WinoPlan wino{};
   // int8 depthwise
   DwPlan dw{};
+  // Plain user formats (nchw / nhwc activations, oihw / hwio weights): the kernels work on the
+  // blocked formats, `d` / `info` describe that internal problem and `ud` / `uinfo` what the caller
+  // passes; activations are converted on the device around every call, weights once.
+  elb_conv_desc_t ud{};
+  elb_conv_info_t uinfo{};
+  bool cvt_in = false, cvt_out = false, cvt_w = false;
+  void *d_cvt_in = nullptr, *d_cvt_out = nullptr;
 
   ~elb_conv() {
     cudaSetDevice(device);
-    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, (void *)d_status, d_in_stage, d_out_stage})
+    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, (void *)d_status, d_in_stage, d_out_stage, d_cvt_in, d_cvt_out})
       if (p) cudaFree(p);
     wino_release(wino);
     dw_release(dw);
@@ -164,6 +171,28 @@ struct DeviceGuard {
   }
   ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
+
+// format_undef defaults of the reference (src/eld_conv.cpp:77-86)
+void resolve_formats(elb_conv_desc_t &d) {
+  if (d.fmt_input == ELB_FMT_UNDEF) d.fmt_input = (d.g == 1 && d.ic < V) ? ELB_NCHW : ELB_NCHW16C;
+  if (d.fmt_weights == ELB_FMT_UNDEF) d.fmt_weights = d.g == 1 ? ELB_HWIO : ELB_GHWIO;
+  if (d.fmt_output == ELB_FMT_UNDEF) d.fmt_output = ELB_NCHW16C;
+}
+
+// The problem the kernels see: plain activation / weight formats replaced by the blocked ones.
+// ghwio depthwise weights ([g][kh][kw][1][1]) are goihw ([g][1][1][kh][kw]) byte for byte.
+elb_conv_desc_t internal_desc(const elb_conv_desc_t &u, bool &cvt_in, bool &cvt_out, bool &cvt_w) {
+  elb_conv_desc_t d = u;
+  const bool depthwise = u.g > 1 && u.g == u.ic && u.g == u.oc;
+  cvt_in = u.fmt_input == ELB_NCHW || u.fmt_input == ELB_NHWC;
+  cvt_out = u.fmt_output == ELB_NCHW || u.fmt_output == ELB_NHWC;
+  cvt_w = !depthwise && (u.fmt_weights == ELB_OIHW || u.fmt_weights == ELB_HWIO);
+  if (cvt_in) d.fmt_input = ELB_NCHW16C;
+  if (cvt_out) d.fmt_output = ELB_NCHW16C;
+  if (cvt_w) d.fmt_weights = ELB_OIHW16I16O;
+  if (depthwise && u.fmt_weights == ELB_GHWIO) d.fmt_weights = ELB_GOIHW;
+  return d;
+}
 
 int validate_common(const elb_conv_desc_t &d) {
   if (d.n <= 0 || d.g <= 0 || d.ic <= 0 || d.oc <= 0 || d.ih <= 0 || d.iw <= 0 || d.oh <= 0 || d.ow <= 0 ||
@@ -461,7 +490,7 @@ bool is_device_ptr(const void *p) {
   return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
-int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
+int do_prepare_inner(elb_conv &pl, const void *weights, const void *bias) {
   if (pl.prepared) return ELB_OK;
   if (!weights) return fail(ELB_GENERAL_ERROR, "weights are null");
   int rc;
@@ -489,8 +518,43 @@ int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
   return rc;
 }
 
+// Weights / bias in the caller's formats -> what the kernels' one-time preparation reads: plain
+// weights (oihw, hwio) are converted to OIhw16i16o on the device, a bias of oc elements (plain
+// output formats, src/eld_conv.cpp:112-114) is zero-padded to a multiple of 16.
+int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
+  if (pl.prepared) return ELB_OK;
+  if (!weights) return fail(ELB_GENERAL_ERROR, "weights are null");
+  const bool pad_bias = pl.d.with_bias && bias && pl.uinfo.size_bias != pl.info.size_bias;
+  if (!pl.cvt_w && !pad_bias) return do_prepare_inner(pl, weights, bias);
+  void *w_src = nullptr, *w_blk = nullptr, *b_pad = nullptr;
+  int rc = ELB_OK;
+  auto cleanup = [&]() { for (void *q : {w_src, w_blk, b_pad}) if (q) cudaFree(q); };
+  if (pl.cvt_w) {
+    bool sup = false;
+    if (cudaMalloc(&w_src, pl.uinfo.bytes_weights) != cudaSuccess || cudaMalloc(&w_blk, pl.info.bytes_weights) != cudaSuccess ||
+        cudaMemcpy(w_src, weights, pl.uinfo.bytes_weights, cudaMemcpyDefault) != cudaSuccess ||
+        cudaMemset(w_blk, 0, pl.info.bytes_weights) != cudaSuccess ||
+        launch_reorder(w_blk, ELB_OIHW16I16O, w_src, pl.ud.fmt_weights, 1, pl.d.oc, pl.d.ic, pl.d.kh, pl.d.kw, 4, nullptr, sup) != cudaSuccess ||
+        !sup || cudaDeviceSynchronize() != cudaSuccess) {
+      cleanup();
+      return fail(ELB_GENERAL_ERROR, "weight format conversion failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+  }
+  if (pad_bias) {
+    if (cudaMalloc(&b_pad, pl.info.bytes_bias) != cudaSuccess || cudaMemset(b_pad, 0, pl.info.bytes_bias) != cudaSuccess ||
+        cudaMemcpy(b_pad, bias, pl.uinfo.bytes_bias, cudaMemcpyDefault) != cudaSuccess) {
+      cleanup();
+      return fail(ELB_GENERAL_ERROR, "bias padding failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+  }
+  rc = do_prepare_inner(pl, pl.cvt_w ? w_blk : weights, pad_bias ? b_pad : bias);
+  cudaDeviceSynchronize();
+  cleanup();
+  return rc;
+}
+
 // Enqueue images [n0, n0 + cnt) of the batch on stream s; `out` / `in` address the full tensors.
-int do_enqueue_range(elb_conv &pl, void *out, const void *in, int n0, int cnt, cudaStream_t s) {
+int do_enqueue_range_inner(elb_conv &pl, void *out, const void *in, int n0, int cnt, cudaStream_t s) {
   switch (pl.info.kernel) {
     case ELB_KERNEL_I8_GEMM_UMMA:
     case ELB_KERNEL_I8_CONV_UMMA:
@@ -516,6 +580,39 @@ int do_enqueue_range(elb_conv &pl, void *out, const void *in, int n0, int cnt, c
     }
     default: return fail(ELB_UNIMPLEMENTED, "no kernel");
   }
+}
+
+// The same in the caller's formats: plain activations (nchw / nhwc) are converted to nChw16c
+// before the kernels and the result back after them, image range by image range, on the same
+// stream (the residual of an in-place sum travels with the output tensor).
+int do_enqueue_range(elb_conv &pl, void *out, const void *in, int n0, int cnt, cudaStream_t s) {
+  if (!pl.cvt_in && !pl.cvt_out) return do_enqueue_range_inner(pl, out, in, n0, cnt, s);
+  const elb_conv_desc_t &d = pl.d;
+  const int N = d.n, ebi = (int)dt_size(d.dt_input), ebo = (int)dt_size(d.dt_output);
+  const size_t u_in = pl.uinfo.bytes_input / N, b_in = pl.info.bytes_input / N;
+  const size_t u_out = pl.uinfo.bytes_output / N, b_out = pl.info.bytes_output / N;
+  bool sup = false;
+  cudaError_t e = cudaSuccess;
+  if (pl.cvt_in) {
+    e = launch_reorder((uint8_t *)pl.d_cvt_in + n0 * b_in, ELB_NCHW16C, (const uint8_t *)in + n0 * u_in, pl.ud.fmt_input, 1, cnt,
+                       d.ic, d.ih, d.iw, ebi, s, sup);
+    ++pl.launches;
+  }
+  if (e == cudaSuccess && pl.cvt_out && d.with_ip_sum) {
+    e = launch_reorder((uint8_t *)pl.d_cvt_out + n0 * b_out, ELB_NCHW16C, (const uint8_t *)out + n0 * u_out, pl.ud.fmt_output, 1,
+                       cnt, d.oc, d.oh, d.ow, ebo, s, sup);
+    ++pl.launches;
+  }
+  if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "format conversion launch failed: %s", cudaGetErrorString(e));
+  int rc = do_enqueue_range_inner(pl, pl.cvt_out ? pl.d_cvt_out : out, pl.cvt_in ? pl.d_cvt_in : in, n0, cnt, s);
+  if (rc != ELB_OK) return rc;
+  if (pl.cvt_out) {
+    e = launch_reorder((uint8_t *)out + n0 * u_out, pl.ud.fmt_output, (const uint8_t *)pl.d_cvt_out + n0 * b_out, ELB_NCHW16C, 1, cnt,
+                       d.oc, d.oh, d.ow, ebo, s, sup);
+    ++pl.launches;
+    if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, "format conversion launch failed: %s", cudaGetErrorString(e));
+  }
+  return ELB_OK;
 }
 
 int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
@@ -549,10 +646,13 @@ int elb_conv_sizes(const elb_conv_desc_t *desc, elb_conv_info_t *info) {
   int rc = validate_common(*desc);
   if (rc != ELB_OK) return rc;
   memset(info, 0, sizeof(*info));
-  compute_sizes(*desc, *info);
+  elb_conv_desc_t ud = *desc;
+  resolve_formats(ud);
+  compute_sizes(ud, *info);
   resolve_algorithm(*desc, info->algorithm, info->tile_size);
   const char *why;
-  info->kernel = choose_kernel(*desc, info->algorithm, info->tile_size, &why);
+  bool ci, co, cw;
+  info->kernel = choose_kernel(internal_desc(ud, ci, co, cw), info->algorithm, info->tile_size, &why);
   info->device = desc->device;
   return ELB_OK;
 }
@@ -562,18 +662,23 @@ int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
   *plan = nullptr;
   int rc = validate_common(*desc);
   if (rc != ELB_OK) return rc;
-  elb_conv_desc_t d = *desc;
+  bool cvt_in = false, cvt_out = false, cvt_w = false;
+  elb_conv_desc_t ud = *desc;
+  resolve_formats(ud);
   // bottom/right padding follow from the output size, as the reference does with a warning
   // (src/eld_conv.cpp:128-139, src/elx_conv.cpp:36-37)
   {
-    const int need_b = (d.oh - 1) * d.stride_h + d.kh - d.ih - d.pad_t;
-    const int need_r = (d.ow - 1) * d.stride_w + d.kw - d.iw - d.pad_l;
-    d.pad_b = need_b > 0 ? need_b : 0;
-    d.pad_r = need_r > 0 ? need_r : 0;
+    const int need_b = (ud.oh - 1) * ud.stride_h + ud.kh - ud.ih - ud.pad_t;
+    const int need_r = (ud.ow - 1) * ud.stride_w + ud.kw - ud.iw - ud.pad_l;
+    ud.pad_b = need_b > 0 ? need_b : 0;
+    ud.pad_r = need_r > 0 ? need_r : 0;
   }
-  elb_conv_info_t info;
+  elb_conv_desc_t d = internal_desc(ud, cvt_in, cvt_out, cvt_w);
+  elb_conv_info_t info, uinfo;
   memset(&info, 0, sizeof(info));
+  memset(&uinfo, 0, sizeof(uinfo));
   compute_sizes(d, info);
+  compute_sizes(ud, uinfo);
   // algorithm choice uses the caller's pads, like the reference
   resolve_algorithm(*desc, info.algorithm, info.tile_size);
   const char *why;
@@ -591,6 +696,8 @@ int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
   elb_conv *pl = new elb_conv();
   pl->d = d;
   pl->info = info;
+  pl->ud = ud;
+  pl->cvt_in = cvt_in; pl->cvt_out = cvt_out; pl->cvt_w = cvt_w;
   pl->device = dev;
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { delete pl; return fail(ELB_GENERAL_ERROR, "device query failed"); }
@@ -618,13 +725,23 @@ int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
     }
   }
   if (rc != ELB_OK) { delete pl; return rc; }
+  // what the caller sees: the sizes of ITS formats, everything else from the internal plan
+  uinfo.algorithm = pl->info.algorithm; uinfo.tile_size = pl->info.tile_size; uinfo.kernel = pl->info.kernel;
+  uinfo.device = pl->info.device; uinfo.launches_per_call = pl->info.launches_per_call + (cvt_in ? 1 : 0) + (cvt_out ? 1 : 0);
+  pl->uinfo = uinfo;
+  if ((cvt_in && cudaMalloc(&pl->d_cvt_in, pl->info.bytes_input) != cudaSuccess) ||
+      (cvt_out && cudaMalloc(&pl->d_cvt_out, pl->info.bytes_output) != cudaSuccess)) {
+    delete pl;
+    return fail(ELB_GENERAL_ERROR, "device allocation failed");
+  }
   *plan = pl;
   return ELB_OK;
 }
 
 int elb_conv_info(const elb_conv_t *plan, elb_conv_info_t *info) {
   if (!plan || !info) return fail(ELB_GENERAL_ERROR, "null argument");
-  *info = plan->info;
+  *info = plan->uinfo;
+  info->workspace_bytes = plan->info.workspace_bytes;
   return ELB_OK;
 }
 
@@ -661,16 +778,16 @@ int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const vo
   // copy of chunk k-1 run at the same time on three streams (the two copy directions use different
   // copy engines), so a call costs about the longer of the two transfers instead of their sum.
   const int N = pl.d.n;
-  const size_t in_img = pl.info.bytes_input / N, out_img = pl.info.bytes_output / N;
-  if (!in_dev && !pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.info.bytes_input));
-  if (!out_dev && !pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.info.bytes_output));
+  const size_t in_img = pl.uinfo.bytes_input / N, out_img = pl.uinfo.bytes_output / N;
+  if (!in_dev && !pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.uinfo.bytes_input));
+  if (!out_dev && !pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.uinfo.bytes_output));
   if (!pl.s_h2d) {
     CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_h2d, cudaStreamNonBlocking));
     CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_d2h, cudaStreamNonBlocking));
   }
   int chunks = 1;
   {
-    const size_t moved = (in_dev ? 0 : pl.info.bytes_input) + (out_dev ? 0 : pl.info.bytes_output);
+    const size_t moved = (in_dev ? 0 : pl.uinfo.bytes_input) + (out_dev ? 0 : pl.uinfo.bytes_output);
     const size_t target = size_t(4) << 20;                       // at least ~4 MB of transfers per chunk
     chunks = (int)std::min<size_t>(8, std::max<size_t>(1, moved / target));
     if (chunks > N) chunks = N;

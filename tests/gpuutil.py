@@ -25,6 +25,13 @@ def make_desc(case: ConvCase, device: int = -1):
                  "u8f32f32f32": (E.u8, E.f32)}[case.types]
     d.data_type.input, d.data_type.weights, d.data_type.output, d.data_type.bias = tin, E.f32, tout, E.f32
     d.formats.weights = E.goihw if case.g > 1 else E.OIhw16i16o
+    fmts = {"nchw": E.nchw, "nhwc": E.nhwc, "oihw": E.oihw, "hwio": E.hwio, "ghwio": E.ghwio}
+    if case.ifmt:
+        d.formats.input = fmts[case.ifmt]
+    if case.ofmt:
+        d.formats.output = fmts[case.ofmt]
+    if case.wfmt:
+        d.formats.weights = fmts[case.wfmt]
     d.algorithm = {"auto": E.CONV_AUTO, "direct": E.CONV_DIRECT, "1x1": E.CONV_DIRECT_1X1,
                    "wino": E.CONV_WINOGRAD}[case.algo]
     d.tile_size = case.tile

@@ -95,6 +95,9 @@ class ConvCase:
     tscale: float | None = None
     tz: float | None = None
     knobs: dict = dataclasses.field(default_factory=dict)   # reference tuning knobs (xopt, blk_i ...)
+    ifmt: str = ""                 # "" = nChw16c; "nchw" | "nhwc": plain user formats
+    ofmt: str = ""
+    wfmt: str = ""                 # "" = OIhw16i16o (goihw for depthwise); "oihw" | "hwio" | "ghwio"
 
     @property
     def oh(self) -> int:
@@ -258,7 +261,43 @@ def _p(a):
 
 
 def out_shape(case: ConvCase):
+    """Shape of the output tensor as the caller holds it (blocked unless the case names a plain format)."""
+    if case.ofmt == "nchw":
+        return (case.n, case.oc, case.oh, case.ow)
+    if case.ofmt == "nhwc":
+        return (case.n, case.oh, case.ow, case.oc)
     return (case.n, alignup(case.oc) // V, case.oh, case.ow, V)
+
+
+def act_to_user(x_blocked: np.ndarray, c: int, fmt: str) -> np.ndarray:
+    """nChw16c -> the plain activation format fmt ("" keeps it blocked)."""
+    if not fmt:
+        return x_blocked
+    x = from_nChw16c(x_blocked, c)
+    return np.ascontiguousarray(x if fmt == "nchw" else x.transpose(0, 2, 3, 1))
+
+
+def act_to_blocked(x_user: np.ndarray, fmt: str) -> np.ndarray:
+    if not fmt:
+        return x_user
+    x = x_user if fmt == "nchw" else x_user.transpose(0, 3, 1, 2)
+    return to_nChw16c(np.ascontiguousarray(x))
+
+
+def user_tensors(case: ConvCase, t: dict) -> dict:
+    """The tensors of make_tensors (blocked layouts) in the formats the case names: what a caller with
+    plain tensors passes.  Bias has oc elements when the output format is plain (src/eld_conv.cpp:112-114)."""
+    u = dict(t)
+    u["input"] = act_to_user(t["input"], case.ic, case.ifmt)
+    if case.sum:
+        u["residual"] = act_to_user(t["residual"], case.oc, case.ofmt)
+    if case.ofmt:
+        u["bias"] = np.ascontiguousarray(t["bias"][:case.oc])
+    if case.wfmt in ("oihw", "hwio"):
+        w = t["weights_plain"]                                   # [oc][ic][kh][kw]
+        w = w if case.wfmt == "oihw" else w.transpose(2, 3, 1, 0)
+        u["weights"] = weights_buffer(np.ascontiguousarray(w))
+    return u
 
 
 def oracle_int8_conv(case: ConvCase, t: dict, fused: bool = True, want_acc: bool = False):
@@ -375,7 +414,13 @@ def reference_args(case: ConvCase, knobs: bool = True) -> list:
         if case.tscale is not None:
             a += [f"tscale={case.tscale!r}", f"tz={case.tz!r}"]
     if case.g > 1:
-        a += ["wfmt=goihw"]
+        a += [f"wfmt={case.wfmt or 'goihw'}"]
+    elif case.wfmt:
+        a += [f"wfmt={case.wfmt}"]
+    if case.ifmt:
+        a += [f"ifmt={case.ifmt}"]
+    if case.ofmt:
+        a += [f"ofmt={case.ofmt}"]
     if knobs:
         for k, v in case.knobs.items():
             a.append(f"{k}={hex(v) if k == 'xopt' else v}")

@@ -112,6 +112,29 @@ def test_fp32_direct_close(name, kw):
     assert R.rel_l2(R.oracle_direct_f64(case, t), ref) < 2e-6
 
 
+@pytest.mark.parametrize("case", [
+    R.ConvCase("ovr_fmt_1x1_nhwc", 2, 64, 32, 8, 8, kh=1, kw=1, pad=0, types="u8f32u8f32", algo="1x1", relu=True, bias=True,
+               ifmt="nhwc", ofmt="nhwc"),      # (the reference's int8 classes abort on hwio / oihw weights)
+    R.ConvCase("ovr_fmt_3x3_nhwc", 1, 32, 32, 10, 10, types="u8f32u8f32", algo="direct", relu=True, bias=True,
+               ifmt="nhwc", ofmt="nhwc"),
+    R.ConvCase("ovr_fmt_wino_f32_nchw_in", 1, 32, 32, 12, 12, types="fp32", algo="wino", tile=6, relu=True, bias=True,
+               ifmt="nchw", wfmt="oihw"),
+], ids=lambda c: c.name)
+def test_plain_formats_are_the_same_convolution(case):
+    """The reference run on nhwc / nchw / hwio / oihw tensors gives the blocked result in another layout."""
+    blocked = dataclasses.replace(case, ifmt="", ofmt="", wfmt="")
+    t = R.make_tensors(blocked)
+    if case.types != "fp32":
+        case, blocked = _with_knobs(case), _with_knobs(blocked)
+    ref, _ = R.run_reference(case, R.user_tensors(case, t))
+    if case.types == "fp32":
+        want = R.act_to_user(R.oracle_wino_f32(blocked, t), case.oc, case.ofmt)
+        assert R.rel_l2(R.from_nChw16c(ref, case.oc), R.from_nChw16c(want, case.oc)) < 2e-6
+    else:
+        want = R.act_to_user(R.oracle_int8_conv(blocked, t), case.oc, case.ofmt)
+        assert np.array_equal(ref, want)
+
+
 DW = dict(algo="direct", bias=True)
 
 
