@@ -114,6 +114,10 @@ eld_conv_t::~eld_conv_t() {
 int eld_conv_t::setup(bool fully_setup) {
   // a stale plan is dropped (the reference overwrites xc and leaks it, src/eld_conv.cpp:141)
   if (xc != nullptr) { elb_conv_destroy(plan_of(*this)); xc = nullptr; }
+  // undefined formats get the reference's defaults, visibly, in the descriptor (src/eld_conv.cpp:77-86)
+  if (formats.input == format_undef) formats.input = (dims.g == 1 && dims.ic / dims.g < 16) ? nchw : nChw16c;
+  if (formats.weights == format_undef) formats.weights = dims.g == 1 ? hwio : ghwio;
+  if (formats.output == format_undef) formats.output = nChw16c;
   elb_conv_desc_t d;
   to_c_desc(*this, d);
   elb_conv_info_t info;

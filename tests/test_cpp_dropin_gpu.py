@@ -64,6 +64,18 @@ def test_fp32_direct_through_euler_hpp(pkg):
     assert R.rel_l2(out, R.oracle_direct_f64(case, t)) <= 1e-5
 
 
+def test_nhwc_tensors_through_euler_hpp(pkg):
+    """nhwc activations and hwio weights, the layout the reference's tuned INT8 ResNet scripts run."""
+    case = R.ConvCase("dropin_nhwc", 2, 64, 48, 14, 14, kh=1, kw=1, pad=0, types="u8f32u8f32", algo="1x1", relu=True,
+                      bias=True, ifmt="nhwc", ofmt="nhwc", wfmt="hwio")
+    blocked = dataclasses.replace(case, ifmt="", ofmt="", wfmt="")
+    t = R.make_tensors(blocked)
+    out, info = _run(case, R.user_tensors(case, t))
+    assert info["rc"] == 0
+    assert info["bytes"]["input"] == 2 * 14 * 14 * 64 and info["bytes"]["bias"] == 48 * 4
+    assert np.array_equal(out, R.act_to_user(R.oracle_int8_conv(blocked, t), case.oc, "nhwc"))
+
+
 def test_unsupported_descriptor_returns_code_instead_of_aborting(pkg):
     case = R.ConvCase("dropin_rej", 1, 32, 32, 8, 8, types="fp32", algo="wino", tile=7)    # F(5x5,3x3): not built
     t = R.make_tensors(case)
