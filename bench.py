@@ -59,6 +59,8 @@ WORKLOADS = {
                  desc="FP32 Winograd F(2x2,3x3) (tile_size 4) VGG-16 conv3_2 N=64 C=K=256 56x56 s1 p1 bias+ReLU nChw16c"),
     "c4t4": dict(metric="effective_conv_tops_int8_winograd_f2x2", unit="TOP/s", dtype="u8",
                  desc="INT8 Winograd F(2x2,3x3) (tile_size 4) N=128 C=K=512 28x28 s1 p1 f32 out nChw16c"),
+    "v12": dict(metric="effective_conv_tflops_fp32_winograd", unit="TFLOP/s", dtype="tf32x3(fp32)",
+                desc="FP32 Winograd F(4x4,3x3) VGG-16 conv1_2 N=32 C=K=64 224x224 s1 p1 bias+ReLU nChw16c"),
     "c2f": dict(metric="effective_conv_tflops_fp32_direct_1x1", unit="TFLOP/s", dtype="tf32x3(fp32)",
                 desc="FP32 direct 1x1 ResNet-50 res4 reduce N=64 C=1024 K=256 14x14 bias+ReLU nChw16c"),
     "c3f": dict(metric="effective_conv_tflops_fp32_direct", unit="TFLOP/s", dtype="tf32x3(fp32)",

@@ -548,12 +548,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // slots in tensor memory, one per shared-memory stage: 16 columns of tf32 hi + 16 of lo
   constexpr uint32_t A_TMEM_COL0 = MAX_BN;
   const bool a_in_tmem = !CTA2 && p.kind == KIND_F32 && p.a_tmem != 0;
-  // Ring geometry.  With A in tensor memory a stage holds the raw 8 KB of A and the BN weight rows
-  // only, so the ring (which may also use the area of the int8 epilogue constants) gets deeper:
-  // 5 stages at BN = 256, up to 8 (the tensor-memory slots left beside the accumulator) below.
-  const int stage_bytes = a_in_tmem ? A_RAW_BYTES + 128 * BN : STAGE_BYTES;
+  // Ring geometry.  A stage holds A (16 KB of hi / lo planes or int8 chunks; only the raw 8 KB when
+  // the planes go to tensor memory) and the BN weight rows, so tiles of fewer output channels get a
+  // deeper ring: 4 stages at BN = 256 (5 with A in tensor memory), 6 at 128, up to 8 below.
+  // (Measured: the extra depth changes nothing on the 64- and 128-channel VGG layers, whose stages
+  // land about 1400 cycles apart however many are in flight.)
+  const int stage_bytes = a_in_tmem ? A_RAW_BYTES + 128 * BN : CTA2 ? STAGE_BYTES : A_STAGE_BYTES + 128 * BN;
   const int b_off = a_in_tmem ? A_RAW_BYTES : A_STAGE_BYTES;
-  const int nstages = a_in_tmem ? min(GEMM_MAX_STAGES, (GEMM_STAGES * STAGE_BYTES + EPI_CONST_BYTES) / stage_bytes) : GEMM_STAGES;
+  // the ring may also use the area of the int8 epilogue constants when the kernel runs fp32
+  const int ring_bytes = GEMM_STAGES * STAGE_BYTES + (p.kind == KIND_F32 ? EPI_CONST_BYTES : 0);
+  const int nstages = CTA2 ? GEMM_STAGES : min(GEMM_MAX_STAGES, ring_bytes / stage_bytes);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_MAX_STAGES; ++s) {

@@ -149,6 +149,9 @@ def baseline_case(cid: str, n: int | None = None) -> ConvCase:
     if cid == "c4":
         return ConvCase("c4_int8_wino", n or 128, 512, 512, 28, 28, types="u8f32f32f32", algo="wino",
                         tile=6, knobs=dict(xopt=0xa161, blk_i=32, blk_o=1, flt_o=2, flt_t=11, pat_o=16))
+    if cid == "v12":    # VGG-16 conv1_2, the slowest layer of the fp32 stack (64 -> 64 channels at 224x224)
+        return ConvCase("v12_fp32_wino_vgg_conv1_2", n or 32, 64, 64, 224, 224, types="fp32", algo="wino", tile=6,
+                        relu=True, bias=True, knobs=dict(xopt=0xa061, blk_i=4, blk_o=4, flt_t=28, pat_o=1))
     if cid == "c2f":    # the c2 layer (ResNet-50 res4 1x1 reduce) in fp32
         return ConvCase("c2f_fp32_1x1_resnet50_res4", n or 64, 1024, 256, 14, 14, kh=1, kw=1, pad=0, types="fp32",
                         algo="1x1", relu=True, bias=True, knobs=dict(blk_i=64, blk_o=1, flt_o=1, flt_t=7))
