@@ -112,6 +112,12 @@ __device__ __forceinline__ void tma_bulk_g2s(void *smem_dst, const void *gmem_sr
                ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// Ask L2 to fetch `bytes` (a multiple of 16) from global memory; nothing is written to shared
+// memory and nothing has to be waited for.  A bulk copy issued later then finds its data in L2.
+__device__ __forceinline__ void tma_prefetch_l2(const void *gmem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 // Tiled tensor copies (descriptor from cuTensorMapEncodeTiled).  Coordinate 0 is the innermost
 // dimension and coordinate0 * element_size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_tile_3d(void *smem_dst, const void *tmap, int c0, int c1, int c2,
