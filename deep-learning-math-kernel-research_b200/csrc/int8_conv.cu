@@ -177,9 +177,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           if (lane == 0 && it < 16) ELB_TRACE(2 + it);
         }
       } else {
-        // BOX mode.  Issuing a copy occupies the issuing warp for about a thousand cycles whatever
-        // its size, but the lanes of ONE instruction issue their copies together.  So the warp works
-        // on TWO pipeline stages per pass: lanes 0..15 serve one stage, lanes 16..31 the next; in
+        // BOX mode.  Issuing a copy costs its lane a few hundred cycles, copies issued by different
+        // lanes of one instruction overlap and different warps issue independently.  A pass serves
+        // p.spp pipeline stages: lanes 0..15 one stage, lanes 16..31 (spp = 2) the next; in
         // each group lanes 0..7 fetch the pixels (one tiled copy per box_c channel blocks of one
         // tap: box_c divides CB, so a copy never straddles two taps) and lane 8 the weight panel.
         // Chunks past the end of K are not fetched: their weights are zero, whatever the slot holds.

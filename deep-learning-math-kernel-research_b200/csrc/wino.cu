@@ -590,11 +590,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   int fail_code = 0;
 
   if (warp == 0 || warp == GEMM_PRODUCER2_WARP) {
-    // -------- producers: two contiguous bulk copies per stage.  Issuing a copy occupies the issuing
-    // warp for about a thousand cycles whatever its size, but the lanes of one instruction issue
-    // together: each pass serves TWO stages (lanes 0/1: A and B of one stage, lanes 2/3: of the
-    // next), and the two producer warps take turns on the passes, so the whole four-stage ring is
-    // being refilled at any time.
+    // -------- producers: two contiguous bulk copies per stage.  Issuing a copy costs its lane a few
+    // hundred cycles; lanes of one instruction overlap and warps issue independently.  A pass serves
+    // p.spp stages (lanes 0/1: A and B of one stage, lanes 2/3: of the next when spp = 2), and the
+    // two producer warps take turns on the passes.
     const uint32_t pw = warp == 0 ? 0u : 1u;
     const int spp = p.spp == 1 ? 1 : 2;
     uint32_t it = 0, gpass = 0;
