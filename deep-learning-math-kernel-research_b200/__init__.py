@@ -21,10 +21,6 @@ PKG_DIR = Path(__file__).resolve().parent
 ROOT = PKG_DIR.parent
 LIB_PATH = PKG_DIR / "lib" / "libeuler_b200.so"
 HOST_LIB_PATH = PKG_DIR / "lib" / "libel.so"
-CSRC = PKG_DIR / "csrc"
-CU_SOURCES = ["elb_api.cu", "int8_conv.cu", "int8_conv2.cu", "wino.cu", "depthwise.cu", "misc.cu"]
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
 
 # ----------------------------------------------------------------------------- constants
 ELB_OK, ELB_UNIMPLEMENTED, ELB_GENERAL_ERROR = 0, 1, 2
@@ -42,32 +38,9 @@ KERNEL_NAMES = {0: "none", 1: "i8_gemm_umma", 2: "i8_conv_umma", 3: "i8_simt", 4
 
 
 def build(verbose: bool = False) -> Path:
-    """Compile csrc/*.cu for sm_100a into lib/libeuler_b200.so (nvcc cross-compiles without a GPU)
-    and the C++ host library lib/libel.so, which exports the reference's own C++ symbols
-    (eld_conv_t, elx_conv, reorder<>) on top of it."""
-    LIB_PATH.parent.mkdir(exist_ok=True)
-    srcs = [str(CSRC / s) for s in CU_SOURCES]
-    deps = list(CSRC.glob("*")) + [ROOT / "include" / "euler_b200.h"]
-    if not LIB_PATH.exists() or any(p.stat().st_mtime > LIB_PATH.stat().st_mtime for p in deps):
-        cmd = ["nvcc"] + NVCC_FLAGS + ["-o", str(LIB_PATH)] + srcs
-        if verbose:
-            print(" ".join(cmd))
-        subprocess.check_call(cmd)
-    # The C++ host library defines the reference's own exported symbols and is therefore compiled
-    # with the reference's public headers; where that tree is absent the prebuilt library is kept.
-    host_src = PKG_DIR / "host" / "euler_host.cpp"
-    ref_inc = Path(os.environ.get("EULER_REFERENCE_INCLUDE", "/root/reference/include"))
-    hdeps = [host_src, LIB_PATH, ROOT / "include" / "euler_b200.h"]
-    if (ref_inc / "euler.hpp").exists() and (
-            not HOST_LIB_PATH.exists() or any(p.stat().st_mtime > HOST_LIB_PATH.stat().st_mtime for p in hdeps)):
-        cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-include", "string",
-               "-include", "cstdint", f"-I{ref_inc}", f"-I{ROOT / 'include'}", "-o", str(HOST_LIB_PATH),
-               str(host_src), f"-L{LIB_PATH.parent}", "-leuler_b200", "-Wl,-rpath,$ORIGIN"]
-        if verbose:
-            print(" ".join(cmd))
-        subprocess.check_call(cmd)
-    return LIB_PATH
+    """Compile the CUDA library and the C++ host library (see _build.py)."""
+    from . import _build
+    return _build.build(verbose)
 
 
 # ----------------------------------------------------------------------------- C structs
@@ -116,6 +89,26 @@ def _load():
         "elb_reorder": (i32, [vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
         "elb_subsample_nChw16c": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
         "elb_selftest_bounded_wait": (i32, [i32, C.c_ulonglong]),
+        "elb_conv_set_trace": (i32, [vp, vp]),
+        "elb_conv_execute_async": (i32, [vp, vp, vp, vp, vp]),
+        "elb_conv_wait": (i32, [vp]),
+        "elb_conv_set_name": (i32, [vp, C.c_char_p]),
+        "elb_stack_create": (i32, [C.POINTER(ElbConvDesc), C.POINTER(i32), i32, C.POINTER(vp)]),
+        "elb_stack_prepare": (i32, [vp, i32, vp, vp]),
+        "elb_stack_enqueue": (i32, [vp, vp, vp, vp]),
+        "elb_stack_execute": (i32, [vp, vp, vp, C.c_int64]),
+        "elb_stack_layer": (i32, [vp, i32, C.POINTER(vp)]),
+        "elb_stack_sizes": (i32, [vp, C.POINTER(i32), C.POINTER(u64), C.POINTER(u64)]),
+        "elb_stack_launch_count": (u64, [vp]),
+        "elb_stack_layer_output": (i32, [vp, i32, C.POINTER(vp), C.POINTER(u64)]),
+        "elb_stack_set_layer_events": (i32, [vp, C.POINTER(vp), i32]),
+        "elb_stack_destroy": (None, [vp]),
+        "elb_conv_multi_create": (i32, [C.POINTER(ElbConvDesc), C.POINTER(i32), i32, C.POINTER(vp)]),
+        "elb_conv_multi_execute": (i32, [vp, vp, vp, vp, vp]),
+        "elb_conv_multi_parts": (i32, [vp, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]),
+        "elb_conv_multi_destroy": (None, [vp]),
+        "elb_wino_f32_conv_noalloc": (i32, [C.POINTER(ElbConvDesc), vp, vp, vp, vp, vp]),
+        "elb_wino_f32_noalloc_status": (i32, []),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)          # AttributeError here = stale library
@@ -127,7 +120,12 @@ lib = _load()
 EXPORTED_SYMBOLS = ["elb_conv_sizes", "elb_conv_create", "elb_conv_info", "elb_conv_execute", "elb_conv_enqueue",
                     "elb_conv_prepare", "elb_conv_set_accumulator_dump", "elb_conv_device_status",
                     "elb_conv_launch_count", "elb_conv_set_stage_events", "elb_conv_destroy", "elb_last_error", "elb_device_supported",
-                    "elb_reorder_nchw_to_nChw16c", "elb_reorder_nChw16c_to_nchw", "elb_reorder", "elb_subsample_nChw16c"]
+                    "elb_reorder_nchw_to_nChw16c", "elb_reorder_nChw16c_to_nchw", "elb_reorder", "elb_subsample_nChw16c",
+                    "elb_conv_execute_async", "elb_conv_wait", "elb_conv_set_name", "elb_conv_set_trace",
+                    "elb_selftest_bounded_wait", "elb_stack_create", "elb_stack_prepare", "elb_stack_enqueue",
+                    "elb_stack_execute", "elb_stack_layer", "elb_stack_sizes", "elb_stack_launch_count",
+                    "elb_stack_layer_output", "elb_stack_set_layer_events", "elb_stack_destroy", "elb_conv_multi_create", "elb_conv_multi_execute", "elb_conv_multi_parts",
+                    "elb_conv_multi_destroy", "elb_wino_f32_conv_noalloc", "elb_wino_f32_noalloc_status"]
 
 
 def last_error() -> str:
@@ -212,6 +210,7 @@ class eld_conv_t:
                 return rc
             self.xc = plan
             lib.elb_conv_info(self.xc, C.byref(info))
+            lib.elb_conv_set_name(self.xc, str(self.name).encode())
         else:
             rc = lib.elb_conv_sizes(C.byref(desc), C.byref(info))
             if rc != ELB_OK:
@@ -251,6 +250,11 @@ class eld_conv_t:
         arr = (C.c_void_p * 4)(*[int(h) for h in handles])
         return lib.elb_conv_set_stage_events(self.xc, arr)
 
+    def wait(self) -> int:
+        """Complete the asynchronous calls made with ``eager_mode = False`` (what a later call with
+        ``stream_sync = True`` does in the reference, src/elx_conv.cpp:234-235)."""
+        return lib.elb_conv_wait(self.xc)
+
     def close(self):
         if self.xc is not None:
             lib.elb_conv_destroy(self.xc)
@@ -268,7 +272,13 @@ def elx_conv(desc: eld_conv_t, output, input, weights, bias) -> int:
     torch tensors (CUDA or CPU), numpy arrays or raw addresses; output comes first."""
     if desc.xc is None:
         raise RuntimeError("elx_conv: descriptor is not set up")
-    return lib.elb_conv_execute(desc.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias))
+    if desc.eager_mode:
+        return lib.elb_conv_execute(desc.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias))
+    # eager_mode = False: enqueue and return; stream_sync = True waits (src/elx_conv.cpp:228-236)
+    rc = lib.elb_conv_execute_async(desc.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias))
+    if rc == ELB_OK and desc.stream_sync:
+        rc = lib.elb_conv_wait(desc.xc)
+    return rc
 
 
 def _elem_bytes(x) -> int:
@@ -294,3 +304,101 @@ def subsample(dst, src, n: int, c: int, h: int, w: int, step_h: int = 2, step_w:
     """Keep every step_h-th row and step_w-th column of a device nChw16c tensor (the glue between two
     layers of a stack; the reference's harness chains layers on the host, tests/elt_conv.cpp:399-410)."""
     return lib.elb_subsample_nChw16c(_ptr(dst), _ptr(src), n, c, h, w, step_h, step_w, _elem_bytes(src), _ptr(stream))
+
+
+class ConvStack:
+    """A chain of convolutions that stays on the device (``elb_stack_*``): ``descs`` are set-up-able
+    ``eld_conv_t`` descriptors, ``subsample_after[k]`` = 2 keeps every second row and column of layer
+    k's output.  The reference's harness chains layers on the host (tests/elt_conv.cpp:399-410)."""
+
+    def __init__(self, descs, subsample_after=None):
+        n = len(descs)
+        arr = (ElbConvDesc * n)(*[d._c_desc() for d in descs])
+        steps = (C.c_int32 * n)(*[int(v) for v in (subsample_after or [1] * n)])
+        h = C.c_void_p()
+        rc = lib.elb_stack_create(arr, steps, n, C.byref(h))
+        if rc != ELB_OK:
+            raise RuntimeError(f"elb_stack_create rc={rc}: {last_error()}")
+        self.h, self.n_layers = h, n
+        nl, bi, bo = C.c_int32(), C.c_uint64(), C.c_uint64()
+        lib.elb_stack_sizes(self.h, C.byref(nl), C.byref(bi), C.byref(bo))
+        self.bytes_input, self.bytes_output = bi.value, bo.value
+
+    def prepare(self, layer: int, weights, bias) -> int:
+        return lib.elb_stack_prepare(self.h, layer, _ptr(weights), _ptr(bias))
+
+    def enqueue(self, output, input, stream=None) -> int:
+        return lib.elb_stack_enqueue(self.h, _ptr(output), _ptr(input), stream)
+
+    def execute(self, output, input, images: int) -> int:
+        return lib.elb_stack_execute(self.h, _ptr(output), _ptr(input), images)
+
+    def layer_plan(self, layer: int):
+        p = C.c_void_p()
+        lib.elb_stack_layer(self.h, layer, C.byref(p))
+        return p
+
+    def layer_kernel(self, layer: int) -> str:
+        info = ElbConvInfo()
+        lib.elb_conv_info(self.layer_plan(layer), C.byref(info))
+        return KERNEL_NAMES.get(info.kernel, "?")
+
+    def launch_count(self) -> int:
+        return int(lib.elb_stack_launch_count(self.h))
+
+    def layer_output(self, layer: int):
+        """(device address, bytes) of layer k's output tensor inside the stack; address None for the last layer."""
+        p, b = C.c_void_p(), C.c_uint64()
+        lib.elb_stack_layer_output(self.h, layer, C.byref(p), C.byref(b))
+        return p.value, b.value
+
+    def set_layer_events(self, handles) -> int:
+        if handles is None:
+            return lib.elb_stack_set_layer_events(self.h, None, 0)
+        arr = (C.c_void_p * len(handles))(*[int(h) for h in handles])
+        return lib.elb_stack_set_layer_events(self.h, arr, len(handles))
+
+    def close(self):
+        if self.h is not None:
+            lib.elb_stack_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class MultiConv:
+    """One convolution whose minibatch is split over the GPUs of this box (``elb_conv_multi_*``):
+    GPU r runs images [r*N/G, (r+1)*N/G) of the host tensors; weights are replicated."""
+
+    def __init__(self, desc: eld_conv_t, devices=None, n_devices: int = 0):
+        cd = desc._c_desc()
+        h = C.c_void_p()
+        arr = (C.c_int32 * len(devices))(*devices) if devices else None
+        rc = lib.elb_conv_multi_create(C.byref(cd), arr, len(devices) if devices else n_devices, C.byref(h))
+        if rc != ELB_OK:
+            raise RuntimeError(f"elb_conv_multi_create rc={rc}: {last_error()}")
+        self.h = h
+
+    def parts(self):
+        n = C.c_int32(64)
+        dev, first, cnt = (C.c_int32 * 64)(), (C.c_int32 * 64)(), (C.c_int32 * 64)()
+        lib.elb_conv_multi_parts(self.h, C.byref(n), dev, first, cnt)
+        return [(dev[i], first[i], cnt[i]) for i in range(n.value)]
+
+    def execute(self, output, input, weights, bias) -> int:
+        return lib.elb_conv_multi_execute(self.h, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias))
+
+    def close(self):
+        if self.h is not None:
+            lib.elb_conv_multi_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -389,8 +389,8 @@ int dw_setup(DwPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, int nu
   // short strips keep many more threads in flight; 4 to 7 rows measured best on B200
   int rs = d.oh >= 28 ? 7 : 4;
   if (d.oh < rs) rs = d.oh;
-  if (const char *e = getenv("ELB_DW_ROWS")) {      // tuning experiments only
-    const int v = atoi(e);
+  {
+    const int v = tune_env("ELB_DW_ROWS", rs);
     if (v >= 1 && v <= 64) rs = v;
   }
   p.rows_strip = rs;

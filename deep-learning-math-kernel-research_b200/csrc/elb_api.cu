@@ -23,6 +23,32 @@ namespace {
 
 thread_local std::string g_last_error;
 
+// Severities and the two environment variables of the reference's logger (src/common/el_def.hpp:17-26,
+// src/el_init.cpp:18-27): EULER_LOG_LEVEL = lowest severity that is printed (default: info),
+// EULER_VERBOSE=1 = one "euler-perf" line per executed convolution.  Messages below perf go to
+// stderr here (the reference prints them to stdout and aborts on errors; this library returns
+// codes instead), perf lines go to stdout as in the reference.
+enum { LOG_TRACE = 1, LOG_DEBUG = 2, LOG_INFO = 3, LOG_WARN = 4, LOG_ERROR = 5, LOG_PERF = 999 };
+struct LogOptions {
+  int level = LOG_INFO;
+  bool verbose = false;
+  LogOptions() {
+    const char *v = getenv("EULER_VERBOSE");
+    verbose = v && v[0] == '1';
+    if (const char *l = getenv("EULER_LOG_LEVEL")) level = atoi(l);
+  }
+};
+const LogOptions &log_options() {
+  static const LogOptions o;
+  return o;
+}
+void log_line(int severity, const char *msg) {
+  if (severity < log_options().level) return;
+  const char *name = severity == LOG_TRACE ? "trace" : severity == LOG_DEBUG ? "debug" : severity == LOG_INFO ? "info"
+                   : severity == LOG_WARN ? "warn" : severity == LOG_ERROR ? "error" : "perf";
+  fprintf(severity == LOG_PERF ? stdout : stderr, "euler-%s, %s\n", name, msg);
+}
+
 int fail(int code, const char *fmt, ...) {
   char buf[512];
   va_list ap;
@@ -30,8 +56,8 @@ int fail(int code, const char *fmt, ...) {
   vsnprintf(buf, sizeof(buf), fmt, ap);
   va_end(ap);
   g_last_error = buf;
-  const char *v = getenv("EULER_VERBOSE");
-  if (v && atoi(v) > 0) fprintf(stderr, "euler-b200: %s\n", buf);
+  // "not implemented on the GPU" is an answer, not a fault: callers probe for it
+  log_line(code == ELB_UNIMPLEMENTED ? LOG_DEBUG : LOG_ERROR, buf);
   return code;
 }
 
@@ -121,7 +147,13 @@ struct elb_conv {
   cudaStream_t stream = nullptr;        // used by elb_conv_execute
   // device workspace
   void *d_wpack = nullptr, *d_wplain = nullptr, *d_scale = nullptr, *d_shift = nullptr;
+  void *d_shift_tbl = nullptr, *d_tap_cls = nullptr;     // int8 direct, zero point with padding: per-class shifts
   int *d_status = nullptr;
+  int *h_status = nullptr;              // pinned: the status word travels back on the stream, behind the kernels
+  std::string name = "ioi";             // eld_conv_t::name, printed in the euler-perf line
+  bool pending = false;                 // an asynchronous execute has not been waited for yet
+  bool pending_d2h = false;
+  cudaEvent_t ev_call_done = nullptr, ev_d2h_done = nullptr;   // end of the previous call on `stream` / `s_d2h`
   void *d_acc_dump = nullptr;           // caller memory
   void *d_trace = nullptr;              // caller memory (debug timeline)
   // staging for host-pointer callers
@@ -148,10 +180,16 @@ struct elb_conv {
 
   ~elb_conv() {
     cudaSetDevice(device);
-    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, (void *)d_status, d_in_stage, d_out_stage, d_cvt_in, d_cvt_out})
+    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, d_shift_tbl, d_tap_cls, (void *)d_status, d_in_stage, d_out_stage,
+                    d_cvt_in, d_cvt_out})
       if (p) cudaFree(p);
     wino_release(wino);
     dw_release(dw);
+    if (stream) cudaStreamSynchronize(stream);
+    if (s_d2h) cudaStreamSynchronize(s_d2h);
+    if (h_status) cudaFreeHost(h_status);
+    if (ev_call_done) cudaEventDestroy(ev_call_done);
+    if (ev_d2h_done) cudaEventDestroy(ev_d2h_done);
     if (stream) cudaStreamDestroy(stream);
     if (s_h2d) cudaStreamDestroy(s_h2d);
     if (s_d2h) cudaStreamDestroy(s_d2h);
@@ -265,12 +303,9 @@ int encode_i8_tmaps(elb_conv &pl, const void *input, int cnt, CUtensorMap *out) 
   if (!enc) return fail(ELB_GENERAL_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
   // IH/IW are the plan's view of the input plane (a 1x1 stride-1 convolution sees it as one row)
   const int s = pl.i8.stride, CB = pl.i8.CB, IH = pl.i8.IH, IW = pl.i8.IW;
-  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-  if (const char *e = getenv("ELB_I8_L2PROMO")) {                  // tuning experiments only
-    const int v = atoi(e);
-    promo = v == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
-          : v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-  }
+  const int pv = tune_env("ELB_I8_L2PROMO", 128);                  // measured without effect on these kernels
+  const CUtensorMapL2promotion promo = pv == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : pv == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                     : pv == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
   if (pl.i8.merged_rows) {
     // stride 1: a row of the box is BW*16 contiguous bytes; describe it as 2*BW 8-byte elements so
     // the copy engine moves whole rows (4-D map: x in 8-byte units, h, channel block, image)
@@ -307,8 +342,6 @@ int setup_i8_direct(elb_conv &pl) {
   I8ConvParams &p = pl.i8;
   if (d.sampling_kind != ELB_CALIBRATED)          // src/elx_int8_conv_direct.cpp:44-46, _1x1.cpp:225-226
     return fail(ELB_UNIMPLEMENTED, "int8 direct: non-calibrated sampling_kind not supported");
-  if (d.input_z != 0.0f && (d.pad_t || d.pad_l || d.pad_b || d.pad_r))
-    return fail(ELB_UNIMPLEMENTED, "int8 direct: non-zero input zero-point with padding is not implemented");
   p.N = d.n; p.IH = d.ih; p.IW = d.iw; p.OH = d.oh; p.OW = d.ow; p.KH = d.kh; p.KW = d.kw;
   p.stride = d.stride_h; p.pad_t = d.pad_t; p.pad_l = d.pad_l;
   p.CB = host::alignup(d.ic, V) / V;
@@ -322,7 +355,7 @@ int setup_i8_direct(elb_conv &pl) {
   p.rq.relu_hi = d.relu_upper;
   // with_ip_sum: honoured by the 1x1 algorithm (src/kernel/elk_u8s8_gemm.hxx:221-237).  The KxK
   // algorithm of the reference ignores the flag (src/elx_int8_conv_direct.cpp:121); this library
-  // applies the 1x1 semantics there as well, see DESIGN notes in the repository root.
+  // applies the 1x1 semantics there as well (f += prev * sum_scale); with the flag off the two agree bit for bit.
   p.rq.with_sum = d.with_ip_sum && d.dt_output != ELB_F32;
   p.rq.sum_scale = d.sum_scale;
   if (pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA || pl.info.kernel == ELB_KERNEL_I8_CONV_UMMA) {
@@ -332,8 +365,7 @@ int setup_i8_direct(elb_conv &pl) {
     // per-run bulk copies instead; it issues many more, smaller copies.)
     int mode = I8_MODE_BOX;
     if (pl.info.kernel == ELB_KERNEL_I8_GEMM_UMMA) {
-      const char *flat = getenv("ELB_I8_FLAT");
-      if (flat && atoi(flat) > 0) mode = I8_MODE_FLAT;
+      if (tune_env("ELB_I8_FLAT", 0) > 0) mode = I8_MODE_FLAT;
       else { p.IH = 1; p.IW = d.ih * d.iw; p.OH = 1; p.OW = d.oh * d.ow; }
     }
     pl.i8cfg = i8_umma_config(p.OCB, p.CB, p.taps, mode);
@@ -344,23 +376,21 @@ int setup_i8_direct(elb_conv &pl) {
     // channel blocks one tiled copy fetches: the largest power of two that divides CB, at most KC
     p.box_c = 1;
     while (p.box_c * 2 <= pl.i8cfg.KC && p.CB % (p.box_c * 2) == 0) p.box_c *= 2;
-    if (const char *e = getenv("ELB_I8_BOXC")) {                   // tuning experiments only
-      const int v = atoi(e);
+    {
+      const int v = tune_env("ELB_I8_BOXC", p.box_c);
       if (v >= 1 && v <= p.box_c && p.box_c % v == 0) p.box_c = v;
     }
     if (mode == I8_MODE_FLAT) {
       p.m_tiles = (p.M + 127) / 128;
     } else {
-      const char *nomerge = getenv("ELB_I8_NO_MERGED_ROWS");      // tuning experiments only
-      p.merged_rows = (p.stride == 1 && !(nomerge && atoi(nomerge) > 0)) ? 1 : 0;
+      p.merged_rows = (p.stride == 1 && tune_env("ELB_I8_NO_MERGED_ROWS", 0) <= 0) ? 1 : 0;
       choose_box(p.OH, p.OW, p.BW, p.BH);
       p.tiles_w = (p.OW + p.BW - 1) / p.BW;
       p.tiles_h = (p.OH + p.BH - 1) / p.BH;
       p.m_tiles = d.n * p.tiles_w * p.tiles_h;
     }
     {
-      const char *norot = getenv("ELB_I8_NO_ROTATE_K");            // tuning experiments only
-      p.rotate_k = (norot && atoi(norot) > 0) ? 0 : 1;
+      p.rotate_k = tune_env("ELB_I8_NO_ROTATE_K", 0) > 0 ? 0 : 1;
       // Producer warps and stages per pass.  A copy instruction occupies its warp for hundreds of
       // cycles, so the issue rate is set by how many warps issue and how many stages each serves per
       // pass; one stage per pass refills a slot as soon as it is free (a pass of two waits for both).
@@ -369,12 +399,11 @@ int setup_i8_direct(elb_conv &pl) {
       // 256 output channels with 4 warps x 1 stage (VGG conv4_2 0.091 -> 0.080 ms, conv3_2 0.081 ->
       // 0.074 ms); long launches of short K loops with 2 warps x 2 stages.  warps x stages must not
       // exceed the ring depth: a warp further ahead could not tell its slot's phase by parity.
-      // ELB_I8_SPP / ELB_I8_NPROD override (tuning experiments only).
       const bool short_launch = (long long)p.m_tiles * p.n_tiles <= 4LL * pl.num_sms;
       p.nprod = (pl.i8cfg.BN >= 128 && p.k_stages >= 16) ? 4 : 2;
       p.spp = (p.nprod == 4 || short_launch) ? 1 : 2;
-      if (const char *e = getenv("ELB_I8_NPROD")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) p.nprod = v; }
-      if (const char *e = getenv("ELB_I8_SPP")) p.spp = atoi(e) == 1 ? 1 : 2;
+      { const int v = tune_env("ELB_I8_NPROD", p.nprod); if (v == 1 || v == 2 || v == 4) p.nprod = v; }
+      p.spp = tune_env("ELB_I8_SPP", p.spp) == 1 ? 1 : 2;
       while (p.nprod * p.spp > pl.i8cfg.STAGES) { if (p.spp > 1) p.spp = 1; else p.nprod /= 2; }
     }
     // Pairs of SMs (int8_conv2.cu: each CTA fetches half of the weight panel) are opt-in with
@@ -383,7 +412,8 @@ int setup_i8_direct(elb_conv &pl) {
     // can be ISSUED, which pairing does not change, and it pays a cluster start-up.
     {
       const char *on2 = getenv("ELB_I8_CTA2");
-      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && on2 && atoi(on2) > 0) ? 1 : 0;
+      const bool zp_classes = d.input_z != 0.0f && (d.pad_t || d.pad_l || d.pad_b || d.pad_r);   // (single CTAs only)
+      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && on2 && atoi(on2) > 0 && !zp_classes) ? 1 : 0;
     }
     if (pl.i8cfg.cta2) CUDA_TRY(init_i8_umma2(pl.i8cfg, pl.num_sms));
     CUDA_TRY(init_i8_umma(pl.i8cfg));
@@ -409,6 +439,40 @@ int prepare_i8_direct(elb_conv &pl, const void *weights, const void *bias) {
   CUDA_TRY(cudaMemcpy(pl.d_scale, scale.data(), scale.size() * 4, cudaMemcpyHostToDevice));
   CUDA_TRY(cudaMemcpy(pl.d_shift, shift.data(), shift.size() * 4, cudaMemcpyHostToDevice));
   pl.info.workspace_bytes += scale.size() * 8;
+  if (d.input_z != 0.0f && (d.pad_t || d.pad_l || d.pad_b || d.pad_r)) {
+    // one shift vector per (valid kh range, valid kw range): src/elx_int8_conv_direct.cpp:227-423
+    const host::TapClasses th = host::tap_classes(d.oh, d.ih, d.kh, d.pad_t, d.stride_h);
+    const host::TapClasses tw = host::tap_classes(d.ow, d.iw, d.kw, d.pad_l, d.stride_w);
+    const int nh = (int)th.ranges.size(), nw = (int)tw.ranges.size(), OCP = wq.OCP;
+    std::vector<float> tbl((size_t)nh * nw * OCP), sc_c, sh_c;
+    std::vector<int32_t> qs(OCP);
+    for (int ch = 0; ch < nh; ++ch)
+      for (int cw = 0; cw < nw; ++cw) {
+        for (int o = 0; o < OCP; ++o) {
+          int32_t sum = 0;
+          for (int a = th.ranges[ch].first; a <= th.ranges[ch].second; ++a)
+            for (int b = tw.ranges[cw].first; b <= tw.ranges[cw].second; ++b) sum += wq.qsum_tap[(size_t)o * wq.taps + a * d.kw + b];
+          qs[o] = sum;
+        }
+        host::fold_constants_i8(wq, hb.data(), d.with_bias != 0, d.dt_output == ELB_F32, d.input_scale, d.input_z,
+                                d.output_scale, d.output_z, pl.i8.rq.with_sum != 0, d.sum_scale, d.sum_z, sc_c, sh_c, qs.data());
+        std::copy(sh_c.begin(), sh_c.end(), tbl.begin() + ((size_t)ch * nw + cw) * OCP);
+      }
+    std::vector<int> cls(th.cls);
+    cls.insert(cls.end(), tw.cls.begin(), tw.cls.end());
+    CUDA_TRY(cudaMalloc(&pl.d_shift_tbl, tbl.size() * 4));
+    CUDA_TRY(cudaMemcpy(pl.d_shift_tbl, tbl.data(), tbl.size() * 4, cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMalloc(&pl.d_tap_cls, cls.size() * 4));
+    CUDA_TRY(cudaMemcpy(pl.d_tap_cls, cls.data(), cls.size() * 4, cudaMemcpyHostToDevice));
+    pl.info.workspace_bytes += tbl.size() * 4 + cls.size() * 4;
+    pl.i8.shift_tbl = (const float *)pl.d_shift_tbl;
+    pl.i8.hclass = (const int *)pl.d_tap_cls;
+    pl.i8.wclass = pl.i8.hclass + d.oh;
+    pl.i8.zp_nw = nw;
+    // pixels that see every tap use the vector in `shift` (kept in shared memory by the tcgen05 kernel);
+    // when no pixel does (tiny images), -1 sends every pixel to the table
+    pl.i8.zp_full = (th.full >= 0 && tw.full >= 0) ? th.full * nw + tw.full : -1;
+  }
   if (pl.info.kernel == ELB_KERNEL_I8_SIMT) {
     CUDA_TRY(cudaMalloc(&pl.d_wplain, wq.q.size()));
     CUDA_TRY(cudaMemcpy(pl.d_wplain, wq.q.data(), wq.q.size(), cudaMemcpyHostToDevice));
@@ -474,14 +538,45 @@ int run_i8_direct(elb_conv &pl, void *out, const void *in, int n0, int cnt, cuda
   return ELB_OK;
 }
 
+// The status word of the kernels follows them on the stream into pinned host memory, so the call's
+// one synchronisation also brings back the verdict (no separate blocking copy).
+int fetch_status_async(elb_conv &pl, cudaStream_t s) {
+  CUDA_TRY(cudaMemcpyAsync(pl.h_status, pl.d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  return ELB_OK;
+}
 int check_status(elb_conv &pl) {
-  int st = 0;
-  CUDA_TRY(cudaMemcpy(&st, pl.d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  const int st = *pl.h_status;
   if (st != 0) {
+    *pl.h_status = 0;
     cudaMemset(pl.d_status, 0, sizeof(int));
     return fail(ELB_GENERAL_ERROR, "device kernel gave up waiting (status %d)", st);
   }
   return ELB_OK;
+}
+
+const char *fmt_name(int f) {
+  static const char *n[] = {"format-unknown", "nchw", "nhwc", "nChw16c", "nChw8c", "oihw", "hwio", "OIhw16i16o",
+                            "OIhw8i8o", "goihw", "ghwio", "gOIhw16i16o", "gOIhw8i8o"};
+  return f >= 1 && f <= 12 ? n[f] : n[0];
+}
+const char *dt_name(int t) {
+  static const char *n[] = {"datatype-unknown", "f32", "f16", "u8", "s8", "s32"};
+  return t >= 1 && t <= 5 ? n[t] : n[0];
+}
+const char *algo_name(int a) {
+  return a == ELB_CONV_DIRECT_1X1 ? "direct_conv_1x1" : a == ELB_CONV_DIRECT ? "direct_conv"
+       : a == ELB_CONV_DIRECT_VMG ? "direct_conv_vmg" : a == ELB_CONV_WINOGRAD ? "winograd_conv"
+       : a == ELB_DECONV_DIRECT ? "deconv" : "algorithm-unknown";
+}
+// The line execute_verbose prints (src/elx_conv.cpp:190-211), same fields in the same order.
+void perf_line(const elb_conv &pl, double ms) {
+  char buf[512];
+  const elb_conv_desc_t &u = pl.ud;
+  snprintf(buf, sizeof(buf), "%s,ih:%d;oh:%d;ic:%d;oc:%d,%s;%x,src:%s;wei:%s;dst:%s,src:%s;wei:%s;dst:%s;b:%s, %lf",
+           pl.name.c_str(), u.ih, u.oh, u.ic, u.oc, algo_name(pl.info.algorithm), u.execution_mode, fmt_name(u.fmt_input),
+           fmt_name(u.fmt_weights), fmt_name(u.fmt_output), dt_name(u.dt_input), dt_name(u.dt_weights),
+           dt_name(u.dt_output), dt_name(u.dt_bias), ms);
+  log_line(LOG_PERF, buf);
 }
 
 bool is_device_ptr(const void *p) {
@@ -619,6 +714,141 @@ int do_enqueue(elb_conv &pl, void *out, const void *in, cudaStream_t s) {
   return do_enqueue_range(pl, out, in, 0, pl.d.n, s);
 }
 
+// Wait for an asynchronous execute that has not been waited for (returns at once when there is none).
+int wait_pending(elb_conv &pl) {
+  if (!pl.pending) return ELB_OK;
+  pl.pending = false;
+  CUDA_TRY(cudaStreamSynchronize(pl.stream));
+  if (pl.pending_d2h) {
+    pl.pending_d2h = false;
+    CUDA_TRY(cudaStreamSynchronize(pl.s_d2h));
+  }
+  return check_status(pl);
+}
+
+// elx_conv (src/elx_conv.cpp:213-240).  wait = true is eager_mode (or stream_sync): the result is
+// there when the call returns.  wait = false is the reference's asynchronous mode
+// (src/elx_stream.cpp:54-62): copies and kernels are enqueued on the plan's streams, the call
+// returns, and elb_conv_wait (or the next waiting call, or the plan's destruction) completes it.
+// Calls on one plan run in submission order, as on the reference's single worker thread.
+int execute_common(elb_conv &pl, void *output, const void *input, const void *weights, const void *bias, bool wait) {
+  DeviceGuard guard(pl.device);
+  int rc = do_prepare(pl, weights, bias);
+  if (rc != ELB_OK) return rc;
+  const bool verbose = log_options().verbose && wait;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  if (verbose) {
+    if (pl.pending && (rc = wait_pending(pl)) != ELB_OK) return rc;
+    CUDA_TRY(cudaEventCreate(&t0));
+    CUDA_TRY(cudaEventCreate(&t1));
+  }
+  auto finish = [&](bool used_d2h) -> int {
+    int r = fetch_status_async(pl, pl.stream);
+    if (r != ELB_OK) return r;
+    if (!wait) {
+      // the next call must not overwrite the staging buffers before this one has used them
+      CUDA_TRY(cudaEventRecord(pl.ev_call_done, pl.stream));
+      if (used_d2h) CUDA_TRY(cudaEventRecord(pl.ev_d2h_done, pl.s_d2h));
+      pl.pending = true;
+      pl.pending_d2h = pl.pending_d2h || used_d2h;
+      return ELB_OK;
+    }
+    pl.pending = true;
+    pl.pending_d2h = pl.pending_d2h || used_d2h;
+    return wait_pending(pl);
+  };
+  const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+  if (in_dev && out_dev) {
+    if (verbose) CUDA_TRY(cudaEventRecord(t0, pl.stream));
+    rc = do_enqueue(pl, output, input, pl.stream);
+    if (rc != ELB_OK) return rc;
+    if (verbose) CUDA_TRY(cudaEventRecord(t1, pl.stream));
+    rc = finish(false);
+  } else {
+    // Host tensors (what a caller of the reference holds) are staged through device buffers of the plan.
+    const int N = pl.d.n;
+    const size_t in_img = pl.uinfo.bytes_input / N, out_img = pl.uinfo.bytes_output / N;
+    if (!in_dev && !pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.uinfo.bytes_input));
+    if (!out_dev && !pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.uinfo.bytes_output));
+    if (!pl.s_h2d) {
+      CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_h2d, cudaStreamNonBlocking));
+      CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_d2h, cudaStreamNonBlocking));
+    }
+    const size_t moved = (in_dev ? 0 : pl.uinfo.bytes_input) + (out_dev ? 0 : pl.uinfo.bytes_output);
+    // Small calls (under 32 MB moved) run in order on ONE stream: copy in, kernels, copy out, status.
+    // Larger ones are cut into chunks of whole images, and the host->device copy of chunk k+1, the
+    // kernels of chunk k and the device->host copy of chunk k-1 run at the same time on three
+    // streams (the two copy directions use different copy engines), so the call costs about the
+    // longer of the two transfers instead of their sum.  ELB_HOST_CHUNKS overrides the chunk count.
+    int chunks = moved < (size_t(32) << 20) ? 1 : (int)std::min<size_t>(8, moved / (size_t(8) << 20));
+    if (const char *e = getenv("ELB_HOST_CHUNKS")) {
+      const int v = atoi(e);
+      if (v >= 1) chunks = v;
+    }
+    if (chunks > N) chunks = N;
+    const void *din = in_dev ? input : pl.d_in_stage;
+    void *dout = out_dev ? output : pl.d_out_stage;
+    if (pl.pending) {         // an unfinished asynchronous call still reads / writes the staging buffers
+      CUDA_TRY(cudaStreamWaitEvent(pl.s_h2d, pl.ev_call_done, 0));
+      if (pl.pending_d2h) CUDA_TRY(cudaStreamWaitEvent(pl.stream, pl.ev_d2h_done, 0));
+    }
+    if (verbose) CUDA_TRY(cudaEventRecord(t0, pl.stream));
+    if (chunks == 1) {
+      if (!in_dev) CUDA_TRY(cudaMemcpyAsync(pl.d_in_stage, input, pl.uinfo.bytes_input, cudaMemcpyHostToDevice, pl.stream));
+      if (!out_dev && pl.d.with_ip_sum)
+        CUDA_TRY(cudaMemcpyAsync(pl.d_out_stage, output, pl.uinfo.bytes_output, cudaMemcpyHostToDevice, pl.stream));
+      rc = do_enqueue(pl, dout, din, pl.stream);
+      if (rc != ELB_OK) { cudaDeviceSynchronize(); return rc; }
+      if (!out_dev) CUDA_TRY(cudaMemcpyAsync(output, pl.d_out_stage, pl.uinfo.bytes_output, cudaMemcpyDeviceToHost, pl.stream));
+      if (verbose) CUDA_TRY(cudaEventRecord(t1, pl.stream));
+      rc = finish(false);
+    } else {
+      while ((int)pl.ev_in.size() < chunks) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        pl.ev_in.push_back(a);
+        pl.ev_done.push_back(b);
+      }
+      for (int k = 0; k < chunks; ++k) {
+        const int n0 = (int)((long long)N * k / chunks), n1 = (int)((long long)N * (k + 1) / chunks);
+        const int cnt = n1 - n0;
+        if (!in_dev)
+          CUDA_TRY(cudaMemcpyAsync((uint8_t *)pl.d_in_stage + n0 * in_img, (const uint8_t *)input + n0 * in_img, cnt * in_img,
+                                   cudaMemcpyHostToDevice, pl.s_h2d));
+        if (!out_dev && pl.d.with_ip_sum)
+          CUDA_TRY(cudaMemcpyAsync((uint8_t *)pl.d_out_stage + n0 * out_img, (const uint8_t *)output + n0 * out_img,
+                                   cnt * out_img, cudaMemcpyHostToDevice, pl.s_h2d));
+        CUDA_TRY(cudaEventRecord(pl.ev_in[k], pl.s_h2d));
+        CUDA_TRY(cudaStreamWaitEvent(pl.stream, pl.ev_in[k], 0));
+        rc = do_enqueue_range(pl, dout, din, n0, cnt, pl.stream);
+        if (rc != ELB_OK) { cudaDeviceSynchronize(); return rc; }
+        if (!out_dev) {
+          CUDA_TRY(cudaEventRecord(pl.ev_done[k], pl.stream));
+          CUDA_TRY(cudaStreamWaitEvent(pl.s_d2h, pl.ev_done[k], 0));
+          CUDA_TRY(cudaMemcpyAsync((uint8_t *)output + n0 * out_img, (uint8_t *)pl.d_out_stage + n0 * out_img, cnt * out_img,
+                                   cudaMemcpyDeviceToHost, pl.s_d2h));
+        }
+      }
+      if (verbose) {
+        if (!out_dev) {       // the call ends with the last copy out: bring it back onto the timed stream
+          CUDA_TRY(cudaEventRecord(pl.ev_d2h_done, pl.s_d2h));
+          CUDA_TRY(cudaStreamWaitEvent(pl.stream, pl.ev_d2h_done, 0));
+        }
+        CUDA_TRY(cudaEventRecord(t1, pl.stream));
+      }
+      rc = finish(!out_dev);
+    }
+  }
+  if (verbose) {
+    float ms = 0.0f;
+    if (rc == ELB_OK && cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess) perf_line(pl, ms);
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+  }
+  return rc;
+}
+
 }  // namespace
 
 // =============================================================================== C ABI
@@ -704,7 +934,10 @@ int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
   pl->num_sms = prop.multiProcessorCount;
   if (cudaStreamCreateWithFlags(&pl->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&pl->d_status, sizeof(int)) != cudaSuccess ||
-      cudaMemset(pl->d_status, 0, sizeof(int)) != cudaSuccess) {
+      cudaMemset(pl->d_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaHostAlloc(&pl->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess ||
+      cudaEventCreateWithFlags(&pl->ev_call_done, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&pl->ev_d2h_done, cudaEventDisableTiming) != cudaSuccess) {
     delete pl;
     return fail(ELB_GENERAL_ERROR, "device allocation failed");
   }
@@ -762,72 +995,24 @@ int elb_conv_enqueue(elb_conv_t *plan, void *output, const void *input, const vo
 
 int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const void *weights, const void *bias) {
   if (!plan || !output || !input) return fail(ELB_GENERAL_ERROR, "null argument");
-  elb_conv &pl = *plan;
-  DeviceGuard guard(pl.device);
-  int rc = do_prepare(pl, weights, bias);
-  if (rc != ELB_OK) return rc;
-  const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
-  if (in_dev && out_dev) {
-    rc = do_enqueue(pl, output, input, pl.stream);
-    if (rc != ELB_OK) return rc;
-    CUDA_TRY(cudaStreamSynchronize(pl.stream));
-    return check_status(pl);
-  }
-  // Host tensors (what a caller of the reference holds): the batch is cut into chunks of whole
-  // images, and the host->device copy of chunk k+1, the kernels of chunk k and the device->host
-  // copy of chunk k-1 run at the same time on three streams (the two copy directions use different
-  // copy engines), so a call costs about the longer of the two transfers instead of their sum.
-  const int N = pl.d.n;
-  const size_t in_img = pl.uinfo.bytes_input / N, out_img = pl.uinfo.bytes_output / N;
-  if (!in_dev && !pl.d_in_stage) CUDA_TRY(cudaMalloc(&pl.d_in_stage, pl.uinfo.bytes_input));
-  if (!out_dev && !pl.d_out_stage) CUDA_TRY(cudaMalloc(&pl.d_out_stage, pl.uinfo.bytes_output));
-  if (!pl.s_h2d) {
-    CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_h2d, cudaStreamNonBlocking));
-    CUDA_TRY(cudaStreamCreateWithFlags(&pl.s_d2h, cudaStreamNonBlocking));
-  }
-  int chunks = 1;
-  {
-    const size_t moved = (in_dev ? 0 : pl.uinfo.bytes_input) + (out_dev ? 0 : pl.uinfo.bytes_output);
-    const size_t target = size_t(4) << 20;                       // at least ~4 MB of transfers per chunk
-    chunks = (int)std::min<size_t>(8, std::max<size_t>(1, moved / target));
-    if (chunks > N) chunks = N;
-    if (const char *e = getenv("ELB_HOST_CHUNKS")) {             // tuning experiments only
-      const int v = atoi(e);
-      if (v >= 1) chunks = v < N ? v : N;
-    }
-  }
-  while ((int)pl.ev_in.size() < chunks) {
-    cudaEvent_t a = nullptr, b = nullptr;
-    CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
-    CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
-    pl.ev_in.push_back(a);
-    pl.ev_done.push_back(b);
-  }
-  const void *din = in_dev ? input : pl.d_in_stage;
-  void *dout = out_dev ? output : pl.d_out_stage;
-  for (int k = 0; k < chunks; ++k) {
-    const int n0 = (int)((long long)N * k / chunks), n1 = (int)((long long)N * (k + 1) / chunks);
-    const int cnt = n1 - n0;
-    if (!in_dev)
-      CUDA_TRY(cudaMemcpyAsync((uint8_t *)pl.d_in_stage + n0 * in_img, (const uint8_t *)input + n0 * in_img, cnt * in_img,
-                               cudaMemcpyHostToDevice, pl.s_h2d));
-    if (!out_dev && pl.d.with_ip_sum)
-      CUDA_TRY(cudaMemcpyAsync((uint8_t *)pl.d_out_stage + n0 * out_img, (const uint8_t *)output + n0 * out_img,
-                               cnt * out_img, cudaMemcpyHostToDevice, pl.s_h2d));
-    CUDA_TRY(cudaEventRecord(pl.ev_in[k], pl.s_h2d));
-    CUDA_TRY(cudaStreamWaitEvent(pl.stream, pl.ev_in[k], 0));
-    rc = do_enqueue_range(pl, dout, din, n0, cnt, pl.stream);
-    if (rc != ELB_OK) { cudaDeviceSynchronize(); return rc; }
-    if (!out_dev) {
-      CUDA_TRY(cudaEventRecord(pl.ev_done[k], pl.stream));
-      CUDA_TRY(cudaStreamWaitEvent(pl.s_d2h, pl.ev_done[k], 0));
-      CUDA_TRY(cudaMemcpyAsync((uint8_t *)output + n0 * out_img, (uint8_t *)pl.d_out_stage + n0 * out_img, cnt * out_img,
-                               cudaMemcpyDeviceToHost, pl.s_d2h));
-    }
-  }
-  CUDA_TRY(cudaStreamSynchronize(pl.stream));
-  if (!out_dev) CUDA_TRY(cudaStreamSynchronize(pl.s_d2h));
-  return check_status(pl);
+  return execute_common(*plan, output, input, weights, bias, true);
+}
+
+int elb_conv_execute_async(elb_conv_t *plan, void *output, const void *input, const void *weights, const void *bias) {
+  if (!plan || !output || !input) return fail(ELB_GENERAL_ERROR, "null argument");
+  return execute_common(*plan, output, input, weights, bias, false);
+}
+
+int elb_conv_wait(elb_conv_t *plan) {
+  if (!plan) return fail(ELB_GENERAL_ERROR, "null plan");
+  DeviceGuard guard(plan->device);
+  return wait_pending(*plan);
+}
+
+int elb_conv_set_name(elb_conv_t *plan, const char *name) {
+  if (!plan) return fail(ELB_GENERAL_ERROR, "null plan");
+  plan->name = name ? name : "";
+  return ELB_OK;
 }
 
 int elb_conv_set_accumulator_dump(elb_conv_t *plan, void *device_int32) {
@@ -910,7 +1095,8 @@ int elb_subsample_nChw16c(void *dst, const void *src, int n, int c, int h, int w
 ELB_API int elb_selftest_bounded_wait(int device, unsigned long long limit_ns) {
   int rc = elb_device_supported(device);
   if (rc != ELB_OK) return -rc;
-  DeviceGuard guard(device < 0 ? 0 : device);
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) return -1;
+  DeviceGuard guard(device);
   int *st = nullptr, h = -1;
   if (cudaMalloc(&st, sizeof(int)) != cudaSuccess) return -1;
   cudaMemset(st, 0, sizeof(int));

@@ -2,12 +2,24 @@
 // requantisation epilogue, status codes and the launcher prototypes the C-ABI layer calls.
 #pragma once
 #include <cstdint>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace elb {
 
 constexpr int V = 16;   // channel block of nChw16c / OIhw16i16o
+
+// Kernel tuning switches.  They read the environment only in builds made with -DELB_TUNING (kernel
+// experiments); the library as shipped ignores the environment and always returns the default, so
+// a user's environment cannot change which kernel variant runs.
+inline int tune_env(const char *name, int dflt) {
+#ifdef ELB_TUNING
+  if (const char *e = getenv(name)) return atoi(e);
+#endif
+  (void)name;
+  return dflt;
+}
 
 // device status word values (0 = ok)
 enum : int {
@@ -123,7 +135,12 @@ struct I8ConvParams {
   const int8_t *wpack;               // UMMA operand image [n_tile][k_stage][KC][BN][16]
   const int8_t *wplain;              // [OCpad][taps][ICpad] (CUDA-core kernel)
   const float *scale;                // [OCpad] folded iS*Sw(/oS)
-  const float *shift;                // [OCpad] folded bias/oS + oz - ...
+  const float *shift;                // [OCpad] folded bias/oS + oz - ...  (pixels that see every filter tap)
+  // non-zero input zero point with padding: pixels near a border see fewer taps and take their shift
+  // from shift_tbl[hclass[oh] * zp_nw + wclass[ow]][OCpad]; null when one shift vector serves all
+  const float *shift_tbl;
+  const int *hclass, *wclass;
+  int zp_nw, zp_full;                // classes along w; index of the class `shift` holds
   void *out;                         // nChw16c u8 / s8 / f32
   int32_t *acc_dump;                 // optional raw accumulators, nChw16c int32
   int *status;

@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <utility>
 #include <vector>
 
 namespace elb {
@@ -24,6 +25,7 @@ struct I8Weights {
   std::vector<int8_t> q;        // [OCP][taps][ICP]
   std::vector<float> absmax;    // [OCP]
   std::vector<int32_t> qsum;    // [OCP] sum of q over all taps and channels
+  std::vector<int32_t> qsum_tap;   // [OCP][taps] sum of q over the channels of one tap
 };
 
 // Per output channel: absmax over the real input channels and all taps; q = rne((w*127)/absmax)
@@ -38,6 +40,7 @@ inline I8Weights quantize_weights_i8(const float *w, int oc, int ic, int kh, int
   r.q.assign((size_t)r.OCP * r.taps * r.ICP, 0);
   r.absmax.assign(r.OCP, 0.0f);
   r.qsum.assign(r.OCP, 0);
+  r.qsum_tap.assign((size_t)r.OCP * r.taps, 0);
   for (int o = 0; o < r.OCP; ++o) {
     float m = 0.0f;
     for (int i = 0; i < ic; ++i)
@@ -56,6 +59,7 @@ inline I8Weights quantize_weights_i8(const float *w, int oc, int ic, int kh, int
           volatile float u = t / m;                                        // roundings separate
           const int8_t qv = (int8_t)std::nearbyintf(u);
           r.q[((size_t)o * r.taps + a * kw + b) * r.ICP + i] = qv;
+          r.qsum_tap[(size_t)o * r.taps + a * kw + b] += qv;
           s += qv;
         }
     r.qsum[o] = s;
@@ -67,9 +71,12 @@ inline I8Weights quantize_weights_i8(const float *w, int oc, int ic, int kh, int
 // Reference: src/elx_int8_conv_direct_1x1.cpp:316-353, src/elx_int8_conv_direct.cpp:357-419.
 //   u8/s8 out: scale = (iS*Sw)*(1/oS); shift = fma(bias, 1/oS, oz) - (iz*Sq)*scale [- sum_z*sum_S]
 //   f32  out: scale =  iS*Sw;         shift = bias - (iz*Sq)*scale
+// qsum: the sum of q that the zero-point term uses, [OCP]; null = wq.qsum (every tap inside the image).
 inline void fold_constants_i8(const I8Weights &wq, const float *bias, bool with_bias, bool out_f32,
                               float iS, float iz, float oS, float oz, bool with_sum, float sum_S,
-                              float sum_z, std::vector<float> &scale, std::vector<float> &shift) {
+                              float sum_z, std::vector<float> &scale, std::vector<float> &shift,
+                              const int32_t *qsum = nullptr) {
+  if (!qsum) qsum = wq.qsum.data();
   scale.assign(wq.OCP, 0.0f);
   shift.assign(wq.OCP, 0.0f);
   volatile float orepS = 1.0f / oS;
@@ -86,7 +93,7 @@ inline void fold_constants_i8(const I8Weights &wq, const float *bias, bool with_
       sh = std::fmaf(b, orepS, oz);
     }
     if (iz != 0.0f) {
-      volatile float zq = iz * (float)wq.qsum[o];
+      volatile float zq = iz * (float)qsum[o];
       volatile float zs = zq * sc;
       sh = sh - zs;
     }
@@ -97,6 +104,36 @@ inline void fold_constants_i8(const I8Weights &wq, const float *bias, bool with_
     scale[o] = sc;
     shift[o] = sh;
   }
+}
+
+// Output pixels near a padded border see fewer filter taps, and with a non-zero input zero point
+// the shift of a pixel depends on WHICH taps lie inside the image: shift = ... - (iz * sum of q over
+// those taps) * scale.  The reference keeps one shift vector per (range of kh, range of kw)
+// (src/elx_int8_conv_direct.cpp:227-309 prepare_weights_acc, :311-423 __trans_weights_acc).  Here a
+// class is the pair (first valid tap, last valid tap) along one axis; cls[o] is the class of output
+// coordinate o and ranges[c] its tap range.  The class of coordinates that see every tap is `full`.
+struct TapClasses {
+  std::vector<int> cls;                          // [out extent]
+  std::vector<std::pair<int, int>> ranges;       // [classes] first / last valid tap
+  int full = -1;
+};
+inline TapClasses tap_classes(int out, int in, int k, int pad, int stride) {
+  TapClasses t;
+  t.cls.resize(out);
+  for (int o = 0; o < out; ++o) {
+    int lo = k, hi = -1;
+    for (int a = 0; a < k; ++a) {
+      const int i = o * stride - pad + a;
+      if (i >= 0 && i < in) { lo = a < lo ? a : lo; hi = a; }
+    }
+    int c = -1;
+    for (size_t j = 0; j < t.ranges.size(); ++j)
+      if (t.ranges[j].first == lo && t.ranges[j].second == hi) c = (int)j;
+    if (c < 0) { c = (int)t.ranges.size(); t.ranges.emplace_back(lo, hi); }
+    if (lo == 0 && hi == k - 1) t.full = c;
+    t.cls[o] = c;
+  }
+  return t;
 }
 
 // Operand image of B for the tcgen05 kernels: [n_tile][k_stage][KC chunks][BN rows][16 bytes].

@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], NUM_EPI_WARPS * 32);
+      mbar_init(&tempty[b], NUM_EPI_WARPS);      // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -196,8 +196,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
           if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
           if (active) {
-            while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
-            }      // every issuing lane observes the completed phase itself
             const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
             uint8_t *a_dst = smem + s * L::STAGE_BYTES;
             uint8_t *b_dst = a_dst + L::A_BYTES;
@@ -291,6 +289,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
       bool valid;
       size_t pix_off;      // element offset of channel-block 0 of this pixel, in units of 16 channels
       size_t blk_stride;   // distance between channel blocks, same units
+      const float *shift_row = s_shift;      // this pixel's shift vector (border pixels: from the class table)
       if (MODE == I8_MODE_FLAT) {
         const int m = mt * BM + row;
         valid = m < p.M;
@@ -306,6 +305,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         valid = oh < p.OH && ow < p.OW;
         pix_off = (static_cast<size_t>(n) * p.OCB * p.OH + oh) * p.OW + ow;
         blk_stride = static_cast<size_t>(p.OH) * p.OW;
+        if (p.shift_tbl && valid) {
+          const int cls = __ldg(p.hclass + oh) * p.zp_nw + __ldg(p.wclass + ow);
+          if (cls != p.zp_full) shift_row = p.shift_tbl + static_cast<size_t>(cls) * (p.OCB * V);
+        }
       }
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
       tc_fence_after_sync();
@@ -323,7 +326,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
 #pragma unroll
             for (int i = 0; i < 4; ++i) d[i] = make_int4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
           }
-          requant_store16(acc, s_scale + ocb * 16, s_shift + ocb * 16,
+          requant_store16(acc, s_scale + ocb * 16, shift_row + ocb * 16,
                           static_cast<uint8_t *>(p.out) + off * elt, p.rq);
         }
       };
@@ -352,7 +355,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         if (k + 3 < nblk) emit(half + P * (k + 3), r3);
       }
       tc_fence_before_sync();
-      mbar_arrive(&tempty[b]);
+      __syncwarp();                             // every lane's tensor-memory loads are done ...
+      if (lane == 0) mbar_arrive(&tempty[b]);   // ... before the warp gives the accumulator back
       if (tcount == 0 && threadIdx.x == 64) ELB_TRACE(42);
     }
   }
@@ -416,7 +420,9 @@ __global__ void __launch_bounds__(128) i8_simt_kernel(const __grid_constant__ I8
     for (int i = 0; i < 16; ++i) p.acc_dump[off + i] = acc[i];
   }
   const int elt = p.rq.out_type == OUT_F32 ? 4 : 1;
-  requant_store16(acc, p.scale + ocb * 16, p.shift + ocb * 16, static_cast<uint8_t *>(p.out) + off * elt, p.rq);
+  const float *shift_row = p.shift;
+  if (p.shift_tbl) shift_row = p.shift_tbl + static_cast<size_t>(__ldg(p.hclass + oh) * p.zp_nw + __ldg(p.wclass + ow)) * (p.OCB * V);
+  requant_store16(acc, p.scale + ocb * 16, shift_row + ocb * 16, static_cast<uint8_t *>(p.out) + off * elt, p.rq);
 }
 
 __global__ void wait_selftest_kernel(int *status, unsigned long long limit_ns) {
@@ -443,8 +449,8 @@ cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool 
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
   const int tiles = p.m_tiles * p.n_tiles;
   int grid = tiles < num_sms ? tiles : num_sms;
-  if (const char *e = getenv("ELB_MAX_CTAS")) {   // tuning experiments only
-    const int v = atoi(e);
+  {
+    const int v = tune_env("ELB_MAX_CTAS", grid);
     if (v > 0 && v < grid) grid = v;
   }
   kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
@@ -454,7 +460,7 @@ cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool 
 }  // namespace
 
 // Tile configuration.  BN (output channels per tile) in {64, 128, 256}; 8 K-chunks (128 bytes of K)
-// per stage; as many stages as fit 227 KB.  ELB_I8_BN overrides the choice (tuning experiments).
+// per stage; as many stages as fit 227 KB.
 I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
   I8UmmaConfig c{};
   c.mode = mode;
@@ -463,8 +469,8 @@ I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
   // per MAC fall with BN: 256 wherever the channel count allows it (measured on the 1x1 and the
   // 3x3 stride-2 benchmark layers: 13.5 vs 18 us and 39 vs 55 us against BN = 128).
   c.BN = ocp >= 256 ? 256 : ocp >= 128 ? 128 : 64;
-  if (const char *e = getenv("ELB_I8_BN")) {
-    const int v = atoi(e);
+  {
+    const int v = tune_env("ELB_I8_BN", c.BN);
     if (v == 64 || v == 128 || v == 256) c.BN = v;
   }
   c.KC = 8;

@@ -68,38 +68,104 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test, but the thread may be suspended by the hardware until the phase completes or
+// `ns` nanoseconds have passed: a waiting thread then issues (almost) no instructions and no
+// shared-memory traffic, where a plain try_wait loop keeps the SM's one barrier unit busy.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t WAIT_SUSPEND_NS = 20000;     // per try: bounds how late a waiter notices the CTA-wide abort flag
+
 // Wait for the phase with the given parity to complete.  Returns false (and raises *abort_flag,
 // a shared-memory word every role of the CTA polls) if the wait ran out of time or another role
 // already gave up.
+//
+// Barrier operations are a scarce resource: measured on B200, every mbarrier instruction of a CTA
+// goes through one unit that serves them one after the other (a wait on an ALREADY completed
+// barrier took 300-400 cycles while thirteen other threads of the CTA were polling).  So a wait
+// first tests once (the common case in a running pipeline), and only then suspends.
+#ifndef ELB_WAIT_MODE
+#define ELB_WAIT_MODE 0
+#endif
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-  // The limit is counted on the SM's own cycle counter: it is a register read, whereas the global
-  // nanosecond timer costs a microsecond-scale round trip that would sit on the critical path of
-  // every pipeline stage.
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-        *abort_flag = 1;
-        return false;
+#if ELB_WAIT_MODE == 0
+  if (mbar_try_wait(bar, parity)) return true;
+#elif ELB_WAIT_MODE == 1
+  if (mbar_test_wait(bar, parity)) return true;
+#elif ELB_WAIT_MODE == 2
+  for (int i = 0; i < 64; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+#elif ELB_WAIT_MODE == 3
+  {
+    const long long t00 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((++spins & 255u) == 0u) {
+        if (*abort_flag) return false;
+        if (clock64() - t00 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
       }
+    }
+  }
+#elif ELB_WAIT_MODE == 4
+  {
+    const long long t00 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+      if (mbar_test_wait(bar, parity)) return true;
+      if ((++spins & 255u) == 0u) {
+        if (*abort_flag) return false;
+        if (clock64() - t00 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
+      }
+    }
+  }
+#endif
+  // The limit is counted on the SM's own cycle counter: it is a register read, whereas the global
+  // nanosecond timer costs a microsecond-scale round trip.
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait_suspend(bar, parity, WAIT_SUSPEND_NS)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
     }
   }
 }
 
-// Warp-uniform form: lane 0 does the bounded wait and the verdict is broadcast, so a time-out can
-// never split the warp (the callers go on to warp-synchronous instructions).  After a success
-// every lane observes the completed phase itself, which gives each lane its own acquire.
+// Warp-uniform form: lane 0 alone waits (one barrier operation per warp instead of thirty-two)
+// and the verdict is broadcast, so a time-out can never split the warp (the callers go on to
+// warp-synchronous instructions).  The warp barrier behind the broadcast orders the other lanes'
+// later accesses after lane 0's acquire of the phase; callers that go on to read tensor memory
+// add tcgen05.fence::after_thread_sync as after any thread synchronisation.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
   ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-  if (ok) {
-    while (!mbar_try_wait(bar, parity)) {
-    }
-  }
+  __syncwarp();
   return ok != 0;
 }
 

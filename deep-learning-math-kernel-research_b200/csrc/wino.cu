@@ -502,6 +502,7 @@ struct WinoGemmParams {
   int rotate_k;             // tiles start their K loop at different stages (spreads the weight reads over L2)
   int spp;                  // pipeline stages a producer warp fills per pass (1 or 2); the two warps alternate passes
   int a_tmem;               // fp32, single CTAs: A planes in tensor memory and ONE accumulator buffer (see the kernel)
+  int ablate;               // -DELB_TUNING builds only: bit mask of pipeline roles switched off to find the bound (results are then wrong)
   const float *bias;
   float *out;
   int with_bias, with_relu, with_sum;
@@ -513,6 +514,16 @@ struct WinoGemmParams {
 // shared-memory reads of the B operand per MMA (the fp32 path is bound by shared-memory bandwidth:
 // three tf32 MMAs per K step, each reading A and B).  Warp 1 of the peer CTA forwards "my stage is
 // ready" to the leader; commits are multicast to both CTAs.
+#ifdef ELB_TUNING
+#define ABL(bit) ((p.ablate & (bit)) != 0)      // 1 no split, 2 no MMA, 4 no result store, 8 no A copy, 16 no B copy
+#else
+#define ABL(bit) false
+#endif
+#ifdef ELB_TUNING
+#define WG_TRACE2(slot) do { if (p.trace && (slot) < 64) p.trace[(gridDim.x + blockIdx.x) * 64 + (slot)] = clock64(); } while (0)
+#else
+#define WG_TRACE2(slot) do { } while (0)
+#endif
 #define WG_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
 template <bool CTA2>
@@ -571,7 +582,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], CTA2 ? 2 * GEMM_EPI_WARPS : GEMM_EPI_WARPS * 32);
+      mbar_init(&tempty[b], CTA2 ? 2 * GEMM_EPI_WARPS : GEMM_EPI_WARPS);      // one arrival per epilogue warp
     }
     *abort_flag = 0;
     *tile_started = -1;
@@ -622,11 +633,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
           if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
           uint8_t *stage = smem + s * stage_bytes;
-          if (active) {
-            while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
-            }
-            if (gl == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(A_RAW_BYTES) + b_stage_bytes);
-          }
+          if (active && gl == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(A_RAW_BYTES) + b_stage_bytes);
           __syncwarp();
           if (active) {
             if (gl < 4) tma_tile_3d(stage + gl * 2048, &p.tmap_a, 4 * gl, ptile * BM, n * p.CB + ksr, &full[s]);
@@ -665,24 +672,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         // empty[s] is committed by the MMAs of the stage's previous use, which also implies that the
         // splitter warps are done with raw slot s
         int w_ok = 1;
+        if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(2 * gpass);
         if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
         if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
+        if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(2 * gpass + 1);
         uint8_t *stage = smem + s * stage_bytes;
-        if (active) {
-          while (!mbar_try_wait(&empty[s], ph ^ 1u)) {
-          }        // every issuing lane observes the completed phase itself
-          if (gl == 0) mbar_arrive_expect_tx(&full[s], (live ? a_gbytes : 0u) + b_stage_bytes);
-        }
+        if (active && gl == 0) mbar_arrive_expect_tx(&full[s], (live && !ABL(8) ? a_gbytes : 0u) + (ABL(16) ? 0u : b_stage_bytes));
         __syncwarp();
         if (active) {
           if (gl == 0) {
-            if (live)
+            if (live && !ABL(8))
               tma_bulk_g2s(stage, a_src + static_cast<size_t>(ksr) * a_gbytes, a_gbytes, &full[s]);
-          } else {
+          } else if (!ABL(16)) {
             tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_pitch, b_stage_bytes, &full[s]);
           }
         }
         __syncwarp();
+        if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(24 + gpass / 2);
       }
       if (spp == 2 && (p.k_stages & 1)) --it;        // the last pass of an odd K loop served one stage only
     }
@@ -734,14 +740,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const int s = it % nstages;
           const uint32_t ph = (it / nstages) & 1u;
+          if (it < 6) WG_TRACE2(32 + 3 * it);
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (CTA2 && !mbar_wait(&pfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           tc_fence_after_sync();
+          if (it < 6) WG_TRACE2(33 + 3 * it);
           if (ks == 0 && tcount < 8) WG_TRACE(16 + tcount);
           const uint32_t a_addr = smem_u32(smem + s * stage_bytes);
           const uint32_t b_addr = a_addr + b_off;
-          if (p.kind == KIND_F32) {
+          if (ABL(2)) {
+          } else if (p.kind == KIND_F32) {
             // planes: A hi at +0, lo at +8 KB; B hi at +0, lo at +4 chunks.  K step = 2 chunks.
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2) {
@@ -776,6 +785,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           }
           if (CTA2) umma_commit_2cta(&empty[s]);
           else umma_commit(&empty[s]);
+          if (it < 6) WG_TRACE2(34 + 3 * it);
         }
         if (ok) {
           if (CTA2) umma_commit_2cta(&tfull[b]);
@@ -798,8 +808,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           if (static_cast<int>(it % GEMM_CONV_GROUPS) != cgrp) continue;       // the other group's stage
           const int s = it % nstages;
           const uint32_t ph = (it / nstages) & 1u;
+          if (tid_c == 0 && it < 6) WG_TRACE2(50 + it);
           if (!mbar_wait_warp(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (tid_c == 0 && it < 8) WG_TRACE(48 + 2 * it);
+          if (ABL(1)) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&cfull[s]);
+            continue;
+          }
           if (a_in_tmem) {
             // single CTAs: the planes go to TENSOR memory, row r of the stage = lane r, so the MMAs
             // read A without touching shared memory (three MMAs per K step re-reading A and B from
@@ -923,7 +939,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           }
           return;
         }
-        if (live && ocb < p.OCB) {
+        if (live && ocb < p.OCB && !ABL(4)) {
           float f[16];
           if (p.kind == KIND_F32) {
 #pragma unroll
@@ -977,13 +993,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         if (k + 3 < nblk) emit(k + 3, r3);
       }
       tc_fence_before_sync();
-      if (CTA2) {
-        // one arrival per warp on the LEADER's barrier: the accumulator is reused by MMAs that write
-        // both CTAs' tensor memory
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(b ? tempty_leader1 : tempty_leader0);
-      } else {
-        mbar_arrive(&tempty[b]);
+      // one arrival per warp (pairs: on the LEADER's barrier, the accumulator is reused by MMAs that
+      // write both CTAs' tensor memory); the warp barrier puts every lane's tensor-memory loads in front of it
+      __syncwarp();
+      if (lane == 0) {
+        if (CTA2) mbar_arrive_cluster(b ? tempty_leader1 : tempty_leader0);
+        else mbar_arrive(&tempty[b]);
       }
       if (threadIdx.x == 64 && tcount < 8) WG_TRACE(40 + tcount);
     }
@@ -1329,7 +1344,7 @@ std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, in
   return u;
 }
 
-// Tuning switches of the GEMM kernel (environment overrides are for experiments only).
+// Tuning switches of the GEMM kernel (tune_env: overridable only in -DELB_TUNING builds).
 // fp32: A in tensor memory costs the second accumulator buffer (the epilogue no longer overlaps the
 // next tile's MMAs) but relieves the shared-memory port and deepens the ring.  Measured on B200,
 // per layer of the VGG-16 stack (32 images): it loses where the K loop is short and the epilogue
@@ -1337,22 +1352,20 @@ std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, in
 // channels x 8 stages, and wins from 256 input channels up (conv4_2 0.308 -> 0.283 ms, conv5_x
 // 0.108 -> 0.097 ms) and whenever a CTA runs a single tile (1x1 benchmark layer 68.9 -> 55.9 us).
 inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms) {
-  if (const char *e = getenv("ELB_F32_A_TMEM")) return atoi(e) > 0 ? 1 : 0;
-  return kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms) ? 1 : 0;
+  const int dflt = kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms) ? 1 : 0;
+  return tune_env("ELB_F32_A_TMEM", dflt) > 0 ? 1 : 0;
 }
 // K rotation spreads the weight reads of CTAs running side by side over L2; measured without effect
 // on this kernel (the weights of one position are 0.5 MB and stay hot), so it is off.
 inline int tune_rotate_k() {
-  if (const char *e = getenv("ELB_WINO_ROTATE_K")) return atoi(e) > 0 ? 1 : 0;
-  return 0;
+  return tune_env("ELB_WINO_ROTATE_K", 0) > 0 ? 1 : 0;
 }
 // Stages per producer pass.  One stage per pass refills a slot as soon as it is free (a pass of two
 // waits for both); two per pass doubles the issue rate.  fp32 needs a stage every ~800 cycles at
 // best and gains from the shorter wait on every layer of the VGG-16 stack (conv3_2 0.368 -> 0.351 ms),
 // int8 Winograd does not care.
 inline int tune_spp(int kind) {
-  if (const char *e = getenv("ELB_WINO_SPP")) return atoi(e) == 1 ? 1 : 2;
-  return kind == KIND_F32 ? 1 : 2;
+  return tune_env("ELB_WINO_SPP", kind == KIND_F32 ? 1 : 2) == 1 ? 1 : 2;
 }
 
 }  // namespace
@@ -1410,7 +1423,9 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   const size_t tiles_img = static_cast<size_t>(g.ht) * g.wt;
   const size_t a_gbytes = w->kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;    // one stage of A in global memory
   const size_t per_tile = static_cast<size_t>(AA) * (static_cast<size_t>(g.k_stages) * a_gbytes / BM + static_cast<size_t>(w->OCP) * 4);
-  size_t imgs = WORKSPACE_BUDGET / (per_tile * tiles_img);
+  size_t budget = WORKSPACE_BUDGET;
+  budget = static_cast<size_t>(tune_env("ELB_WINO_CHUNK_MB", static_cast<int>(budget >> 20))) << 20;
+  size_t imgs = budget / (per_tile * tiles_img);
   if (imgs < 1) imgs = 1;
   if (imgs > static_cast<size_t>(d.n) || w->flat) imgs = d.n;       // flat mode needs no transform-domain buffers
   w->imgs_per_chunk = static_cast<int>(imgs);
@@ -1675,7 +1690,8 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.spp = tune_spp(w->kind);
     gp.rotate_k = tune_rotate_k();
     // opt-in: measured without effect (VGG conv1_2 GEMM 0.786 vs 0.788 ms, conv3_2 0.427 vs 0.433 ms)
-    gp.prefetch = (getenv("ELB_WINO_PREFETCH") && atoi(getenv("ELB_WINO_PREFETCH")) > 0) ? 1 : 0;
+    gp.prefetch = tune_env("ELB_WINO_PREFETCH", 0) > 0 ? 1 : 0;
+    gp.ablate = tune_env("ELB_ABL", 0);
     gp.a_tmem = tune_a_tmem(w->kind, gp.k_stages, static_cast<long long>(gp.positions) * gp.m_tiles * gp.n_tiles, num_sms);
     if (w->cta2) {
       const int pairs = gp.positions * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
@@ -1773,8 +1789,11 @@ __device__ __forceinline__ void g3_dev(float f0, float f1, float f2, float (&o)[
 // [a][n tile][k stage = ic/16][plane][chunk = (ic%16)/4][BN rows][4 floats].
 __global__ void wino_weights_f32_kernel(const float *__restrict__ w, float *__restrict__ b_img, int oc, int ic,
                                         int OCP, int ICP, int BN, int n_tiles) {
+  // one thread per row of EVERY n tile (n_tiles * BN >= OCP): rows past the last output channel are
+  // written as zeros, because the scratch behind them still holds an earlier call's bytes
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= OCP * ICP) return;
+  if (idx >= n_tiles * BN * ICP) return;
+  (void)OCP;
   const int o = idx / ICP, i = idx - o * ICP;
   float g[3][3];
 #pragma unroll
@@ -1894,8 +1913,8 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
 
   // the status word must start at zero; everything else the kernels read is rewritten below
   if (cudaMemsetAsync(status, 0, 256, s) != cudaSuccess) return fail(ELB_GENERAL_ERROR, "cudaMemsetAsync failed");
-  wino_weights_f32_kernel<<<(OCP * ICP + 255) / 256, 256, 0, s>>>(static_cast<const float *>(weights), b_img, d.oc, d.ic,
-                                                                OCP, ICP, BN, n_tiles);
+  wino_weights_f32_kernel<<<(n_tiles * BN * ICP + 255) / 256, 256, 0, s>>>(static_cast<const float *>(weights), b_img, d.oc,
+                                                                         d.ic, OCP, ICP, BN, n_tiles);
   WinoInParams ip{};
   ip.in = input; ip.a_img = a_img; ip.g = g;
   wino_input_kernel<false><<<dim3((g.Tpad + TRANS_TILES - 1) / TRANS_TILES, g.CB), TRANS_THREADS, 0, s>>>(ip);
@@ -1917,4 +1936,17 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("kernel launch failed: ") + cudaGetErrorString(e));
   return ELB_OK;
+}
+
+// Status word of the allocation-free path on the current device: 0 = every bounded wait of the last
+// elb_wino_f32_conv_noalloc call completed, otherwise the code of the wait that gave up (the output
+// of that call is then invalid); -1 = the entry point has not run on this device yet or the read
+// failed.  Call it after synchronising the stream the convolution was enqueued on.  It copies four
+// bytes from the static array to the host and allocates nothing.
+extern "C" ELB_API int elb_wino_f32_noalloc_status(void) {
+  using namespace elb;
+  int dev = 0, st = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= NOALLOC_MAX_DEVICES || !g_noalloc_ptr[dev]) return -1;
+  if (cudaMemcpy(&st, g_noalloc_ptr[dev], sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return st;
 }

@@ -20,6 +20,10 @@
 //   ~eld_conv_t()       releases the plan (src/eld_conv.cpp:52-57)
 //   reorder<...>        layout conversions of HOST tensors as the reference's test harness uses them
 //                       (src/elx_reorder.cpp:11-207); plain loops, not part of any timed path
+// eager_mode = false enqueues the call on the plan's CUDA streams and returns (the reference hands
+// it to one worker thread, src/elx_stream.cpp:54-62); stream_sync = true then waits
+// (src/elx_conv.cpp:234-235), and so does the destructor.  With EULER_GPUS=G (G > 1) in the
+// environment a fully set-up descriptor splits its minibatch over GPUs 0..G-1 (host tensors only).
 // Differences a caller can observe: unsupported descriptors return ELD_UNIMPLEMENTED where the
 // reference prints "euler-error" and aborts; the CPU tuning knobs are ignored (flatting.t is
 // honoured by the int8 depthwise path, whose rounding depends on it).
@@ -35,8 +39,25 @@
 
 namespace euler {
 
-// `xc` is an opaque pointer for callers; here it carries the C-ABI plan.
-static inline elb_conv_t *plan_of(eld_conv_t &d) { return reinterpret_cast<elb_conv_t *>(d.xc); }
+// `xc` is an opaque pointer for callers; here it carries the C-ABI plan (one GPU) or the
+// minibatch-split plan (EULER_GPUS > 1).
+struct host_plan {
+  elb_conv_t *single = nullptr;
+  elb_conv_multi_t *multi = nullptr;
+};
+static inline host_plan *plan_of(eld_conv_t &d) { return reinterpret_cast<host_plan *>(d.xc); }
+static void drop_plan(eld_conv_t &d) {
+  host_plan *h = plan_of(d);
+  if (h == nullptr) return;
+  if (h->single) elb_conv_destroy(h->single);      // waits for asynchronous calls still in flight
+  if (h->multi) elb_conv_multi_destroy(h->multi);
+  delete h;
+  d.xc = nullptr;
+}
+static int gpus_from_env() {
+  const char *e = getenv("EULER_GPUS");
+  return e ? atoi(e) : 1;
+}
 
 static void to_c_desc(const eld_conv_t &s, elb_conv_desc_t &d) {
   std::memset(&d, 0, sizeof(d));
@@ -64,10 +85,8 @@ static void to_c_desc(const eld_conv_t &s, elb_conv_desc_t &d) {
   d.device = -1;      // the calling thread's current CUDA device
 }
 
-static void report(const char *where) {
-  const char *v = getenv("EULER_VERBOSE");
-  if (v && atoi(v) > 0) fprintf(stderr, "euler-b200: %s: %s\n", where, elb_last_error());
-}
+// (the C-ABI layer has already logged the message under EULER_LOG_LEVEL; nothing to add here)
+static void report(const char *) {}
 
 eld_conv_t::eld_conv_t() {
   std::memset(&dims, 0, sizeof(dims));
@@ -106,14 +125,11 @@ eld_conv_t::eld_conv_t() {
   xc = nullptr;
 }
 
-eld_conv_t::~eld_conv_t() {
-  if (xc != nullptr) elb_conv_destroy(plan_of(*this));
-  xc = nullptr;
-}
+eld_conv_t::~eld_conv_t() { drop_plan(*this); }
 
 int eld_conv_t::setup(bool fully_setup) {
   // a stale plan is dropped (the reference overwrites xc and leaks it, src/eld_conv.cpp:141)
-  if (xc != nullptr) { elb_conv_destroy(plan_of(*this)); xc = nullptr; }
+  drop_plan(*this);
   // undefined formats get the reference's defaults, visibly, in the descriptor (src/eld_conv.cpp:77-86)
   if (formats.input == format_undef) formats.input = (dims.g == 1 && dims.ic / dims.g < 16) ? nchw : nChw16c;
   if (formats.weights == format_undef) formats.weights = dims.g == 1 ? hwio : ghwio;
@@ -130,19 +146,29 @@ int eld_conv_t::setup(bool fully_setup) {
   algorithm = info.algorithm;
   tile_size = info.tile_size;
   if (!fully_setup) return ELD_OK;                 // src/eld_conv.cpp:161-163
-  elb_conv_t *plan = nullptr;
-  rc = elb_conv_create(&d, &plan);
-  if (rc != ELB_OK) { report("setup"); return rc; }
-  xc = reinterpret_cast<elx_conv_t *>(plan);
+  host_plan *h = new host_plan();
+  const int gpus = gpus_from_env();
+  if (gpus > 1 && dims.n >= 2) rc = elb_conv_multi_create(&d, nullptr, gpus, &h->multi);
+  else rc = elb_conv_create(&d, &h->single);
+  if (rc != ELB_OK) { delete h; report("setup"); return rc; }
+  if (h->single) elb_conv_set_name(h->single, name.c_str());
+  xc = reinterpret_cast<elx_conv_t *>(h);
   return ELD_OK;
 }
 
 int elx_conv(eld_conv_t &desc, void *output, void *input, void *weights, void *bias) {
   if (desc.xc == nullptr || output == nullptr || input == nullptr) return ELX_GENERAL_ERROR;   // src/elx_conv.cpp:218-222
-  // eager_mode = true and stream_sync = true both mean "return when the result is there"; the
-  // reference's asynchronous mode (one global worker thread) has no counterpart that would be
-  // observable through this interface, so every call completes before it returns.
-  const int rc = elb_conv_execute(plan_of(desc), output, input, weights, bias);
+  host_plan *h = plan_of(desc);
+  int rc;
+  if (h->multi) {
+    rc = elb_conv_multi_execute(h->multi, output, input, weights, bias);
+  } else if (desc.eager_mode) {
+    rc = elb_conv_execute(h->single, output, input, weights, bias);
+  } else {
+    // src/elx_conv.cpp:228-236: submit, and wait only when stream_sync is set
+    rc = elb_conv_execute_async(h->single, output, input, weights, bias);
+    if (rc == ELB_OK && desc.stream_sync) rc = elb_conv_wait(h->single);
+  }
   if (rc != ELB_OK) report("elx_conv");
   return rc;
 }

@@ -4,8 +4,9 @@
  * This is the boundary a host-language binding (C++, ctypes, cgo, JNI ...) talks to.  It carries
  * the same information as the reference's C++ descriptor `euler::eld_conv_t` and the same two-step
  * protocol (describe + set up once, then execute many times), but with plain C types only: no
- * std::string, no C++ classes, no torch types.  `include/euler.hpp` in this repository implements
- * the reference's C++ surface (eld_conv_t::setup / elx_conv) on top of these functions.
+ * std::string, no C++ classes, no torch types.  The C++ host library (host/euler_host.cpp, built
+ * against the reference's own include/euler.hpp) implements the reference's C++ surface
+ * (eld_conv_t::setup / elx_conv / reorder<>) on top of these functions.
  *
  * Each entry point names the reference interface it replaces (file:line in the reference project).
  *
@@ -13,6 +14,20 @@
  * passed to elb_conv_enqueue must be device memory of the plan's device.  Tensor layouts are the
  * reference's blocked layouts: nChw16c activations, OIhw16i16o weights (goihw for depthwise),
  * fp32 bias of ALIGNUP(oc,16) elements.
+ *
+ * Environment variables the library reads:
+ *   EULER_VERBOSE=1     one "euler-perf, ..." line per executed convolution on stdout, in the
+ *                       reference's format (src/elx_conv.cpp:190-211, src/el_init.cpp:18-22)
+ *   EULER_LOG_LEVEL=n   lowest severity printed (1 trace .. 5 error; default 3 = info), as
+ *                       src/el_init.cpp:24-27; messages go to stderr
+ *   EULER_GPUS=G        elb_conv_multi_create without a device list: split over GPUs 0..G-1
+ *   ELB_HOST_CHUNKS=k   elb_conv_execute with host tensors: cut the batch into k chunks
+ *   ELB_I8_CTA2=1, ELB_WINO_CTA2=1   run the tcgen05 kernels on pairs of CTAs (cta_group::2); measured
+ *                       not faster than single CTAs, kept as a tested option
+ *   ELB_FORCE_SIMT=1, ELB_F32_NO_FLAT=1   select the CUDA-core int8 kernel / the three-kernel fp32
+ *                       direct path where the tcgen05 single-kernel path would run (used by the tests
+ *                       to cover both)
+ * Nothing else in the environment changes which kernel runs.
  */
 #ifndef EULER_B200_H_
 #define EULER_B200_H_
@@ -124,6 +139,22 @@ ELB_API int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, 
 ELB_API int elb_conv_enqueue(elb_conv_t *plan, void *output, const void *input, const void *weights,
                              const void *bias, void *cuda_stream);
 
+/* elx_conv with eager_mode = false (src/elx_conv.cpp:228-236): the same work as elb_conv_execute,
+ * host or device tensors, but the call returns once the copies and kernels are enqueued on the
+ * plan's own streams -- the counterpart of the reference handing the call to its worker thread
+ * (src/elx_stream.cpp:54-62).  Calls on one plan run in submission order.  Host tensors must stay
+ * valid, and the output must not be read, until elb_conv_wait returns. */
+ELB_API int elb_conv_execute_async(elb_conv_t *plan, void *output, const void *input, const void *weights,
+                                   const void *bias);
+
+/* Wait for every elb_conv_execute_async issued on this plan -- stream_sync = true
+ * (src/elx_conv.cpp:234-235, src/elx_stream.cpp:95-98).  Returns ELB_GENERAL_ERROR when a kernel of
+ * one of those calls gave up a bounded wait. */
+ELB_API int elb_conv_wait(elb_conv_t *plan);
+
+/* eld_conv_t::name (include/euler.hpp:172): the label of this convolution in the euler-perf line. */
+ELB_API int elb_conv_set_name(elb_conv_t *plan, const char *name);
+
 /* Do the first-call weight preparation now -- the `setup_workspace` step of the reference
  * (src/elx_conv.hpp:130-145) made explicit so that callers can keep it out of a timed region. */
 ELB_API int elb_conv_prepare(elb_conv_t *plan, const void *weights, const void *bias);
@@ -142,6 +173,16 @@ ELB_API int elb_conv_device_status(elb_conv_t *plan);
  * output transform) on every following call; NULL switches it off.  Must be off during CUDA
  * graph capture. */
 ELB_API int elb_conv_set_stage_events(elb_conv_t *plan, void **cuda_events4);
+
+/* Debug hook, no counterpart in the reference: per-CTA timeline of the tcgen05 kernels (SM cycle
+ * counter), 64 int64 slots per CTA in caller DEVICE memory; NULL switches it off. */
+ELB_API int elb_conv_set_trace(elb_conv_t *plan, void *device_int64);
+
+/* Self test of the bounded waits, no counterpart in the reference: a one-CTA kernel waits on a
+ * barrier nobody arrives at, gives up after limit_ns and returns normally.  Returns the status word
+ * it wrote (104 = gave up as designed), or a negative number when the test could not run.
+ * device = -1: the current device. */
+ELB_API int elb_selftest_bounded_wait(int device, unsigned long long limit_ns);
 
 /* Number of kernels this plan has launched since it was created. */
 ELB_API uint64_t elb_conv_launch_count(const elb_conv_t *plan);
@@ -183,6 +224,59 @@ ELB_API int elb_reorder(void *dst, int dst_format, const void *src, int src_form
 ELB_API int elb_subsample_nChw16c(void *dst, const void *src, int n, int c, int h, int w, int step_h,
                                   int step_w, int elem_bytes, void *cuda_stream);
 
+/* ---- A chain of convolutions that stays on the device --------------------------------------
+ * Replaces the layer-to-layer modes of the reference's harness (tests/elt_conv.cpp:399-410:
+ * --output_as_input feeds a layer's output tensor to the next call, --dbuffering alternates two
+ * buffer sets): layer k's output is layer k+1's input, u8 between int8 layers, fp32 between fp32
+ * layers; subsample_after[k] = s > 1 keeps every s-th row and column of layer k's output (the
+ * stride-2 stand-in for pooling between the stages of VGG-16).  All descriptors name the same batch
+ * n, nChw16c activations and one device (descs[0].device). */
+typedef struct elb_stack elb_stack_t;
+ELB_API int elb_stack_create(const elb_conv_desc_t *descs, const int32_t *subsample_after, int n_layers,
+                             elb_stack_t **stack);
+/* Weights and bias of one layer (read once, like the first elx_conv of that layer). */
+ELB_API int elb_stack_prepare(elb_stack_t *stack, int layer, const void *weights, const void *bias);
+/* Enqueue the chain for one batch of n images on cuda_stream; DEVICE pointers; does not wait.
+ * May be captured into a CUDA graph by the caller. */
+ELB_API int elb_stack_enqueue(elb_stack_t *stack, void *output, const void *input, void *cuda_stream);
+/* Run `images` images (a multiple of n) and wait.  Host or device tensors.  Host tensors go through
+ * two staging slots: the copy in of batch b+1, the chain of batch b (one CUDA graph launch) and the
+ * copy out of batch b-1 overlap. */
+ELB_API int elb_stack_execute(elb_stack_t *stack, void *output, const void *input, int64_t images);
+/* The plan of one layer (owned by the stack): for elb_conv_info, launch counts, stage events. */
+ELB_API int elb_stack_layer(elb_stack_t *stack, int layer, elb_conv_t **plan);
+/* Device address and size of layer k's output tensor inside the stack (nChw16c, the whole batch;
+ * before any subsample): what the reference's harness would hand to the next call.  Valid until the
+ * stack is destroyed; read it only after the run that wrote it has finished.  NULL for the last
+ * layer when its output goes straight to the caller's tensor. */
+ELB_API int elb_stack_layer_output(elb_stack_t *stack, int layer, void **device_ptr, uint64_t *bytes);
+/* Measurement hook, no counterpart in the reference: n_layers + 1 cudaEvent_t handles recorded
+ * before every layer and after the last one by elb_stack_enqueue; NULL switches it off (it must be
+ * off during stream capture and for elb_stack_execute on host tensors). */
+ELB_API int elb_stack_set_layer_events(elb_stack_t *stack, void **cuda_events, int count);
+/* Layer count and the byte sizes of one batch of the first input and the last output. */
+ELB_API int elb_stack_sizes(const elb_stack_t *stack, int32_t *n_layers, uint64_t *bytes_input, uint64_t *bytes_output);
+ELB_API uint64_t elb_stack_launch_count(const elb_stack_t *stack);
+ELB_API void elb_stack_destroy(elb_stack_t *stack);
+
+/* ---- One convolution, minibatch split over the GPUs of one box ------------------------------
+ * The reference spreads images / tiles over the OpenMP threads of one process
+ * (src/elx_conv_wino_xopt.hpp:41-64, src/elx_int8_conv_direct_1x1_xopt.hpp:91-97); here GPU r takes
+ * images [r*N/G, (r+1)*N/G) of ONE host tensor.  Every GPU prepares its own copy of the weights on
+ * the first call; nothing is exchanged between GPUs, so the result is bit-identical to the
+ * one-GPU result.  devices = NULL: GPUs 0..G-1 with G = n_devices if > 0, else EULER_GPUS, else all
+ * visible GPUs. */
+typedef struct elb_conv_multi elb_conv_multi_t;
+ELB_API int elb_conv_multi_create(const elb_conv_desc_t *desc, const int32_t *devices, int n_devices,
+                                  elb_conv_multi_t **multi);
+/* elx_conv on host tensors of all N images; returns when every slab is back in `output`. */
+ELB_API int elb_conv_multi_execute(elb_conv_multi_t *multi, void *output, const void *input, const void *weights,
+                                   const void *bias);
+/* How the batch was split: in: *n_parts = capacity of the arrays; out: *n_parts = GPUs used. */
+ELB_API int elb_conv_multi_parts(const elb_conv_multi_t *multi, int32_t *n_parts, int32_t *devices,
+                                 int32_t *first_image, int32_t *image_count);
+ELB_API void elb_conv_multi_destroy(elb_conv_multi_t *multi);
+
 /* FP32 Winograd F(4x4,3x3) convolution that allocates nothing -- no counterpart in the reference.
  *
  * For callers that may not allocate device memory at the point where they run a convolution (a
@@ -206,6 +300,13 @@ ELB_API int elb_subsample_nChw16c(void *dst, const void *src, int n, int c, int 
  * attribute; issue it once before any CUDA stream capture starts. */
 ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, void *output, const void *input,
                                       const void *weights, const void *bias, void *cuda_stream);
+
+/* Verdict of the last elb_wino_f32_conv_noalloc on the current device -- no counterpart in the
+ * reference.  The kernels' waits are bounded; one that gives up leaves a code in the first word of
+ * the static array, and the output of that call is invalid.  0 = ok, > 0 = the code, -1 = the
+ * entry point has not run on this device (or the read failed).  Call it after synchronising the
+ * stream the convolution ran on; it copies four bytes to the host and allocates nothing. */
+ELB_API int elb_wino_f32_noalloc_status(void);
 
 #ifdef __cplusplus
 }

@@ -35,6 +35,13 @@ def cases():
         C("g_i8_3x3_s1", 1, 32, 32, 12, 12, algo="direct", **i8),
         C("g_i8_3x3_s2", 1, 32, 32, 14, 14, stride=2, algo="direct", **i8),
         C("g_i8_3x3_c3_shape", 1, 128, 256, 56, 56, stride=2, algo="direct", **i8),
+        # non-zero input zero point WITH padding: border pixels see fewer taps, so their shift differs
+        # (the reference's per-position tables, src/elx_int8_conv_direct.cpp:227-423)
+        C("g_i8_3x3_s1_iz128", 1, 32, 32, 12, 12, algo="direct", iz=128.0, oscale=0.3, **i8),
+        C("g_i8_3x3_s2_iz128", 2, 32, 48, 14, 14, stride=2, algo="direct", iz=128.0, oscale=0.3, **i8),
+        C("g_i8_5x5_iz", 1, 32, 32, 14, 14, kh=5, kw=5, pad=2, algo="direct", iz=3.0, oscale=0.5, **i8),
+        C("g_i8_7x7_s2_iz_s8", 1, 32, 32, 28, 28, kh=7, kw=7, pad=3, stride=2, algo="direct", types="u8f32s8f32",
+          bias=True, iz=17.0, oscale=0.5),
         C("g_wino_f32", 1, 32, 32, 12, 12, types="fp32", algo="wino", tile=6, relu=True, bias=True),
         C("g_wino_f32_partial", 1, 16, 16, 10, 7, types="fp32", algo="wino", tile=6, bias=True),
         C("g_wino_f32_sum", 1, 16, 32, 8, 8, types="fp32", algo="wino", tile=6, bias=True, sum=True),

@@ -48,9 +48,46 @@ def make_desc(case: ConvCase, device: int = -1):
     return d
 
 
+GUARD_BYTES = 4096          # poisoned band on either side of a guarded device tensor
+GUARD_BYTE = 0xA5
+
+
+class Guarded:
+    """A device tensor with a poisoned band in front of it and behind it.  compute-sanitizer is not
+    available to these tests, so every output (and accumulator dump) the GPU tests hand to the
+    library lies between two bands of 0xA5 bytes that must still be intact afterwards: a kernel
+    that writes outside the tensor it was given fails the test that ran it."""
+
+    def __init__(self, init: np.ndarray):
+        import torch
+        self.nbytes = init.nbytes
+        pad = (-self.nbytes) % 256
+        self.raw = torch.full((GUARD_BYTES + self.nbytes + pad + GUARD_BYTES,), GUARD_BYTE, dtype=torch.uint8, device="cuda")
+        self.dtype, self.shape = init.dtype, init.shape
+        self.view_u8 = self.raw[GUARD_BYTES:GUARD_BYTES + self.nbytes]
+        self.view_u8.copy_(torch.from_numpy(np.ascontiguousarray(init).view(np.uint8).reshape(-1)))
+
+    def data_ptr(self) -> int:
+        return self.view_u8.data_ptr()
+
+    def numpy(self) -> np.ndarray:
+        return self.view_u8.cpu().numpy().view(self.dtype).reshape(self.shape)
+
+    def check(self, what: str = "output"):
+        import torch
+        torch.cuda.synchronize()
+        front = self.raw[:GUARD_BYTES]
+        back = self.raw[GUARD_BYTES + self.nbytes:]
+        bad_f = int((front != GUARD_BYTE).sum().item())
+        bad_b = int((back != GUARD_BYTE).sum().item())
+        assert bad_f == 0 and bad_b == 0, (f"{what}: {bad_f} bytes in front of the tensor and {bad_b} behind it were "
+                                           "overwritten (out-of-bounds write)")
+
+
 def run_gpu(case: ConvCase, t: dict, host_buffers: bool = False, want_acc: bool = False, acc_shape=None,
             repeat: int = 1):
-    """Run one case through elx_conv.  Returns (output ndarray, desc[, acc ndarray])."""
+    """Run one case through elx_conv.  Returns (output ndarray, desc[, acc ndarray]).  Device
+    outputs and accumulator dumps are guarded (see Guarded)."""
     import torch
     E = package()
     d = make_desc(case)
@@ -61,8 +98,8 @@ def run_gpu(case: ConvCase, t: dict, host_buffers: bool = False, want_acc: bool 
         out_np[...] = t["residual"]
     acc_t = None
     if want_acc:
-        acc_t = torch.zeros(acc_shape or out_shape(case), dtype=torch.int32, device="cuda")
-        d.set_accumulator_dump(acc_t)
+        acc_t = Guarded(np.zeros(acc_shape or out_shape(case), dtype=np.int32))
+        d.set_accumulator_dump(acc_t.data_ptr())
     if host_buffers:
         for _ in range(repeat):
             if case.sum:
@@ -75,11 +112,12 @@ def run_gpu(case: ConvCase, t: dict, host_buffers: bool = False, want_acc: bool 
         w = torch.from_numpy(t["weights"]).cuda()
         b = torch.from_numpy(t["bias"]).cuda()
         for _ in range(repeat):
-            o = torch.from_numpy(out_np).cuda()
-            rc = E.elx_conv(d, o, x, w, b)
+            o = Guarded(out_np)
+            rc = E.elx_conv(d, o.data_ptr(), x, w, b)
             assert rc == E.ELX_OK, f"elx_conv rc={rc}: {E.last_error()}"
-        torch.cuda.synchronize()
-        res = o.cpu().numpy()
+            o.check(f"{case.name}: output tensor")
+        res = o.numpy()
     if want_acc:
-        return res, d, acc_t.cpu().numpy()
+        acc_t.check(f"{case.name}: accumulator dump")
+        return res, d, acc_t.numpy()
     return res, d

@@ -1,0 +1,189 @@
+"""The VGG-16 convolution stack as a test / benchmark workload: layer table, seeded weights and
+inputs, the stack object of the library, the u8 calibration pass and the CPU chain it is checked
+against.  TEST INFRASTRUCTURE (imports refutil, the door to oracle/); bench.py uses it for its
+c5 / c5i8 workloads."""
+from __future__ import annotations
+
+import dataclasses
+import importlib
+
+PKG = "deep-learning-math-kernel-research_b200"
+
+
+def oracle_fn(case):
+    """The C restatement that matches a case."""
+    import refutil as R
+    if case.types == "fp32":
+        return R.oracle_wino_f32 if case.algo == "wino" else R.oracle_direct_f64
+    if case.algo == "wino":
+        return R.oracle_int8_wino
+    return R.oracle_int8_depthwise if case.g > 1 else R.oracle_int8_conv
+
+
+VGG16 = [(3, 64, 224), (64, 64, 224), "pool", (64, 128, 112), (128, 128, 112), "pool", (128, 256, 56),
+         (256, 256, 56), (256, 256, 56), "pool", (256, 512, 28), (512, 512, 28), (512, 512, 28), "pool",
+         (512, 512, 14), (512, 512, 14), (512, 512, 14)]
+VGG_NAMES = ["conv1_1", "conv1_2", "conv2_1", "conv2_2", "conv3_1", "conv3_2", "conv3_3", "conv4_1", "conv4_2",
+             "conv4_3", "conv5_1", "conv5_2", "conv5_3"]
+
+
+def vgg_layers():
+    """[(ic, oc, hw, subsample_after)] of the 13 convolutions."""
+    out = []
+    for item in VGG16:
+        if item == "pool":
+            out[-1] = out[-1][:3] + (2,)
+        else:
+            out.append(item + (1,))
+    return out
+
+
+def vgg_layer_case(idx, ic, oc, hw, n, int8, iscale=1.0, oscale=1.0):
+    import refutil as R
+    if int8:
+        return R.ConvCase(f"vgg_{VGG_NAMES[idx]}", n, ic, oc, hw, hw, types="u8f32u8f32", algo="direct", relu=True,
+                          bias=True, iscale=iscale, oscale=oscale,
+                          knobs=dict(blk_i=max(1, R.alignup(ic) // 16), blk_o=1, flt_o=1, flt_t=min(hw, 14)))
+    return R.ConvCase(f"vgg_{VGG_NAMES[idx]}", n, ic, oc, hw, hw, types="fp32", algo="wino", tile=6, relu=True, bias=True)
+
+
+def vgg_weights(idx, ic, oc):
+    """He-initialised fp32 weights N(0, sqrt(2/(9*ic))) and bias U[-0.1, 0.1], seeded per layer."""
+    import numpy as np
+    import refutil as R
+    g = np.random.Generator(np.random.Philox(R.seed_for("vgg16", VGG_NAMES[idx])))
+    w = (g.standard_normal((oc, ic, 3, 3)) * np.sqrt(2.0 / (9 * ic))).astype(np.float32)
+    b = np.zeros(R.alignup(oc), np.float32)
+    b[:oc] = g.uniform(-0.1, 0.1, oc).astype(np.float32)
+    return R.weights_buffer(R.to_OIhw16i16o(w)), b
+
+
+def vgg_input(chunk: int, n: int, int8: bool):
+    """Blocked network input of chunk `chunk` (n images): 3 channels zero-padded to 16 (fp32 U[-1,1] / u8 U[0,255])."""
+    import numpy as np
+    import refutil as R
+    g = np.random.Generator(np.random.Philox(R.seed_for("vgg16", f"input{chunk}")))
+    if int8:
+        x = g.integers(0, 256, (n, 3, 224, 224), dtype=np.uint8)
+    else:
+        x = g.uniform(-1.0, 1.0, (n, 3, 224, 224)).astype(np.float32)
+    return R.to_nChw16c(x)
+
+
+def build_stack(n, int8, device, scales=None):
+    """The 13 convolutions as ONE stack object of the library (elb_stack_*), weights prepared."""
+    import torch
+    import gpuutil as G
+    E = importlib.import_module(PKG)
+    layers = vgg_layers()
+    descs, cases = [], []
+    for k, (ic, oc, hw, _) in enumerate(layers):
+        isc, osc = (scales[k], scales[k + 1]) if int8 else (1.0, 1.0)
+        case = vgg_layer_case(k, ic, oc, hw, n, int8, isc, osc)
+        descs.append(G.make_desc(case, device=device))
+        cases.append(case)
+    st = E.ConvStack(descs, [l[3] for l in layers])
+    for k, (ic, oc, _, _) in enumerate(layers):
+        w, b = vgg_weights(k, ic, oc)
+        wd, bd = torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+        rc = st.prepare(k, wd, bd)
+        if rc != 0:
+            raise RuntimeError(f"prepare of {cases[k].name} failed rc={rc}: {E.last_error()}")
+    torch.cuda.synchronize()
+    return st, cases
+
+
+def device_view(ptr, nbytes, dtype):
+    """A torch view of device memory owned by the library."""
+    import torch
+
+    class _Mem:
+        pass
+    m = _Mem()
+    m.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+    return torch.as_tensor(m, device="cuda").view(dtype)
+
+
+def vgg_calibrate(device):
+    """Per-tensor u8 scales of the INT8 stack, frozen before anything is timed: the fp32 stack runs
+    once on two images of de-quantised input (scale 1/255) and every layer's scale is its largest
+    activation / 255 (zero points are 0: activations are post-ReLU)."""
+    import torch
+    st, cases = build_stack(2, False, device)
+    x = torch.from_numpy(vgg_input(0, 2, True)).cuda().to(torch.float32) * (1.0 / 255.0)
+    last = cases[-1]
+    y = torch.zeros((2, last.oc // 16, last.oh, last.ow, 16), dtype=torch.float32, device="cuda")
+    s = torch.cuda.current_stream()
+    assert st.enqueue(y, x, s.cuda_stream) == 0
+    torch.cuda.synchronize()
+    scales = [1.0 / 255.0]
+    for k in range(len(cases)):
+        ptr, nb = st.layer_output(k)
+        v = y if ptr is None else device_view(ptr, nb, torch.float32)
+        scales.append(float(v.max().item()) / 255.0)
+    st.close()
+    return scales
+
+
+def stack_reference_chain(cases, x_np, int8, keep=None):
+    """The chain on the CPU: every layer through the reference's library (the C restatement where
+    it cannot run), the harness keeping every second row / column behind the pooled layers.
+    keep: optional list that receives every layer's output (before the subsample)."""
+    import numpy as np
+    import refutil as R
+    x = x_np
+    layers = vgg_layers()
+    kind = "reference" if R.reference_available() else "port"
+    for k, case in enumerate(cases):
+        c = dataclasses.replace(case, n=x.shape[0])
+        w, b = vgg_weights(k, c.ic, c.oc)
+        t = {"input": np.ascontiguousarray(x), "weights": w, "bias": b}
+        if kind == "reference":
+            y, _ = R.run_reference(c, t)
+        else:
+            y = oracle_fn(c)(c, t)
+        if keep is not None:
+            keep.append(y)
+        if layers[k][3] == 2:
+            y = np.ascontiguousarray(y[:, :, ::2, ::2, :])
+        x = y
+    return x, kind
+
+
+def stack_layer_outputs(st, cases, y_last, images=None):
+    """Every layer's output tensor (before its subsample) as the stack holds it after a run:
+    numpy arrays [images][OC/16][oh][ow][16]; y_last is the caller's tensor of the last layer."""
+    import numpy as np
+    import torch
+    import refutil as R
+    outs = []
+    for k, c in enumerate(cases):
+        dt = torch.uint8 if c.out_dtype == np.uint8 else torch.float32
+        ptr, nb = st.layer_output(k)
+        v = y_last if ptr is None else device_view(ptr, nb, dt)
+        v = v.reshape(c.n, R.alignup(c.oc) // 16, c.oh, c.ow, 16)
+        outs.append(v[:images].cpu().numpy() if images else v.cpu().numpy())
+    return outs
+
+
+def per_layer_parity(cases, x_np, gpu_outs, int8):
+    """Each layer against the CPU library ON THE GPU'S OWN INPUT of that layer (the previous GPU
+    output, subsampled on the host where the stack subsamples): isolates one layer's error from
+    what the layers before it accumulated, and still catches any slip in how the layers are wired
+    (scale, layout, subsample).  Returns (per-layer figures, comparand): fp32 rel-L2, int8 the
+    number of differing bytes."""
+    import numpy as np
+    import refutil as R
+    layers = vgg_layers()
+    kind = "reference" if R.reference_available() else "port"
+    figures = []
+    x = x_np
+    for k, case in enumerate(cases):
+        c = dataclasses.replace(case, n=x.shape[0])
+        w, b = vgg_weights(k, c.ic, c.oc)
+        t = {"input": np.ascontiguousarray(x), "weights": w, "bias": b}
+        want = R.run_reference(c, t)[0] if kind == "reference" else oracle_fn(c)(c, t)
+        got = gpu_outs[k]
+        figures.append(int((got != want).sum()) if int8 else R.rel_l2(got, want))
+        x = got[:, :, ::2, ::2, :] if layers[k][3] == 2 else got
+    return figures, kind

@@ -54,6 +54,22 @@ BOX_CASES = [
 ]
 
 
+# Non-zero input zero point together with padding: padded taps contribute nothing (not z), so the
+# zero-point correction of a border pixel covers only the taps inside the image and its shift differs
+# from an interior pixel's (the reference's per-position tables, src/elx_int8_conv_direct.cpp:227-423).
+ZP_CASES = [
+    _case("zp_3x3_s1_128", 2, 32, 64, 14, 14, algo="direct", iz=128.0, oscale=0.3),
+    _case("zp_3x3_s2_odd", 1, 48, 32, 15, 9, stride=2, algo="direct", iz=128.0, oscale=0.3),
+    _case("zp_5x5", 1, 16, 32, 12, 12, kh=5, kw=5, pad=2, algo="direct", iz=3.0, oscale=0.5),
+    _case("zp_7x7_s2_s8", 1, 32, 32, 28, 28, kh=7, kw=7, pad=3, stride=2, algo="direct", types="u8f32s8f32", relu=False,
+          iz=17.0, oscale=0.5),
+    _case("zp_tiny_2x2", 3, 16, 16, 2, 2, algo="direct", iz=100.0, oscale=0.2),      # no pixel sees all nine taps
+    _case("zp_f32_out", 1, 32, 32, 9, 9, algo="direct", types="u8f32f32f32", iz=64.0),
+    _case("zp_sum", 1, 32, 32, 10, 10, algo="direct", iz=128.0, oscale=0.5, sum=True, sscale=0.5, sz=3.0),
+    _case("zp_c3_shape", 2, 128, 256, 56, 56, stride=2, algo="direct", iz=128.0, oscale=0.4),
+]
+
+
 def _check(case, kernel_expected=None, host_buffers=False, tensors=None):
     import gpuutil as G
     t = tensors if tensors is not None else R.make_tensors(case)
@@ -106,7 +122,13 @@ def test_accumulators_beyond_2_pow_22(pkg, case):
     _check(case, tensors=t)
 
 
-@pytest.mark.parametrize("case", [FLAT_CASES[1], FLAT_CASES[3], BOX_CASES[0], BOX_CASES[3]], ids=lambda c: c.name)
+@pytest.mark.parametrize("case", ZP_CASES, ids=lambda c: c.name)
+def test_int8_zero_point_with_padding(pkg, case):
+    _check(case, "i8_conv_umma")
+
+
+@pytest.mark.parametrize("case", [FLAT_CASES[1], FLAT_CASES[3], BOX_CASES[0], BOX_CASES[3], ZP_CASES[0], ZP_CASES[4]],
+                         ids=lambda c: c.name)
 def test_int8_simt_matches_oracle(pkg, case, monkeypatch):
     monkeypatch.setenv("ELB_FORCE_SIMT", "1")
     _check(case, "i8_simt")

@@ -1,6 +1,7 @@
 """Multi-rank behaviour on CPU (gloo, world_size 2): the path shards by image with replicated
-weights and no exchange, so the only cross-rank logic is (a) the max-over-ranks of the timings and
-the aggregate throughput, (b) the reference arm running on rank 0 alone."""
+weights and no exchange, so the only cross-rank logic is (a) which images of the global minibatch a
+rank owns, (b) the max-over-ranks of the timings and the whole-job throughput, (c) the reference
+arm running on rank 0 alone."""
 import json
 import os
 import subprocess
@@ -18,10 +19,17 @@ import torch, torch.distributed as dist
 import bench
 dist.init_process_group("gloo")
 rank = dist.get_rank()
+world = dist.get_world_size()
 ms, e2e = bench.max_over_ranks([10.0 + rank * 5.0, 100.0 - rank], dist, device="cpu")
-val = bench.aggregate_throughput(ops=2_000_000_000, ms_per_step=ms, world=dist.get_world_size())
+val = bench.throughput(2_000_000_000, ms)
+# every rank's share of a global batch of 7 images (odd on purpose) and of the 8 chunks of the stack
+first, count = bench.split_batch(7, world, rank)
+mine = torch.zeros(7, dtype=torch.int64)
+mine[first:first + count] = 1
+dist.all_reduce(mine)
+c_first, c_count = bench.split_batch(8, world, rank)
 if rank == 0:
-    print(json.dumps({{"ms": ms, "e2e": e2e, "value": val}}))
+    print(json.dumps({{"ms": ms, "e2e": e2e, "value": val, "owners": mine.tolist(), "chunks0": [c_first, c_count]}}))
 dist.destroy_process_group()
 """
 
@@ -41,13 +49,15 @@ def test_max_over_ranks_and_aggregate(tmp_path):
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
     out = json.loads(line)
     assert out["ms"] == 15.0 and out["e2e"] == 100.0           # max over the two ranks
-    # two ranks, each the full batch (weak scaling): 2 * ops / time
-    assert abs(out["value"] - 2 * 2e9 / 15e-3 / 1e12) < 1e-9
+    # the global batch's op count over the slowest rank's time (strong scaling: the batch is split)
+    assert abs(out["value"] - 2e9 / 15e-3 / 1e12) < 1e-9
+    assert out["owners"] == [1] * 7            # every image has exactly one owner
+    assert out["chunks0"] == [0, 4]
 
 
 @pytest.mark.skipif(not (ROOT / "oracle" / "_ref" / "ref_driver").exists(), reason="reference build missing")
 def test_reference_arm_runs_on_rank0_only():
-    r = _torchrun(["bench.py", "--impl", "reference", "--gpus", "2", "--steps", "3", "--warmup", "1"])
+    r = _torchrun(["bench.py", "--impl", "reference", "--workload", "c2", "--gpus", "2", "--steps", "3", "--warmup", "1"])
     assert r.returncode == 0, r.stderr[-2000:]
     lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
     assert len(lines) == 1

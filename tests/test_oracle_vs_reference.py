@@ -26,6 +26,16 @@ def _with_knobs(c):
                sum=True, sscale=0.25, oscale=0.5),
     R.ConvCase("ovr_3x3", 2, 48, 32, 11, 11, types="u8f32u8f32", algo="direct", relu=True, bias=True),
     R.ConvCase("ovr_3x3_s2", 1, 32, 64, 14, 14, stride=2, types="u8f32u8f32", algo="direct", relu=True, bias=True),
+    # non-zero input zero point with padding: the reference's per-position shift tables
+    # (src/elx_int8_conv_direct.cpp:227-423) against the restatement's "sum of q over the taps inside the image"
+    R.ConvCase("ovr_3x3_iz128", 1, 32, 32, 12, 12, types="u8f32u8f32", algo="direct", relu=True, bias=True, iz=128.0,
+               oscale=0.3),
+    R.ConvCase("ovr_3x3_s2_iz128", 1, 32, 32, 14, 14, stride=2, types="u8f32u8f32", algo="direct", relu=True, bias=True,
+               iz=128.0, oscale=0.3),
+    R.ConvCase("ovr_5x5_iz", 1, 32, 32, 14, 14, kh=5, kw=5, pad=2, types="u8f32u8f32", algo="direct", relu=True, bias=True,
+               iz=3.0, oscale=0.5),
+    R.ConvCase("ovr_7x7_s2_iz_s8", 1, 32, 32, 28, 28, kh=7, kw=7, pad=3, stride=2, types="u8f32s8f32", algo="direct",
+               bias=True, iz=17.0, oscale=0.5),
 ], ids=lambda c: c.name)
 def test_int8_direct_bit_exact(case):
     case = _with_knobs(case)
