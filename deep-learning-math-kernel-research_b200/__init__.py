@@ -34,7 +34,7 @@ forward_training, forward_inference, backward_data, backward_weights = range(4)
 FINE, COARSE, CALIBRATED = range(3)
 EL_NO_CALI = 3.4028234663852886e38
 KERNEL_NAMES = {0: "none", 1: "i8_gemm_umma", 2: "i8_conv_umma", 3: "i8_simt", 4: "wino_f32_umma",
-                5: "wino_i8_umma", 6: "i8_depthwise", 7: "f32_direct_umma"}
+                5: "wino_i8_umma", 6: "i8_depthwise", 7: "f32_direct_umma", 8: "f32_small_ic"}
 
 
 def build(verbose: bool = False) -> Path:

@@ -595,6 +595,7 @@ int do_prepare_inner(elb_conv &pl, const void *weights, const void *bias) {
     case ELB_KERNEL_I8_SIMT: rc = prepare_i8_direct(pl, weights, bias); break;
     case ELB_KERNEL_WINO_F32_UMMA:
     case ELB_KERNEL_F32_DIRECT_UMMA:
+    case ELB_KERNEL_F32_SMALL_IC:
     case ELB_KERNEL_WINO_I8_UMMA: {
       std::string err;
       rc = wino_prepare(pl.wino, pl.d, pl.info, weights, bias, err);
@@ -664,6 +665,7 @@ int do_enqueue_range_inner(elb_conv &pl, void *out, const void *in, int n0, int 
     }
     case ELB_KERNEL_WINO_F32_UMMA:
     case ELB_KERNEL_F32_DIRECT_UMMA:
+    case ELB_KERNEL_F32_SMALL_IC:
     case ELB_KERNEL_WINO_I8_UMMA: {
       std::string err;
       int nl = 0;

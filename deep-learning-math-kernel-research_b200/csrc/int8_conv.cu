@@ -241,6 +241,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
     if (lane == 0) {
       constexpr uint32_t IDESC = umma_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b s8*/ 1, BM, BN);
       uint32_t it = 0, tcount = 0;
+      // This loop is ONE thread: every instruction costs its full latency, so the ring slot and its
+      // phase are counters and the operand descriptors are a constant upper half plus the stage's
+      // shared-memory address (measured: divisions and descriptor construction cost this loop more
+      // than issuing the MMAs).
+      int s = 0;
+      uint32_t ph = 0;
+      constexpr uint64_t A_DESC_HI = (static_cast<uint64_t>((BM * 16) >> 4) << 16) | (static_cast<uint64_t>(128 >> 4) << 32) |
+                                     (static_cast<uint64_t>(1) << 46);
+      constexpr uint64_t B_DESC_HI = (static_cast<uint64_t>((BN * 16) >> 4) << 16) | (static_cast<uint64_t>(128 >> 4) << 32) |
+                                     (static_cast<uint64_t>(1) << 46);
+      const uint32_t smem_base = smem_u32(smem);
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
         const uint32_t b = tcount & 1u, tph = (tcount >> 1) & 1u;
@@ -248,26 +259,35 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + b * BN;
         const int ks0 = p.rotate_k ? tile % p.k_stages : 0;      // same rotation as the producer
+        int ks = ks0;
+        // The wait for stage ki + 1 is issued in the MIDDLE of stage ki's MMAs: even on a completed
+        // barrier it costs this thread a few hundred cycles of latency, which the MMAs already queued
+        // in the tensor pipe cover; between the stages it would leave the pipe idle.
+        if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        tc_fence_after_sync();
         for (int ki = 0; ki < p.k_stages; ++ki, ++it) {
-          const int ks = ki + ks0 < p.k_stages ? ki + ks0 : ki + ks0 - p.k_stages;
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-          tc_fence_after_sync();
           if (it < 16) ELB_TRACE(20 + it);
-          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + L::A_BYTES;
+          const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
+          const uint64_t ad0 = A_DESC_HI | (a_addr >> 4), bd0 = B_DESC_HI | ((a_addr + L::A_BYTES) >> 4);
+          int s_next = s + 1;
+          uint32_t ph_next = ph;
+          if (s_next == STAGES) { s_next = 0; ph_next ^= 1u; }
           // K = 32 bytes = two chunks per instruction; the last stage may hold fewer than KC chunks
           const int pairs = (min(KC, p.Q - ks * KC) + 1) >> 1;
 #pragma unroll
           for (int k2 = 0; k2 < KC / 2; ++k2) {
-            if (k2 < pairs) {
-              const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 2 * (BM * 16), BM * 16, 128);
-              const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * (BN * 16), BN * 16, 128);
-              umma_i8(d_tmem, ad, bd, IDESC, (ki | k2) != 0 ? 1u : 0u);
+            if (k2 < pairs)
+              umma_i8(d_tmem, ad0 + ((k2 * 2 * (BM * 16)) >> 4), bd0 + ((k2 * 2 * (BN * 16)) >> 4), IDESC, (ki | k2) != 0 ? 1u : 0u);
+            if (k2 == KC / 4 - 1 && ki + 1 < p.k_stages) {
+              if (!mbar_wait(&full[s_next], ph_next, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
+              tc_fence_after_sync();
             }
           }
+          if (!ok) break;
           umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
+          s = s_next;
+          ph = ph_next;
+          if (++ks == p.k_stages) ks = 0;
         }
         if (ok) umma_commit(&tfull[b]);  // accumulator complete
         if (tcount == 0) ELB_TRACE(40);

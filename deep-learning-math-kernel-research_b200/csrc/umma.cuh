@@ -90,13 +90,12 @@ constexpr uint32_t WAIT_SUSPEND_NS = 20000;     // per try: bounds how late a wa
 // a shared-memory word every role of the CTA polls) if the wait ran out of time or another role
 // already gave up.
 //
-// Barrier operations are a scarce resource: measured on B200, every mbarrier instruction of a CTA
-// goes through one unit that serves them one after the other (a wait on an ALREADY completed
-// barrier took 300-400 cycles while thirteen other threads of the CTA were polling).  So a wait
-// first tests once (the common case in a running pipeline), and only then suspends.
-#ifndef ELB_WAIT_MODE
-#define ELB_WAIT_MODE 0
-#endif
+// Measured on B200 (per-CTA timelines of the GEMM kernel with every role's work switched off): the
+// role loops are single threads, so what a pipeline stage costs them is instruction LATENCY -- a
+// wait on an already completed barrier took 300-400 cycles when it was a polling loop around
+// try_wait plus a cycle-counter read, ~150 as one test.  So a wait first tests once (the common
+// case in a running pipeline) and only then reads the clock and suspends; suspended waiters also
+// keep the issue slots and the shared-memory port free for the roles that have work.
 __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -111,38 +110,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-#if ELB_WAIT_MODE == 0
-  if (mbar_try_wait(bar, parity)) return true;
-#elif ELB_WAIT_MODE == 1
   if (mbar_test_wait(bar, parity)) return true;
-#elif ELB_WAIT_MODE == 2
-  for (int i = 0; i < 64; ++i)
-    if (mbar_test_wait(bar, parity)) return true;
-#elif ELB_WAIT_MODE == 3
-  {
-    const long long t00 = clock64();
-    uint32_t spins = 0;
-    while (true) {
-      if (mbar_try_wait(bar, parity)) return true;
-      if ((++spins & 255u) == 0u) {
-        if (*abort_flag) return false;
-        if (clock64() - t00 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
-      }
-    }
-  }
-#elif ELB_WAIT_MODE == 4
-  {
-    const long long t00 = clock64();
-    uint32_t spins = 0;
-    while (true) {
-      if (mbar_test_wait(bar, parity)) return true;
-      if ((++spins & 255u) == 0u) {
-        if (*abort_flag) return false;
-        if (clock64() - t00 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
-      }
-    }
-  }
-#endif
   // The limit is counted on the SM's own cycle counter: it is a register read, whereas the global
   // nanosecond timer costs a microsecond-scale round trip.
   const long long t0 = clock64();

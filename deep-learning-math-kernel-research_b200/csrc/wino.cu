@@ -501,7 +501,9 @@ struct WinoGemmParams {
   int prefetch;             // a separate warp asks L2 for the A stages one tile ahead
   int rotate_k;             // tiles start their K loop at different stages (spreads the weight reads over L2)
   int spp;                  // pipeline stages a producer warp fills per pass (1 or 2); the two warps alternate passes
-  int a_tmem;               // fp32, single CTAs: A planes in tensor memory and ONE accumulator buffer (see the kernel)
+  int a_tmem;               // fp32, single CTAs: A planes in tensor memory (see the kernel)
+  int stack;                // fp32, single CTAs, BN <= 128: the hi and lo weight rows of a K chunk lie one after the
+                            // other, so hi*[hi;lo] is ONE MMA of 2*BN columns and the 3xTF32 product takes two MMAs
   int ablate;               // -DELB_TUNING builds only: bit mask of pipeline roles switched off to find the bound (results are then wrong)
   const float *bias;
   float *out;
@@ -562,6 +564,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // slots in tensor memory, one per shared-memory stage: 16 columns of tf32 hi + 16 of lo
   constexpr uint32_t A_TMEM_COL0 = MAX_BN;
   const bool a_in_tmem = !CTA2 && p.kind == KIND_F32 && p.a_tmem != 0;
+  // Stacked weights (see WinoGemmParams::stack): the accumulator is 2*BN columns wide, columns
+  // [BN, 2*BN) collect hi*lo and are added to [0, BN) by the epilogue.
+  const bool stack = !CTA2 && p.kind == KIND_F32 && p.stack != 0;
+  const int acc_width = stack ? 2 * BN : BN;
+  // Accumulator buffers: two (the epilogue of a tile overlaps the next tile's MMAs) unless the A
+  // slots in tensor memory leave room for one only: columns [0,256) hold the accumulators (two of at
+  // most 128 columns, or one wider), [256,512) the A slots.
+  const int acc_bufs = (a_in_tmem && acc_width > 128) ? 1 : 2;
+  const uint32_t acc_stride = a_in_tmem ? 128u : static_cast<uint32_t>(MAX_BN);
   // Ring geometry.  A stage holds A (16 KB of hi / lo planes or int8 chunks; only the raw 8 KB when
   // the planes go to tensor memory) and the BN weight rows, so tiles of fewer output channels get a
   // deeper ring: 4 stages at BN = 256 (5 with A in tensor memory), 6 at 128, up to 8 below.
@@ -608,6 +619,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     const uint32_t pw = warp == 0 ? 0u : 1u;
     const int spp = p.spp == 1 ? 1 : 2;
     uint32_t it = 0, gpass = 0;
+    // ring slot / phase of stage `it`, kept as counters (an integer division costs this one-warp loop
+    // more than the copy instructions it issues)
+    int s_base = 0;
+    uint32_t ph_base = 0;
+    auto adv = [&](int n) { s_base += n; if (s_base >= nstages) { s_base -= nstages; ph_base ^= 1u; } };
+    auto back1 = [&]() { if (s_base == 0) { s_base = nstages - 1; ph_base ^= 1u; } else --s_base; };
     bool ok = true;
     if (p.flat) {
       // flat mode: lanes 0..3 / 8..11 fetch the four 16-byte channel chunks of a stage (boxes of
@@ -621,14 +638,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         // CTAs that run side by side multiply by the same weights: each tile starts its K loop at a
         // different stage so that they do not all ask the same L2 lines at the same moment
         const int rot = p.rotate_k ? tile % p.k_stages : 0;
-        for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass) {
+        for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass, adv(spp)) {
           if ((gpass & 1u) != pw) continue;
           const int ks = ks0 + grp;
           const int ksr = ks + rot < p.k_stages ? ks + rot : ks + rot - p.k_stages;     // rotated K stage
           const bool active = grp < spp && gl < 5 && ks < p.k_stages;
-          const uint32_t my_it = it + grp;
-          const int s = my_it % nstages;
-          const uint32_t ph = (my_it / nstages) & 1u;
+          int s = s_base + grp;
+          uint32_t ph = ph_base;
+          if (s >= nstages) { s -= nstages; ph ^= 1u; }
           int w_ok = 1;
           if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
           if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
@@ -641,7 +658,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           }
           __syncwarp();
         }
-        if (spp == 2 && (p.k_stages & 1)) --it;
+        if (spp == 2 && (p.k_stages & 1)) { --it; back1(); }
       }
     }
     const int grp = lane >> 1, gl = lane & 1;      // lanes 0..3 work: stage-in-pass, A / B
@@ -659,16 +676,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
                              (CTA2 ? rank * b_stage_bytes : 0);
       const size_t b_pitch = static_cast<size_t>(CTA2 ? 2 : 1) * b_stage_bytes;
       const int rot = p.rotate_k ? tile % p.k_stages : 0;      // see the flat-mode loop above
-      if (pw == 0 && lane == 0) *tile_started = static_cast<int>(it / p.k_stages);
-      if (pw == 0 && lane == 0 && it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
-      for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass) {
+      if (pw == 0 && lane == 0 && (p.prefetch || p.trace)) {
+        *tile_started = static_cast<int>(it / p.k_stages);
+        if (it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
+      }
+      for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass, adv(spp)) {
         if ((gpass & 1u) != pw) continue;            // the other producer warp's pass
         const int ks = ks0 + grp;
         const int ksr = ks + rot < p.k_stages ? ks + rot : ks + rot - p.k_stages;
         const bool active = grp < spp && ks < p.k_stages;
-        const uint32_t my_it = it + grp;
-        const int s = my_it % nstages;
-        const uint32_t ph = (my_it / nstages) & 1u;
+        int s = s_base + grp;
+        uint32_t ph = ph_base;
+        if (s >= nstages) { s -= nstages; ph ^= 1u; }
         // empty[s] is committed by the MMAs of the stage's previous use, which also implies that the
         // splitter warps are done with raw slot s
         int w_ok = 1;
@@ -690,7 +709,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         __syncwarp();
         if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(24 + gpass / 2);
       }
-      if (spp == 2 && (p.k_stages & 1)) --it;        // the last pass of an odd K loop served one stage only
+      if (spp == 2 && (p.k_stages & 1)) { --it; back1(); }        // the last pass of an odd K loop served one stage only
     }
   } else if (warp == GEMM_PREFETCH_WARP) {
     // -------- optional L2 prefetch of the A operand, one tile ahead of the producers (an experiment:
@@ -718,8 +737,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       bool ok = true;
       for (int tile = first; tile < total_tiles && ok; tile += step) {
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = it % nstages;
-          const uint32_t ph = (it / nstages) & 1u;
+          const int s = static_cast<int>(it % static_cast<uint32_t>(nstages));
+          const uint32_t ph = (it / static_cast<uint32_t>(nstages)) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag) ||
               (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag))) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           mbar_arrive_cluster(mapa_u32(&pfull[s], 0));
@@ -730,34 +749,75 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const uint32_t idesc = p.kind == KIND_F32 ? umma_idesc(1, 2, 2, MM, BN) : umma_idesc(2, 0, 1, MM, BN);
       const uint32_t b_lbo = 16u * BNL;
       uint32_t it = 0, tcount = 0;
+      // This loop is ONE thread: every instruction in it costs its full latency (measured ~330 cycles
+      // per stage for two integer divisions and eight descriptor constructions alone), so the ring
+      // slot and its phase are counters and the descriptors are a constant upper half OR-ed with the
+      // stage's shared-memory address.
+      int s = 0;
+      uint32_t ph = 0;
+      const uint64_t a_desc_hi = umma_desc_kmajor(0, 2048, 128), b_desc_hi = umma_desc_kmajor(0, b_lbo, 128);
+      // stacked weights: a K chunk is [hi rows | lo rows] = 2*BN rows of 16 bytes
+      const uint32_t st_lbo = 32u * BN;
+      const uint64_t st_desc_hi = umma_desc_kmajor(0, st_lbo, 128);
+      const uint32_t idesc2 = umma_idesc(1, 2, 2, MM, 2 * BN);
+      const uint32_t smem_base = smem_u32(smem);
       bool ok = true;
       for (int tile = first; tile < total_tiles && ok; tile += step, ++tcount) {
-        const uint32_t b = a_in_tmem ? 0u : (tcount & 1u), tph = a_in_tmem ? (tcount & 1u) : ((tcount >> 1) & 1u);
+        const uint32_t b = acc_bufs == 1 ? 0u : (tcount & 1u), tph = acc_bufs == 1 ? (tcount & 1u) : ((tcount >> 1) & 1u);
         if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
         tc_fence_after_sync();
         if (tcount < 8) WG_TRACE(8 + tcount);
-        const uint32_t d_tmem = tmem_base + b * MAX_BN;
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = it % nstages;
-          const uint32_t ph = (it / nstages) & 1u;
-          if (it < 6) WG_TRACE2(32 + 3 * it);
-          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-          if (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-          if (CTA2 && !mbar_wait(&pfull[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        const uint32_t d_tmem = tmem_base + b * acc_stride;
+        // The waits for stage ks + 1 are issued BETWEEN the two K steps of stage ks: a wait costs this
+        // thread ~300 cycles of latency even when the barrier has completed, and behind the first K
+        // step's three MMAs (queued in the tensor pipe) that latency is hidden; done between the
+        // stages it left the pipe idle a third of the time (measured timeline, 256-channel layer).
+        auto wait_stage = [&](int st, uint32_t phase) -> bool {
+          if (!mbar_wait(&full[st], phase, abort_flag)) return false;
+          if (p.kind == KIND_F32 && !mbar_wait(&cfull[st], phase, abort_flag)) return false;
+          if (CTA2 && !mbar_wait(&pfull[st], phase, abort_flag)) return false;
           tc_fence_after_sync();
+          return true;
+        };
+        if (!wait_stage(s, ph)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           if (it < 6) WG_TRACE2(33 + 3 * it);
           if (ks == 0 && tcount < 8) WG_TRACE(16 + tcount);
-          const uint32_t a_addr = smem_u32(smem + s * stage_bytes);
+          const uint32_t a_addr = smem_base + s * stage_bytes;
           const uint32_t b_addr = a_addr + b_off;
+          const uint64_t a_desc = a_desc_hi | (a_addr >> 4), b_desc = b_desc_hi | (b_addr >> 4);   // (addresses < 256 KB: 14 bits)
+          int s_next = s + 1;
+          uint32_t ph_next = ph;
+          if (s_next == nstages) { s_next = 0; ph_next ^= 1u; }
+          const bool more = ks + 1 < p.k_stages;
           if (ABL(2)) {
+            if (more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          } else if (stack) {
+            // hi * [hi; lo] in one MMA of 2*BN columns, lo * hi in one of BN columns (same descriptor:
+            // the first BN rows of a chunk are the hi rows)
+            const uint64_t st_desc = st_desc_hi | (b_addr >> 4);
+#pragma unroll
+            for (int k2 = 0; k2 < 2; ++k2) {
+              const uint64_t bst = st_desc + ((k2 * 2 * st_lbo) >> 4);
+              if (a_in_tmem) {
+                const uint32_t t_hi = tmem_base + A_TMEM_COL0 + s * 32 + k2 * 8, t_lo = t_hi + 16;
+                umma_tf32_ts(d_tmem, t_hi, bst, idesc2, (ks | k2) != 0 ? 1u : 0u);
+                umma_tf32_ts(d_tmem, t_lo, bst, idesc, 1u);
+              } else {
+                umma_tf32(d_tmem, a_desc + ((k2 * 4096) >> 4), bst, idesc2, (ks | k2) != 0 ? 1u : 0u);
+                umma_tf32(d_tmem, a_desc + ((8192 + k2 * 4096) >> 4), bst, idesc, 1u);
+              }
+              if (k2 == 0 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
+            }
+            if (!ok) break;
           } else if (p.kind == KIND_F32) {
             // planes: A hi at +0, lo at +8 KB; B hi at +0, lo at +4 chunks.  K step = 2 chunks.
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2) {
-              const uint64_t ahi = umma_desc_kmajor(a_addr + k2 * 4096, 2048, 128);
-              const uint64_t alo = umma_desc_kmajor(a_addr + 8192 + k2 * 4096, 2048, 128);
-              const uint64_t bhi = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
-              const uint64_t blo = umma_desc_kmajor(b_addr + 4 * b_lbo + k2 * 2 * b_lbo, b_lbo, 128);
+              const uint64_t ahi = a_desc + ((k2 * 4096) >> 4);
+              const uint64_t alo = a_desc + ((8192 + k2 * 4096) >> 4);
+              const uint64_t bhi = b_desc + ((k2 * 2 * b_lbo) >> 4);
+              const uint64_t blo = b_desc + ((4 * b_lbo + k2 * 2 * b_lbo) >> 4);
               if (a_in_tmem) {
                 // A planes in tensor memory: hi at columns [0,16) of the stage's slot, lo at [16,32)
                 const uint32_t t_hi = tmem_base + A_TMEM_COL0 + s * 32 + k2 * 8, t_lo = t_hi + 16;
@@ -773,19 +833,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
                 umma_tf32(d_tmem, ahi, blo, idesc, 1u);
                 umma_tf32(d_tmem, ahi, bhi, idesc, 1u);
               }
+              if (k2 == 0 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
             }
+            if (!ok) break;
           } else {
 #pragma unroll
             for (int k2 = 0; k2 < 4; ++k2) {
-              const uint64_t ad = umma_desc_kmajor(a_addr + k2 * 4096, 2048, 128);
-              const uint64_t bd = umma_desc_kmajor(b_addr + k2 * 2 * b_lbo, b_lbo, 128);
+              const uint64_t ad = a_desc + ((k2 * 4096) >> 4);
+              const uint64_t bd = b_desc + ((k2 * 2 * b_lbo) >> 4);
               if (CTA2) umma_i8_2cta(d_tmem, ad, bd, idesc, (ks | k2) != 0 ? 1u : 0u);
               else umma_i8(d_tmem, ad, bd, idesc, (ks | k2) != 0 ? 1u : 0u);
+              if (k2 == 1 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
             }
+            if (!ok) break;
           }
           if (CTA2) umma_commit_2cta(&empty[s]);
           else umma_commit(&empty[s]);
           if (it < 6) WG_TRACE2(34 + 3 * it);
+          s = s_next;
+          ph = ph_next;
         }
         if (ok) {
           if (CTA2) umma_commit_2cta(&tfull[b]);
@@ -802,12 +868,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const int cgrp = (warp - 2 - GEMM_EPI_WARPS) / GEMM_CONV_WARPS;       // this warp's group
       const int tid_c = ((warp - 2 - GEMM_EPI_WARPS) % GEMM_CONV_WARPS) * 32 + lane;
       uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
+      auto next_slot = [&]() { if (++s == nstages) { s = 0; ph ^= 1u; } };      // (no divisions: see the MMA loop)
       bool ok = true;
       for (int tile = first; tile < total_tiles && ok; tile += step) {
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          if (static_cast<int>(it % GEMM_CONV_GROUPS) != cgrp) continue;       // the other group's stage
-          const int s = it % nstages;
-          const uint32_t ph = (it / nstages) & 1u;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it, next_slot()) {
+          if (GEMM_CONV_GROUPS > 1 && static_cast<int>(it % GEMM_CONV_GROUPS) != cgrp) continue;       // the other group's stage
           if (tid_c == 0 && it < 6) WG_TRACE2(50 + it);
           if (!mbar_wait_warp(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           if (tid_c == 0 && it < 8) WG_TRACE(48 + 2 * it);
@@ -886,12 +953,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const int nt = r / m_units, mu = r - nt * m_units;
       const int mt = CTA2 ? 2 * mu + static_cast<int>(rank) : mu;
       const bool live = mt < p.m_tiles;
-      const uint32_t b = a_in_tmem ? 0u : (tcount & 1u), tph = a_in_tmem ? (tcount & 1u) : ((tcount >> 1) & 1u);
+      const uint32_t b = acc_bufs == 1 ? 0u : (tcount & 1u), tph = acc_bufs == 1 ? (tcount & 1u) : ((tcount >> 1) & 1u);
       const int t = mt * BM + row;
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
       tc_fence_after_sync();
       if (threadIdx.x == 64 && tcount < 8) WG_TRACE(32 + tcount);
-      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * MAX_BN;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * acc_stride;
       // int8: this warp's slice of the per-(position, channel) constants goes to a warp-private
       // piece of shared memory first (one 16-byte load per lane and array), so that the loop below
       // reads them with broadcast shared-memory loads instead of waiting on global memory
@@ -912,9 +979,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       // flat mode: this thread's row is pixel flat_pix of image flat_n
       const int flat_n = p.flat ? mt / p.tiles_img : 0;
       const int flat_pix = p.flat ? (mt - flat_n * p.tiles_img) * BM + row : 0;
-      auto emit = [&](int k, const uint32_t (&rr)[16]) {      // k-th 16-column block of this warp
+      auto emit = [&](int k, uint32_t (&rr)[16]) {      // k-th 16-column block of this warp
         const int blk = half + 2 * k;
         const int ocb = nt * (BN / 16) + blk;
+        if (stack) {
+          // columns [BN, 2*BN) hold the hi*lo part of the same outputs
+          uint32_t r2[16];
+          tmem_ld16(t_addr + BN + blk * 16, r2);
+          tmem_ld_wait16(r2);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) rr[i] = __float_as_uint(__fadd_rn(__uint_as_float(rr[i]), __uint_as_float(r2[i])));
+        }
         if (p.flat) {
           if (flat_pix < p.HW && ocb < p.OCB) {
             float4 *o = reinterpret_cast<float4 *>(p.out + ((static_cast<size_t>(flat_n) * p.OCB + ocb) * p.HW + flat_pix) * 16);
@@ -1351,8 +1426,10 @@ std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, in
 // therefore weighs most (64 / 128 input channels: 1.29 -> 1.52 ms, 0.42 -> 0.49 ms), is even at 128
 // channels x 8 stages, and wins from 256 input channels up (conv4_2 0.308 -> 0.283 ms, conv5_x
 // 0.108 -> 0.097 ms) and whenever a CTA runs a single tile (1x1 benchmark layer 68.9 -> 55.9 us).
-inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms) {
-  const int dflt = kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms) ? 1 : 0;
+// With stacked weights of at most 64 output channels the accumulator is 128 columns wide, two of
+// them fit beside the A slots, and A in tensor memory costs nothing: always on there.
+inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms, int acc_width = 256) {
+  const int dflt = kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms || acc_width <= 128) ? 1 : 0;
   return tune_env("ELB_F32_A_TMEM", dflt) > 0 ? 1 : 0;
 }
 // K rotation spreads the weight reads of CTAs running side by side over L2; measured without effect
@@ -1380,9 +1457,13 @@ struct WinoImpl {
   float relu_lo = 0.f, relu_hi = 3.402823466e38f;
   bool direct = false;     // fp32 direct convolution on the GEMM kernel (g.A == 1)
   bool flat = false;       // ... 1x1 stride 1 without padding: the GEMM kernel alone, reading the user's tensor
+  bool small_ic = false;   // fp32 Winograd asked for a layer with <= 4 input channels: the CUDA-core direct kernel
+  void *d_w_small = nullptr;
+  int ic_real = 0;
   size_t in_img_bytes = 0, out_img_bytes = 0;
   size_t a_bytes = 0, b_bytes = 0, m_bytes = 0;
   bool cta2 = false;       // GEMM on pairs of CTAs (weight rows split over the pair)
+  bool stack = false;      // fp32, BN <= 128: hi and lo weight rows stacked per K chunk (two MMAs per K step instead of three)
   int max_clusters = 0;    // pairs the device holds at once
   void *d_a = nullptr, *d_b = nullptr, *d_m = nullptr, *d_bias = nullptr, *d_scale = nullptr, *d_shift = nullptr;
 };
@@ -1401,6 +1482,13 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
             d.oh == d.ih && d.ow == d.iw && !(getenv("ELB_F32_NO_FLAT") && atoi(getenv("ELB_F32_NO_FLAT")) > 0);
   w->relu_lo = d.relu_lower; w->relu_hi = d.relu_upper;
   w->kind = info.kernel == ELB_KERNEL_WINO_I8_UMMA ? KIND_I8 : KIND_F32;
+  // fp32 Winograd on a layer with at most four input channels (an image network's first layer): 13 of
+  // the 16 transformed channels would be zeros; the direct CUDA-core kernel does it in one pass over
+  // the input and the output
+  w->small_ic = info.kernel == ELB_KERNEL_WINO_F32_UMMA && d.ic <= 4 && host::alignup(d.oc, V) <= 256 &&
+                f32_small_ic_smem_bytes(host::alignup(d.oc, V) / V) <= 200 * 1024;
+  w->ic_real = d.ic;
+  if (w->small_ic) info.kernel = ELB_KERNEL_F32_SMALL_IC;
   if (w->kind == KIND_I8) {
     if (d.sampling_kind != ELB_CALIBRATED) { err = "int8 Winograd: only CALIBRATED sampling is implemented"; return ELB_UNIMPLEMENTED; }
     if (d.input_z != 0.0f) { err = "Support abs-max scaling for input only in Conv Winograd"; return ELB_UNIMPLEMENTED; }  // src/eld_conv.cpp:224-229
@@ -1427,7 +1515,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   budget = static_cast<size_t>(tune_env("ELB_WINO_CHUNK_MB", static_cast<int>(budget >> 20))) << 20;
   size_t imgs = budget / (per_tile * tiles_img);
   if (imgs < 1) imgs = 1;
-  if (imgs > static_cast<size_t>(d.n) || w->flat) imgs = d.n;       // flat mode needs no transform-domain buffers
+  if (imgs > static_cast<size_t>(d.n) || w->flat || w->small_ic) imgs = d.n;       // (no transform-domain buffers in these modes)
   w->imgs_per_chunk = static_cast<int>(imgs);
   g.N = w->imgs_per_chunk;
   g.T = static_cast<int>(imgs * tiles_img);
@@ -1436,7 +1524,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
   w->a_bytes = static_cast<size_t>(AA) * g.m_tiles * g.k_stages * a_gbytes;
   w->b_bytes = static_cast<size_t>(AA) * w->n_tiles * g.k_stages * 128 * w->BN;
   w->m_bytes = static_cast<size_t>(AA) * g.OCB * g.Tpad * 16 * 4;
-  if (w->flat) { w->a_bytes = 256; w->m_bytes = 256; }
+  if (w->flat || w->small_ic) { w->a_bytes = 256; w->m_bytes = 256; }
   w->in_img_bytes = static_cast<size_t>(w->ICP) * d.ih * d.iw * (d.dt_input == ELB_F32 ? 4 : 1);
   w->out_type = d.dt_output == ELB_F32 ? OUT_F32 : d.dt_output == ELB_U8 ? OUT_U8 : OUT_S8;
   w->out_img_bytes = static_cast<size_t>(w->OCP) * d.oh * d.ow * (w->out_type == OUT_F32 ? 4 : 1);
@@ -1481,7 +1569,12 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
       w->max_clusters = n;
     }
   }
-  info.launches_per_call = w->flat ? 1 : 3 * ((d.n + w->imgs_per_chunk - 1) / w->imgs_per_chunk);
+  w->stack = w->kind == KIND_F32 && !w->cta2 && w->BN <= 128 && tune_env("ELB_F32_STACK", 1) > 0;
+  info.launches_per_call = (w->flat || w->small_ic) ? 1 : 3 * ((d.n + w->imgs_per_chunk - 1) / w->imgs_per_chunk);
+  if (w->small_ic) {
+    e = init_f32_small_ic(g.OCB);
+    if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return ELB_GENERAL_ERROR; }
+  }
   return ELB_OK;
 }
 
@@ -1501,6 +1594,20 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
   if (d.with_bias) {
     if (!bias) { err = "bias is null but with_bias is set"; return ELB_GENERAL_ERROR; }
     W_TRY(cudaMemcpy(hb.data(), bias, static_cast<size_t>(w->OCP) * 4, cudaMemcpyDefault));
+  }
+  if (w->small_ic) {
+    // [tap][channel 0..3][OCP]: the layout the direct kernel reads as broadcast float4s
+    std::vector<float> ws(static_cast<size_t>(9) * 4 * w->OCP, 0.0f);
+    for (int o = 0; o < d.oc; ++o)
+      for (int i = 0; i < d.ic; ++i)
+        for (int tap = 0; tap < 9; ++tap)
+          ws[(static_cast<size_t>(tap) * 4 + i) * w->OCP + o] = hw[host::w_index(w->ICP / 16, 3, 3, o, i, tap / 3, tap % 3)];
+    W_TRY(cudaMalloc(&w->d_w_small, ws.size() * 4));
+    W_TRY(cudaMemcpy(w->d_w_small, ws.data(), ws.size() * 4, cudaMemcpyHostToDevice));
+    W_TRY(cudaMalloc(&w->d_bias, static_cast<size_t>(w->OCP) * 4));
+    W_TRY(cudaMemcpy(w->d_bias, hb.data(), static_cast<size_t>(w->OCP) * 4, cudaMemcpyHostToDevice));
+    info.workspace_bytes += ws.size() * 4 + static_cast<size_t>(w->OCP) * 4;
+    return ELB_OK;
   }
   std::vector<float> u;
   if (w->direct) {
@@ -1534,8 +1641,13 @@ int wino_prepare(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, 
               const float hi = tf32_rna(src[c]);
               volatile float lo = src[c] - hi;
               const int j = c >> 2, e = c & 3;
-              stage[(static_cast<size_t>(j) * BNH + rr) * 4 + e] = hi;
-              stage[(static_cast<size_t>(4 + j) * BNH + rr) * 4 + e] = lo;
+              if (w->stack) {      // [chunk j][hi rows | lo rows][4 floats]
+                stage[(static_cast<size_t>(j) * 2 * BN + rr) * 4 + e] = hi;
+                stage[(static_cast<size_t>(j) * 2 * BN + BN + rr) * 4 + e] = lo;
+              } else {             // [plane hi / lo][chunk j][rows][4 floats]
+                stage[(static_cast<size_t>(j) * BNH + rr) * 4 + e] = hi;
+                stage[(static_cast<size_t>(4 + j) * BNH + rr) * 4 + e] = lo;
+              }
             }
           }
   } else {
@@ -1595,6 +1707,23 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     return ELB_GENERAL_ERROR;
   }
   if (first < 0 || count <= 0 || first + count > w->N) { err = "image range outside the batch"; return ELB_GENERAL_ERROR; }
+  if (w->small_ic) {
+    const WinoGeom &g = w->g;
+    SmallIcParams sp{};
+    sp.in = static_cast<const float *>(in) + static_cast<size_t>(first) * (w->in_img_bytes / 4);
+    sp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
+    sp.w = static_cast<const float *>(w->d_w_small);
+    sp.bias = static_cast<const float *>(w->d_bias);
+    sp.N = count; sp.H = g.IH; sp.W = g.IW; sp.CB = g.CB; sp.OCB = g.OCB;
+    sp.ic = w->ic_real;
+    sp.with_bias = w->with_bias; sp.with_relu = w->with_relu; sp.with_sum = w->with_sum;
+    const bool timed = pl.stage_ev[0] != nullptr;
+    if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[0], s)); W_TRY(cudaEventRecord(pl.stage_ev[1], s)); }
+    W_TRY(launch_f32_small_ic(sp, s));
+    if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[2], s)); W_TRY(cudaEventRecord(pl.stage_ev[3], s)); }
+    launches = 1;
+    return ELB_OK;
+  }
   if (w->flat) {
     // the whole convolution in the GEMM kernel: A straight from the user's tensor, fused epilogue
     const WinoGeom &g = w->g;
@@ -1622,7 +1751,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.flat = 1; gp.HW = HW; gp.tiles_img = tiles_img; gp.CB = g.CB;
     gp.spp = tune_spp(KIND_F32);
     gp.rotate_k = tune_rotate_k();
-    gp.a_tmem = tune_a_tmem(KIND_F32, gp.k_stages, static_cast<long long>(gp.m_tiles) * gp.n_tiles, num_sms);
+    gp.stack = w->stack ? 1 : 0;
+    gp.a_tmem = tune_a_tmem(KIND_F32, gp.k_stages, static_cast<long long>(gp.m_tiles) * gp.n_tiles, num_sms,
+                            w->stack ? 2 * w->BN : w->BN);
     gp.bias = static_cast<const float *>(w->d_bias);
     gp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
     gp.with_bias = w->with_bias; gp.with_relu = w->with_relu; gp.with_sum = w->with_sum;
@@ -1692,7 +1823,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     // opt-in: measured without effect (VGG conv1_2 GEMM 0.786 vs 0.788 ms, conv3_2 0.427 vs 0.433 ms)
     gp.prefetch = tune_env("ELB_WINO_PREFETCH", 0) > 0 ? 1 : 0;
     gp.ablate = tune_env("ELB_ABL", 0);
-    gp.a_tmem = tune_a_tmem(w->kind, gp.k_stages, static_cast<long long>(gp.positions) * gp.m_tiles * gp.n_tiles, num_sms);
+    gp.stack = w->stack ? 1 : 0;
+    gp.a_tmem = tune_a_tmem(w->kind, gp.k_stages, static_cast<long long>(gp.positions) * gp.m_tiles * gp.n_tiles, num_sms,
+                            w->stack ? 2 * w->BN : w->BN);
     if (w->cta2) {
       const int pairs = gp.positions * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
       cudaLaunchConfig_t cfg{};
@@ -1736,7 +1869,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
 void wino_release(WinoPlan &pl) {
   WinoImpl *w = pl.impl;
   if (!w) return;
-  for (void *p : {w->d_a, w->d_b, w->d_m, w->d_bias, w->d_scale, w->d_shift})
+  for (void *p : {w->d_a, w->d_b, w->d_m, w->d_bias, w->d_scale, w->d_shift, w->d_w_small})
     if (p) cudaFree(p);
   delete w;
   pl.impl = nullptr;
@@ -1788,7 +1921,7 @@ __device__ __forceinline__ void g3_dev(float f0, float f1, float f2, float (&o)[
 // One thread = one (oc, ic) pair: U = G g G^T, 3xTF32 split, written into the GEMM's B image
 // [a][n tile][k stage = ic/16][plane][chunk = (ic%16)/4][BN rows][4 floats].
 __global__ void wino_weights_f32_kernel(const float *__restrict__ w, float *__restrict__ b_img, int oc, int ic,
-                                        int OCP, int ICP, int BN, int n_tiles) {
+                                        int OCP, int ICP, int BN, int n_tiles, int stack) {
   // one thread per row of EVERY n tile (n_tiles * BN >= OCP): rows past the last output channel are
   // written as zeros, because the scratch behind them still holds an earlier call's bytes
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1827,8 +1960,13 @@ __global__ void wino_weights_f32_kernel(const float *__restrict__ w, float *__re
       const float hi = __uint_as_float(hb);
       const float lo = __fsub_rn(r[b], hi);
       float *stage = b_img + ((static_cast<size_t>(a * 6 + b) * n_tiles + nt) * KS + ks) * (32 * BN);
-      stage[(static_cast<size_t>(j) * BN + row) * 4 + e] = hi;
-      stage[(static_cast<size_t>(4 + j) * BN + row) * 4 + e] = lo;
+      if (stack) {       // [chunk j][hi rows | lo rows][4 floats]
+        stage[(static_cast<size_t>(j) * 2 * BN + row) * 4 + e] = hi;
+        stage[(static_cast<size_t>(j) * 2 * BN + BN + row) * 4 + e] = lo;
+      } else {           // [plane hi / lo][chunk j][rows][4 floats]
+        stage[(static_cast<size_t>(j) * BN + row) * 4 + e] = hi;
+        stage[(static_cast<size_t>(4 + j) * BN + row) * 4 + e] = lo;
+      }
     }
   }
 }
@@ -1913,8 +2051,9 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
 
   // the status word must start at zero; everything else the kernels read is rewritten below
   if (cudaMemsetAsync(status, 0, 256, s) != cudaSuccess) return fail(ELB_GENERAL_ERROR, "cudaMemsetAsync failed");
+  const int stack = BN <= 128 ? 1 : 0;
   wino_weights_f32_kernel<<<(n_tiles * BN * ICP + 255) / 256, 256, 0, s>>>(static_cast<const float *>(weights), b_img, d.oc,
-                                                                         d.ic, OCP, ICP, BN, n_tiles);
+                                                                         d.ic, OCP, ICP, BN, n_tiles, stack);
   WinoInParams ip{};
   ip.in = input; ip.a_img = a_img; ip.g = g;
   wino_input_kernel<false><<<dim3((g.Tpad + TRANS_TILES - 1) / TRANS_TILES, g.CB), TRANS_THREADS, 0, s>>>(ip);
@@ -1926,7 +2065,8 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   gp.positions = 36;
   gp.spp = 1;
   const int total = 36 * gp.m_tiles * gp.n_tiles;
-  gp.a_tmem = (gp.k_stages >= 16 || total <= num_sms) ? 1 : 0;
+  gp.stack = stack;
+  gp.a_tmem = (gp.k_stages >= 16 || total <= num_sms || (stack ? 2 * BN : BN) <= 128) ? 1 : 0;
   wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
   WinoOutParams op{};
   op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;

@@ -24,4 +24,17 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
              int first, int count, cudaStream_t s, int &launches, std::string &err);
 void wino_release(WinoPlan &pl);
 
+// fp32 3x3 stride-1 pad-1 convolution with at most four input channels (f32_small_ic.cu)
+struct SmallIcParams {
+  const float *in;      // nChw16c fp32, first image of the range
+  const float *w;       // [9 taps][4 channels][OCP] fp32
+  const float *bias;    // [OCP]
+  float *out;           // nChw16c fp32
+  int N, H, W, CB, OCB, ic;
+  int with_bias, with_relu, with_sum;
+};
+size_t f32_small_ic_smem_bytes(int OCB);
+cudaError_t init_f32_small_ic(int OCB);        // once per plan and device (kernel attribute)
+cudaError_t launch_f32_small_ic(const SmallIcParams &p, cudaStream_t s);
+
 }  // namespace elb

@@ -35,6 +35,11 @@ F32_CASES = [
     _f32("wino_oc512", 1, 64, 512, 8, 8),                       # two N tiles of 256
     _f32("wino_oc320", 1, 32, 320, 8, 8),                       # N tiles of 160
     _f32("wino_tiny", 1, 16, 16, 4, 4),
+    # at most four input channels: served by the CUDA-core direct kernel (f32_small_ic)
+    _f32("small_ic_3", 2, 3, 64, 30, 21),
+    _f32("small_ic_4_sum", 1, 4, 40, 9, 10, sum=True),
+    _f32("small_ic_1_plain", 2, 1, 16, 5, 3, relu=False, bias=False),
+    _f32("small_ic_3_f2x2", 1, 3, 32, 8, 8, tile=4),
     # F(2x2,3x3)
     _f32("wino4_small", 2, 32, 32, 14, 14, tile=4),
     _f32("wino4_partial_tiles", 1, 16, 48, 13, 11, tile=4),     # odd oh, ow: clipped 2x2 tiles
@@ -52,7 +57,7 @@ def test_fp32_winograd_matches_oracle(pkg, case):
     want = R.oracle_wino_f32(case, t)
     got, d = G.run_gpu(case, t)
     try:
-        assert d.kernel == "wino_f32_umma"
+        assert d.kernel == ("f32_small_ic" if case.ic <= 4 else "wino_f32_umma")
         assert d.device_status() == 0
         err = R.rel_l2(got, want)
         assert err <= F32_TOL, f"rel-L2 vs restated Winograd {err:.3e}"
