@@ -692,10 +692,11 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
 
 
 def stack_cpu_baseline(int8, gbatch, wl, steps=2):
-    """The 13 layers through the reference's CPU library on a bounded sample (2 images per call),
-    per-layer times summed and scaled to the global batch."""
+    """The 13 layers through the reference's CPU library on a bounded sample (8 images per call, enough
+    for its thread partitioning over images / tiles to fill the cores), per-layer times summed and
+    scaled to the global batch."""
     import refutil as R
-    n_s = 2
+    n_s = 8
     total_ms, r = 0.0, None
     for k, (ic, oc, hw, _) in enumerate(vgg_layers()):
         case = vgg_layer_case(k, ic, oc, hw, n_s, int8, 1.0 / 255.0 if k == 0 else 0.02, 0.02)

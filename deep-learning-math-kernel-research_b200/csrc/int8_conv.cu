@@ -89,33 +89,49 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   constexpr uint32_t TMEM_COLS = 2 * BN;          // two accumulator buffers (power of two >= 32)
   const int total_tiles = p.m_tiles * p.n_tiles;
 
+  // Set-up in two groups, so that the first copies are on their way while the rest of the CTA is
+  // still getting ready (measured on the 1x1 benchmark layer: with one CTA-wide barrier the first
+  // copy was issued 4.6-5.0 k cycles into a 22 k-cycle kernel):
+  //   producers (warp 0 and the last three warps) only need the barriers: they wait on named
+  //   barrier 1 for the MMA warp, which initialises them, and start fetching;
+  //   MMA and epilogue warps load the per-channel constants, allocate tensor memory and meet on
+  //   named barrier 2.
+  const bool is_producer = warp == 0 || warp >= PRODUCER2_WARP;
   if (threadIdx.x == 0) {
     ELB_TRACE(0);
     // the copy engine fetches a tensor map from global memory on first use (a few microseconds cold):
-    // start that now, behind the barrier and tensor-memory set-up
+    // start that now
     if (MODE == I8_MODE_BOX)
       for (int i = 0; i < p.stride * p.stride; ++i) tma_prefetch_desc(&p.tmap[i]);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], NUM_EPI_WARPS);      // one arrival per epilogue warp
-    }
-    *abort_flag = 0;
-    fence_barrier_init();
-    fence_proxy_async_smem();
   }
-  for (int i = threadIdx.x; i < p.OCB * V; i += NUM_THREADS) {
-    s_scale[i] = p.scale[i];
-    s_shift[i] = p.shift[i];
+  if (warp == 1) {
+    if (lane == 0) {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&full[s], 1);
+        mbar_init(&empty[s], 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&tfull[b], 1);
+        mbar_init(&tempty[b], NUM_EPI_WARPS);      // one arrival per epilogue warp
+      }
+      *abort_flag = 0;
+      fence_barrier_init();
+      fence_proxy_async_smem();
+    }
+    __syncwarp();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  if (is_producer || warp == 1) named_bar_sync(1, 32 * (MAX_PRODUCERS + 1));
+  if (!is_producer) {
+    for (int i = threadIdx.x - 32; i < p.OCB * V; i += 32 * (1 + NUM_EPI_WARPS)) {
+      s_scale[i] = p.scale[i];
+      s_shift[i] = p.shift[i];
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before_sync();
+    named_bar_sync(2, 32 * (1 + NUM_EPI_WARPS));
+    tc_fence_after_sync();
+  }
+  const uint32_t tmem_base = is_producer ? 0u : *tmem_slot;      // (producers never touch tensor memory)
   if (threadIdx.x == 0) ELB_TRACE(1);
   int fail_code = 0;
 
@@ -260,33 +276,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         const uint32_t d_tmem = tmem_base + b * BN;
         const int ks0 = p.rotate_k ? tile % p.k_stages : 0;      // same rotation as the producer
         int ks = ks0;
-        // The wait for stage ki + 1 is issued in the MIDDLE of stage ki's MMAs: even on a completed
-        // barrier it costs this thread a few hundred cycles of latency, which the MMAs already queued
-        // in the tensor pipe cover; between the stages it would leave the pipe idle.
-        if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-        tc_fence_after_sync();
+        // (Waiting for stage ki + 1 in the middle of stage ki's MMAs, which pays in the fp32 GEMM
+        // kernel, measured slower here: 13.2 vs 12.6 us on the 1x1 benchmark layer.)
         for (int ki = 0; ki < p.k_stages; ++ki, ++it) {
+          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+          tc_fence_after_sync();
           if (it < 16) ELB_TRACE(20 + it);
           const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
           const uint64_t ad0 = A_DESC_HI | (a_addr >> 4), bd0 = B_DESC_HI | ((a_addr + L::A_BYTES) >> 4);
-          int s_next = s + 1;
-          uint32_t ph_next = ph;
-          if (s_next == STAGES) { s_next = 0; ph_next ^= 1u; }
           // K = 32 bytes = two chunks per instruction; the last stage may hold fewer than KC chunks
           const int pairs = (min(KC, p.Q - ks * KC) + 1) >> 1;
 #pragma unroll
           for (int k2 = 0; k2 < KC / 2; ++k2) {
             if (k2 < pairs)
               umma_i8(d_tmem, ad0 + ((k2 * 2 * (BM * 16)) >> 4), bd0 + ((k2 * 2 * (BN * 16)) >> 4), IDESC, (ki | k2) != 0 ? 1u : 0u);
-            if (k2 == KC / 4 - 1 && ki + 1 < p.k_stages) {
-              if (!mbar_wait(&full[s_next], ph_next, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
-              tc_fence_after_sync();
-            }
           }
-          if (!ok) break;
           umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
-          s = s_next;
-          ph = ph_next;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
           if (++ks == p.k_stages) ks = 0;
         }
         if (ok) umma_commit(&tfull[b]);  // accumulator complete

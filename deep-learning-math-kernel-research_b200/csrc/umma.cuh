@@ -34,6 +34,11 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Named barrier among `count` threads (a multiple of 32) of the CTA; id 0 is __syncthreads' own.
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // ------------------------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");

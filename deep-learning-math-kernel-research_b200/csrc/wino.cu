@@ -23,8 +23,11 @@
 //      shared-memory stages and bounded waits as the direct-convolution kernel.
 //   3. wino_output_kernel: Y = A^T M A, + bias, (requantise), + in-place sum, ReLU, clipped store
 //      into nChw16c.
-// Batches whose transform-domain buffers would exceed the workspace budget are processed in
-// chunks of whole images.
+// Batches whose transform-domain buffers would exceed the workspace budget (6 GiB) are processed in
+// chunks of whole images.  (Chunks small enough to keep those buffers in L2 were measured and lose:
+// the three kernels of a small chunk each pay a fixed 15-20 us.)
+// A Winograd request for a layer with at most four input channels is served by the direct kernel of
+// f32_small_ic.cu instead.
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -44,7 +47,7 @@ constexpr int BM = 128;
 constexpr int GEMM_STAGES_1 = 4;             // pipeline stages: one CTA per tile (16 KB A + 32 KB B each)
 constexpr int GEMM_STAGES_2 = 6;             // pairs of CTAs (16 KB A + 16 KB of B each)
 constexpr int GEMM_MAX_STAGES = 8;           // barrier slots; fp32 with A in tensor memory runs 5..8 smaller stages
-constexpr int EPI_CONST_BYTES = 16384;       // int8: per-epilogue-warp copies of the tile's scale / shift slice
+constexpr int EPI_CONST_BYTES = 32768;       // int8: per-epilogue-warp copies of the tile's scale / shift slice (16 KB used); fp32: more ring
 constexpr int A_STAGE_BYTES = 16384;          // in shared memory. fp32: hi + lo planes x 4 chunks x 2 KB; int8: 8 chunks x 2 KB
 constexpr int A_RAW_BYTES = 8192;             // fp32 only: one stage of V as it lies in global memory (4 chunks x 2 KB)
 constexpr int GEMM_CONV_WARPS = 4;            // fp32 only: warps that split a raw stage into its tf32 hi / lo planes
@@ -581,6 +584,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   const int stage_bytes = a_in_tmem ? A_RAW_BYTES + 128 * BN : CTA2 ? STAGE_BYTES : A_STAGE_BYTES + 128 * BN;
   const int b_off = a_in_tmem ? A_RAW_BYTES : A_STAGE_BYTES;
   // the ring may also use the area of the int8 epilogue constants when the kernel runs fp32
+  // (Staging the result of a one-accumulator tile through shared memory and bulk-storing it from
+  // there, so that tensor memory is released after it has been read, was measured and is SLOWER: c1
+  // GEMM 0.367 -> 0.429 ms.  The kernel is bound by shared-memory bandwidth -- per stage 48 KB of B
+  // reads by the MMAs, 40 KB of incoming copies and 8 KB of splitter reads against 128 B/clk -- and
+  // the detour adds 256 KB of shared-memory traffic per tile.)
   const int ring_bytes = GEMM_STAGES * STAGE_BYTES + (p.kind == KIND_F32 ? EPI_CONST_BYTES : 0);
   const int nstages = CTA2 ? GEMM_STAGES : min(GEMM_MAX_STAGES, ring_bytes / stage_bytes);
 
