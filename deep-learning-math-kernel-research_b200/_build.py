@@ -20,6 +20,15 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
 
 
+def reference_root() -> Path:
+    """The reference project's tree (only its public headers are needed here): $EULER_REFERENCE, else a
+    checkout named `reference` beside this repository.  $EULER_REFERENCE_INCLUDE may name the include
+    directory itself."""
+    if os.environ.get("EULER_REFERENCE_INCLUDE"):
+        return Path(os.environ["EULER_REFERENCE_INCLUDE"]).parent
+    return Path(os.environ.get("EULER_REFERENCE", ROOT.parent / "reference"))
+
+
 def build(verbose: bool = False) -> Path:
     """See the module docstring.  Returns the path of the CUDA library."""
     LIB_PATH.parent.mkdir(exist_ok=True)
@@ -50,7 +59,7 @@ def build(verbose: bool = False) -> Path:
     # The C++ host library defines the reference's own exported symbols and is therefore compiled
     # with the reference's public headers; where that tree is absent the prebuilt library is kept.
     host_src = PKG_DIR / "host" / "euler_host.cpp"
-    ref_inc = Path(os.environ.get("EULER_REFERENCE_INCLUDE", "/root/reference/include"))
+    ref_inc = reference_root() / "include"
     hdeps = [host_src, LIB_PATH, ROOT / "include" / "euler_b200.h"]
     if (ref_inc / "euler.hpp").exists() and (
             not HOST_LIB_PATH.exists() or any(p.stat().st_mtime > HOST_LIB_PATH.stat().st_mtime for p in hdeps)):

@@ -11,9 +11,10 @@
 // Winograd kernels, the figure of this kernel is in the profile notes.  The result differs from the
 // reference's Winograd output by fp32 rounding only (both are within 1e-6 of the exact convolution).
 //
-// One thread computes 4 consecutive output pixels of a row for every output channel: its 3 x 6
-// input window (float4 = the four real channels of a pixel) stays in registers, the weights
-// [tap][channel][OC] sit in shared memory and are read as broadcast float4s (16 FMAs per load).
+// One thread computes 4 consecutive output pixels of a row for every output channel, eight channels
+// at a time: its 3 x 6 input window (float4 = the four real channels of a pixel) stays in registers,
+// the weights [tap][channel][OC] and the bias sit in shared memory and are read as broadcast float4s
+// (16 FMAs per load).
 #include <cuda_runtime.h>
 
 #include "wino.cuh"
@@ -24,11 +25,17 @@ namespace {
 
 constexpr int SI_THREADS = 128;
 
-__global__ void __launch_bounds__(SI_THREADS) f32_small_ic_kernel(const SmallIcParams p) {
-  extern __shared__ float4 s_w4[];                 // [9 taps][4 channels][OCP] floats
+// Output channels are processed eight at a time: 32 accumulators + the 18 float4 of the window keep
+// the thread near 128 registers, i.e. four resident blocks per SM.  (With sixteen channels at a time
+// the kernel ran two blocks per SM and its issue slots were 30 % busy, most stalls waiting on the
+// per-block bias loads from global memory; the bias now sits in shared memory behind the weights.)
+__global__ void __launch_bounds__(SI_THREADS, 4) f32_small_ic_kernel(const SmallIcParams p) {
+  extern __shared__ float4 s_w4[];                 // [9 taps][4 channels][OCP] floats, then [OCP] bias
   float *s_w = reinterpret_cast<float *>(s_w4);
   const int OCP = p.OCB * 16;
+  float *s_b = s_w + 9 * 4 * OCP;
   for (int i = threadIdx.x; i < 9 * 4 * OCP / 4; i += SI_THREADS) s_w4[i] = reinterpret_cast<const float4 *>(p.w)[i];
+  for (int i = threadIdx.x; i < OCP; i += SI_THREADS) s_b[i] = p.with_bias ? p.bias[i] : 0.0f;
   __syncthreads();
   const int w4 = (p.W + 3) >> 2;                   // groups of 4 pixels per row
   const long long idx = static_cast<long long>(blockIdx.x) * SI_THREADS + threadIdx.x;
@@ -54,11 +61,13 @@ __global__ void __launch_bounds__(SI_THREADS) f32_small_ic_kernel(const SmallIcP
     }
   }
 
-  for (int ocb = 0; ocb < p.OCB; ++ocb) {
-    float acc[4][16];
+  const int groups = OCP >> 3;                     // groups of eight output channels
+#pragma unroll 1
+  for (int og = 0; og < groups; ++og) {
+    float acc[4][8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float b = p.with_bias ? __ldg(p.bias + ocb * 16 + i) : 0.0f;
+    for (int i = 0; i < 8; ++i) {
+      const float b = s_b[og * 8 + i];
 #pragma unroll
       for (int px = 0; px < 4; ++px) acc[px][i] = b;
     }
@@ -69,39 +78,37 @@ __global__ void __launch_bounds__(SI_THREADS) f32_small_ic_kernel(const SmallIcP
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           if (c < p.ic) {                          // uniform: the same for every thread
-            const float4 *wr = reinterpret_cast<const float4 *>(s_w + ((kh * 3 + kw) * 4 + c) * OCP + ocb * 16);
-            float wv[16];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float4 t = wr[q];
-              wv[4 * q] = t.x; wv[4 * q + 1] = t.y; wv[4 * q + 2] = t.z; wv[4 * q + 3] = t.w;
-            }
+            const float4 *wr = reinterpret_cast<const float4 *>(s_w + ((kh * 3 + kw) * 4 + c) * OCP + og * 8);
+            const float4 w0 = wr[0], w1 = wr[1];
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
             for (int px = 0; px < 4; ++px) {
               const float4 xv = win[kh][px + kw];
               const float x = c == 0 ? xv.x : c == 1 ? xv.y : c == 2 ? xv.z : xv.w;
 #pragma unroll
-              for (int i = 0; i < 16; ++i) acc[px][i] = __fmaf_rn(x, wv[i], acc[px][i]);
+              for (int i = 0; i < 8; ++i) acc[px][i] = __fmaf_rn(x, wv[i], acc[px][i]);
             }
           }
         }
-    // bias is in; + stored output (in-place sum), ReLU, store
+    // bias is in; + stored output (in-place sum), ReLU, store: 32 bytes of each of the four pixels
+    const int ocb = og >> 1, half = og & 1;
 #pragma unroll
     for (int px = 0; px < 4; ++px) {
       const int ow = ow0 + px;
-      if (ow >= p.W) break;
-      float4 *dst = reinterpret_cast<float4 *>(p.out + (((static_cast<size_t>(n) * p.OCB + ocb) * p.H + oh) * p.W + ow) * 16);
+      if (ow < p.W) {
+        float4 *dst = reinterpret_cast<float4 *>(p.out + (((static_cast<size_t>(n) * p.OCB + ocb) * p.H + oh) * p.W + ow) * 16) + half * 2;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float4 v = make_float4(acc[px][4 * q], acc[px][4 * q + 1], acc[px][4 * q + 2], acc[px][4 * q + 3]);
-        if (p.with_sum) {
-          const float4 pv = dst[q];
-          v.x = __fadd_rn(v.x, pv.x); v.y = __fadd_rn(v.y, pv.y); v.z = __fadd_rn(v.z, pv.z); v.w = __fadd_rn(v.w, pv.w);
+        for (int q = 0; q < 2; ++q) {
+          float4 v = make_float4(acc[px][4 * q], acc[px][4 * q + 1], acc[px][4 * q + 2], acc[px][4 * q + 3]);
+          if (p.with_sum) {
+            const float4 pv = dst[q];
+            v.x = __fadd_rn(v.x, pv.x); v.y = __fadd_rn(v.y, pv.y); v.z = __fadd_rn(v.z, pv.z); v.w = __fadd_rn(v.w, pv.w);
+          }
+          if (p.with_relu) {                       // the Winograd output transform's ReLU: a plain max with 0
+            v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f);
+          }
+          dst[q] = v;
         }
-        if (p.with_relu) {                         // the Winograd output transform's ReLU: a plain max with 0
-          v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f);
-        }
-        dst[q] = v;
       }
     }
   }
@@ -109,7 +116,7 @@ __global__ void __launch_bounds__(SI_THREADS) f32_small_ic_kernel(const SmallIcP
 
 }  // namespace
 
-size_t f32_small_ic_smem_bytes(int OCB) { return static_cast<size_t>(9) * 4 * OCB * 16 * 4; }
+size_t f32_small_ic_smem_bytes(int OCB) { return (static_cast<size_t>(9) * 4 + 1) * OCB * 16 * 4; }
 
 cudaError_t init_f32_small_ic(int OCB) {
   return cudaFuncSetAttribute(f32_small_ic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -4,7 +4,8 @@
 # against it and so that it can be timed as the CPU baseline.  Nothing the product ships or runs
 # depends on anything produced here.
 #
-#   usage:  oracle/build_ref.sh [REFERENCE_ROOT]        (default /root/reference)
+#   usage:  oracle/build_ref.sh [REFERENCE_ROOT]
+#           (default: $EULER_REFERENCE, else a checkout named `reference` beside this repository)
 #
 # Outputs go to oracle/_ref/ only (git-ignored):
 #   oracle/_ref/kgen/*.cpp     (O,T) function-table translation units (see below)
@@ -26,8 +27,8 @@
 # and the int8 depthwise units are compiled with -include ref_gxx_unaligned.h (unaligned 64-byte
 # moves where g++ would emit aligned ones; no arithmetic changes).
 set -euo pipefail
-REF=${1:-/root/reference}
 HERE=$(cd "$(dirname "$0")" && pwd)
+REF=${1:-${EULER_REFERENCE:-$(cd "$HERE/../.." && pwd)/reference}}
 OUT=$HERE/_ref
 JOBS=${JOBS:-$(nproc)}
 CXX=${ORACLE_CXX:-$( [ -x /usr/bin/g++ ] && echo /usr/bin/g++ || echo g++ )}
