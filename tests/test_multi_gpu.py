@@ -63,3 +63,23 @@ def test_more_gpus_than_images_leaves_spares_idle(pkg):
     m = E.MultiConv(G.make_desc(case), devices=_devices())
     assert len(m.parts()) == 1
     m.close()
+
+
+def test_euler_gpus_through_the_cpp_surface(pkg, monkeypatch):
+    """EULER_GPUS=G makes euler::elx_conv itself split the minibatch (the same C++ driver that runs the
+    reference library, linked against this repository's libel.so).  Needs two GPUs; with one, the
+    request for a second GPU must come back as a setup error code, not as a crash."""
+    import torch
+    if not R.DROPIN_DRIVER.exists():
+        pytest.skip("tests/bin/euler_driver_b200 was not built (reference headers missing at build time)")
+    case = R.baseline_case("c3", 6)
+    t = R.make_tensors(case)
+    monkeypatch.setenv("EULER_GPUS", "2")
+    if torch.cuda.device_count() >= 2:
+        out, info = R.run_reference(case, t, driver=R.DROPIN_DRIVER, iters=2, warmup=0)
+        assert info["rc_setup"] == 0 and info["rc"] == 0
+        assert np.array_equal(out, R.oracle_int8_conv(case, t))
+    else:
+        with pytest.raises(RuntimeError) as e:
+            R.run_reference(case, t, driver=R.DROPIN_DRIVER)
+        assert '"rc_setup": 2' in str(e.value)
