@@ -103,8 +103,10 @@ PUBLISHED = {"c1": 11.2}
 STACK_CHUNK = 32
 
 # DRAM bytes (read + written) per step from the ncu captures summarised under profiles/ (sum over
-# the kernels of a step, full-size workloads).
-NCU_TRAFFIC = {"c1": 2139.6e6, "c2": 13.15e6, "c3": 26.03e6, "c3s": 38.88e6, "c4": 1268.9e6, "dw": 25.72e6, "c2f": 53.5e6}
+# the kernels of a step, full-size workloads; c5: captured at 8 images and scaled to the 256 of a
+# step -- the traffic of every kernel of the stack grows in proportion to the images).
+NCU_TRAFFIC = {"c1": 2139.6e6, "c2": 13.15e6, "c3": 26.03e6, "c3s": 38.88e6, "c4": 1268.9e6, "dw": 25.72e6, "c2f": 53.5e6,
+               "c5": 100.9e9}
 
 
 # ------------------------------------------------------------------------------------ helpers
@@ -672,7 +674,8 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
                 "call": "elb_stack_execute"},
         "gpu_launches": int(launches_per_step * len(per) * steps),
         "roofline": {"bound": "tensor+hbm per layer", "achieved": value, "peak": attainable, "unit": wl["unit"],
-                     "frac": value / ctx.world / attainable, "traffic": None,
+                     "frac": value / ctx.world / attainable,
+                     "traffic": NCU_TRAFFIC[wid] / ctx.world if wid in NCU_TRAFFIC and not args.batch else None,
                      "algorithmic_bytes": alg_bytes * chunks_g,
                      "peak_source": f"sum over layers of max(ops / tensor ceiling, bytes / {ctx.peak_kind} "
                                     f"{ctx.peaks['hbm_gbs']} GB/s); tensor ceiling from the repository's tcgen05 "

@@ -621,7 +621,15 @@ int do_prepare(elb_conv &pl, const void *weights, const void *bias) {
   if (pl.prepared) return ELB_OK;
   if (!weights) return fail(ELB_GENERAL_ERROR, "weights are null");
   const bool pad_bias = pl.d.with_bias && bias && pl.uinfo.size_bias != pl.info.size_bias;
-  if (!pl.cvt_w && !pad_bias) return do_prepare_inner(pl, weights, bias);
+  if (!pl.cvt_w && !pad_bias) {
+    const int rc0 = do_prepare_inner(pl, weights, bias);
+    // The preparation copies from pageable host memory, and such a cudaMemcpy may return while its
+    // DMA into device memory is still running; the plan's streams are non-blocking, so nothing else
+    // would order the first kernel behind it.
+    if (cudaDeviceSynchronize() != cudaSuccess && rc0 == ELB_OK)
+      return fail(ELB_GENERAL_ERROR, "preparation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return rc0;
+  }
   void *w_src = nullptr, *w_blk = nullptr, *b_pad = nullptr;
   int rc = ELB_OK;
   auto cleanup = [&]() { for (void *q : {w_src, w_blk, b_pad}) if (q) cudaFree(q); };
