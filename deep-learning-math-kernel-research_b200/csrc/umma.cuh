@@ -372,4 +372,15 @@ __device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
                :: "memory");
 }
 
+// Register reallocation between warpgroups (all four warps of a group execute it): a group that needs
+// few registers hands them back, a group that needs many takes them from the pool of the launch.
+template <int REGS>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+template <int REGS>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
 }  // namespace elb

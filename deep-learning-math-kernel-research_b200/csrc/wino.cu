@@ -37,6 +37,8 @@
 #include "elb_common.cuh"
 #include "host_prep.hpp"
 #include "umma.cuh"
+#include <type_traits>
+
 #include "wino.cuh"
 
 namespace elb {
@@ -64,9 +66,19 @@ constexpr int GEMM_EPI_WARPS = 8;
 #define TRANS_THREADS 64
 #endif
 constexpr int TRANS_TILES = TRANS_THREADS / 4;      // tiles per block (4 threads = the 16 channels of a block)
-constexpr int GEMM_THREADS = 64 + GEMM_EPI_WARPS * 32 + GEMM_CONV_GROUPS * GEMM_CONV_WARPS * 32 + 32 + 32;    // + the second producer warp + the prefetch warp (last)
-constexpr int GEMM_PRODUCER2_WARP = 2 + GEMM_EPI_WARPS + GEMM_CONV_GROUPS * GEMM_CONV_WARPS;
-constexpr int GEMM_PREFETCH_WARP = GEMM_PRODUCER2_WARP + 1;
+// Warp roles of the GEMM kernel, laid out in whole warpgroups (register reallocation works on groups of
+// four warps): 0, 2 producers (3: a third one, unused by default), 1 MMA issuer | 4..11 epilogue | 12.. splitters
+constexpr int GEMM_PRODUCERS = 3;             // producer warps the kernel can run
+constexpr int GEMM_PRODUCERS_DEFAULT = 2;     // measured: a third changes nothing (VGG conv1_2 GEMM 0.615 vs 0.624 ms, c1 0.335 vs 0.338 ms)
+constexpr int GEMM_EPI_WARP0 = 4;
+constexpr int GEMM_SPLIT_WARP0 = GEMM_EPI_WARP0 + GEMM_EPI_WARPS;
+constexpr int GEMM_THREADS = (GEMM_SPLIT_WARP0 + GEMM_CONV_GROUPS * GEMM_CONV_WARPS) * 32;
+static_assert(GEMM_EPI_WARP0 % 4 == 0 && GEMM_EPI_WARPS % 4 == 0 && GEMM_CONV_WARPS == 4, "roles must fill whole warpgroups");
+// Registers per thread after the set-up: the epilogue warpgroups hold a whole 128 x 256 accumulator
+// (128 values per thread) so that tensor memory is released before the global stores; the other
+// warpgroups give theirs up.  (2 x 128 x 176 + 2 x 128 x 80 = the 64 K registers the launch owns.)
+constexpr int GEMM_EPI_REGS = 184, GEMM_OTHER_REGS = 72;
+static_assert(GEMM_CONV_GROUPS == 1, "the register split assumes four warpgroups");
 constexpr size_t WORKSPACE_BUDGET = size_t(6) << 30;   // transform-domain buffers per chunk
 
 enum : int { KIND_F32 = 0, KIND_I8 = 1 };
@@ -501,9 +513,11 @@ struct WinoGemmParams {
   // A is fetched from the user's tensor by tiled copies, the epilogue adds bias (+ stored output),
   // clamps and writes nChw16c.
   int flat, HW, tiles_img, CB;
-  int prefetch;             // a separate warp asks L2 for the A stages one tile ahead
   int rotate_k;             // tiles start their K loop at different stages (spreads the weight reads over L2)
-  int spp;                  // pipeline stages a producer warp fills per pass (1 or 2); the two warps alternate passes
+  int producers;            // producer warps taking turns on the stages (1..3)
+  int kmul;                 // fp32 with A in tensor memory: K stages (16 channels each) fetched, split and handed over as ONE
+                            // pipeline step (1 or 2; divides k_stages; the kernel's KMUL).  The hand-overs between the roles cost about a
+                            // thousand cycles per step whatever its size, which narrow tiles cannot hide behind their MMAs.
   int a_tmem;               // fp32, single CTAs: A planes in tensor memory (see the kernel)
   int stack;                // fp32, single CTAs, BN <= 128: the hi and lo weight rows of a K chunk lie one after the
                             // other, so hi*[hi;lo] is ONE MMA of 2*BN columns and the 3xTF32 product takes two MMAs
@@ -529,9 +543,17 @@ struct WinoGemmParams {
 #else
 #define WG_TRACE2(slot) do { } while (0)
 #endif
+#ifdef ELB_TUNING
+#define TR0 (static_cast<uint32_t>(p.ablate) >> 16)     // first pipeline stage the timeline records (steady state instead of start-up)
+#else
+#define TR0 0u
+#endif
 #define WG_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
-template <bool CTA2>
+// KMUL: K stages per pipeline step (WinoGemmParams::kmul); a template argument because the role
+// loops are single threads bound by instruction latency -- as a run-time loop count the same code
+// measured 10-20 % slower at kmul = 1.
+template <bool CTA2, int KMUL = 1>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid_constant__ WinoGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -548,7 +570,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   uint64_t *tempty = tfull + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  volatile int *tile_started = reinterpret_cast<volatile int *>(tmem_slot + 2);     // producers' progress, for the prefetch warp
   // int8 only: per-epilogue-warp copies of the scale / shift slice of the current tile
   float *epi_consts = reinterpret_cast<float *>(consts_area);
 
@@ -581,8 +602,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // deeper ring: 4 stages at BN = 256 (5 with A in tensor memory), 6 at 128, up to 8 below.
   // (Measured: the extra depth changes nothing on the 64- and 128-channel VGG layers, whose stages
   // land about 1400 cycles apart however many are in flight.)
-  const int stage_bytes = a_in_tmem ? A_RAW_BYTES + 128 * BN : CTA2 ? STAGE_BYTES : A_STAGE_BYTES + 128 * BN;
-  const int b_off = a_in_tmem ? A_RAW_BYTES : A_STAGE_BYTES;
+  constexpr int kmul = KMUL;                      // (KMUL > 1 is launched only with A in tensor memory, not in flat mode)
+  const int ksteps = p.k_stages / kmul;           // pipeline steps per tile
+  const int stage_bytes = a_in_tmem ? kmul * (A_RAW_BYTES + 128 * BN) : CTA2 ? STAGE_BYTES : A_STAGE_BYTES + 128 * BN;
+  const int b_off = a_in_tmem ? kmul * A_RAW_BYTES : A_STAGE_BYTES;
   // the ring may also use the area of the int8 epilogue constants when the kernel runs fp32
   // (Staging the result of a one-accumulator tile through shared memory and bulk-storing it from
   // there, so that tensor memory is released after it has been read, was measured and is SLOWER: c1
@@ -590,7 +613,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // reads by the MMAs, 40 KB of incoming copies and 8 KB of splitter reads against 128 B/clk -- and
   // the detour adds 256 KB of shared-memory traffic per tile.)
   const int ring_bytes = GEMM_STAGES * STAGE_BYTES + (p.kind == KIND_F32 ? EPI_CONST_BYTES : 0);
-  const int nstages = CTA2 ? GEMM_STAGES : min(GEMM_MAX_STAGES, ring_bytes / stage_bytes);
+  const int nstages = CTA2 ? GEMM_STAGES : min(GEMM_MAX_STAGES / kmul, ring_bytes / stage_bytes);     // (8 A slots of 16 channels in tensor memory)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_MAX_STAGES; ++s) {
@@ -604,7 +627,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       mbar_init(&tempty[b], CTA2 ? 2 * GEMM_EPI_WARPS : GEMM_EPI_WARPS);      // one arrival per epilogue warp
     }
     *abort_flag = 0;
-    *tile_started = -1;
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -619,124 +641,94 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   const uint32_t tmem_base = *tmem_slot;
   int fail_code = 0;
 
-  if (warp == 0 || warp == GEMM_PRODUCER2_WARP) {
-    // -------- producers: two contiguous bulk copies per stage.  Issuing a copy costs its lane a few
-    // hundred cycles; lanes of one instruction overlap and warps issue independently.  A pass serves
-    // p.spp stages (lanes 0/1: A and B of one stage, lanes 2/3: of the next when spp = 2), and the
-    // two producer warps take turns on the passes.
-    const uint32_t pw = warp == 0 ? 0u : 1u;
-    const int spp = p.spp == 1 ? 1 : 2;
-    uint32_t it = 0, gpass = 0;
-    // ring slot / phase of stage `it`, kept as counters (an integer division costs this one-warp loop
-    // more than the copy instructions it issues)
-    int s_base = 0;
-    uint32_t ph_base = 0;
-    auto adv = [&](int n) { s_base += n; if (s_base >= nstages) { s_base -= nstages; ph_base ^= 1u; } };
-    auto back1 = [&]() { if (s_base == 0) { s_base = nstages - 1; ph_base ^= 1u; } else --s_base; };
-    bool ok = true;
+  if (warp < GEMM_EPI_WARP0) {
+  reg_dealloc<GEMM_OTHER_REGS>();      // (one instruction for the whole warpgroup, before its warps part ways)
+  if (warp != 1) {
+    // -------- producers (warps 0, 2 and optionally 3): two contiguous bulk copies per stage, issued by
+    // lanes 0 (A) and 1 (B).  Issuing a copy costs its lane a few hundred cycles and a pass through
+    // this loop about a thousand, all of it latency of a single warp -- so the warps take turns on
+    // the stages: stage i belongs to producer i mod p.producers.
+    const int pw = warp == 0 ? 0 : warp - 1;
+    const int np = p.producers;
+    int turn = 0;               // whose stage the current one is
+    // ring slot / phase of the current stage, kept as counters (an integer division costs this
+    // one-warp loop more than the copy instructions it issues)
+    int s = 0;
+    uint32_t ph = 0;
+    uint32_t my_pass = 0;       // (timeline only)
+    auto next_stage = [&]() {
+      if (++s == nstages) { s = 0; ph ^= 1u; }
+      if (++turn == np) turn = 0;
+    };
+    bool ok = pw < np;
     if (p.flat) {
-      // flat mode: lanes 0..3 / 8..11 fetch the four 16-byte channel chunks of a stage (boxes of
-      // 4 floats x 128 pixels, rows past the end of the plane arrive as zeros), lanes 4 / 12 the weights
-      const int grp = lane >> 3, gl = lane & 7;
+      // flat mode: lanes 0..3 fetch the four 16-byte channel chunks of a stage (boxes of 4 floats x
+      // 128 pixels, rows past the end of the plane arrive as zeros), lane 4 the weights
       if (lane == 0) tma_prefetch_desc(&p.tmap_a);
       for (int tile = first; tile < total_tiles && ok; tile += step) {
         const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
         const int n = mt / p.tiles_img, ptile = mt - n * p.tiles_img;
         const uint8_t *b_src = p.b_img + static_cast<size_t>(nt) * p.k_stages * b_stage_bytes;
-        // CTAs that run side by side multiply by the same weights: each tile starts its K loop at a
+        // CTAs that run side by side multiply by the same weights: each tile may start its K loop at a
         // different stage so that they do not all ask the same L2 lines at the same moment
         const int rot = p.rotate_k ? tile % p.k_stages : 0;
-        for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass, adv(spp)) {
-          if ((gpass & 1u) != pw) continue;
-          const int ks = ks0 + grp;
+        for (int ks = 0; ks < p.k_stages; ++ks, next_stage()) {
+          if (turn != pw) continue;
           const int ksr = ks + rot < p.k_stages ? ks + rot : ks + rot - p.k_stages;     // rotated K stage
-          const bool active = grp < spp && gl < 5 && ks < p.k_stages;
-          int s = s_base + grp;
-          uint32_t ph = ph_base;
-          if (s >= nstages) { s -= nstages; ph ^= 1u; }
           int w_ok = 1;
-          if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
+          if (lane == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
           if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
           uint8_t *stage = smem + s * stage_bytes;
-          if (active && gl == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(A_RAW_BYTES) + b_stage_bytes);
+          if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(A_RAW_BYTES) + b_stage_bytes);
           __syncwarp();
-          if (active) {
-            if (gl < 4) tma_tile_3d(stage + gl * 2048, &p.tmap_a, 4 * gl, ptile * BM, n * p.CB + ksr, &full[s]);
-            else tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_stage_bytes, b_stage_bytes, &full[s]);
-          }
+          if (lane < 4) tma_tile_3d(stage + lane * 2048, &p.tmap_a, 4 * lane, ptile * BM, n * p.CB + ksr, &full[s]);
+          else if (lane == 4) tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_stage_bytes, b_stage_bytes, &full[s]);
           __syncwarp();
         }
-        if (spp == 2 && (p.k_stages & 1)) { --it; back1(); }
       }
     }
-    const int grp = lane >> 1, gl = lane & 1;      // lanes 0..3 work: stage-in-pass, A / B
-    for (int tile = first; tile < total_tiles && ok && !p.flat; tile += step) {
-      const int a = tile / tiles_per_a;
-      const int r = tile - a * tiles_per_a;
-      const int nt = r / m_units, mu = r - nt * m_units;
+    // fp32: A arrives as plain fp32 (8 KB per stage) in the raw ring; int8: straight into the stage
+    const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
+    const size_t b_pitch = static_cast<size_t>(CTA2 ? 2 : 1) * b_stage_bytes;
+    // position a and index r within it of the current tile, carried along instead of divided out
+    int a = first / tiles_per_a, r = first - a * tiles_per_a;
+    uint32_t tcount = 0;
+    for (int tile = first; tile < total_tiles && ok && !p.flat; tile += step, ++tcount) {
+      int nt = 0, mu = r;
+      while (mu >= m_units) { mu -= m_units; ++nt; }        // (one or two n tiles)
       const int mt = CTA2 ? 2 * mu + static_cast<int>(rank) : mu;
       const bool live = mt < p.m_tiles;            // an odd number of row blocks leaves the last peer without one
-      // fp32: A arrives as plain fp32 (8 KB per stage) in the raw ring; int8: straight into the stage
-      const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
       const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + (live ? mt : 0)) * p.k_stages * a_gbytes;
       // pairs: the weight image holds the two halves of every stage one after the other
-      const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * (CTA2 ? 2 : 1) * b_stage_bytes +
+      const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * b_pitch +
                              (CTA2 ? rank * b_stage_bytes : 0);
-      const size_t b_pitch = static_cast<size_t>(CTA2 ? 2 : 1) * b_stage_bytes;
-      const int rot = p.rotate_k ? tile % p.k_stages : 0;      // see the flat-mode loop above
-      if (pw == 0 && lane == 0 && (p.prefetch || p.trace)) {
-        *tile_started = static_cast<int>(it / p.k_stages);
-        if (it / p.k_stages < 8) WG_TRACE(it / p.k_stages);
-      }
-      for (int ks0 = 0; ks0 < p.k_stages; ks0 += spp, it += spp, ++gpass, adv(spp)) {
-        if ((gpass & 1u) != pw) continue;            // the other producer warp's pass
-        const int ks = ks0 + grp;
-        const int ksr = ks + rot < p.k_stages ? ks + rot : ks + rot - p.k_stages;
-        const bool active = grp < spp && ks < p.k_stages;
-        int s = s_base + grp;
-        uint32_t ph = ph_base;
-        if (s >= nstages) { s -= nstages; ph ^= 1u; }
+      const int rot = p.rotate_k ? tile % ksteps : 0;      // see the flat-mode loop above
+      if (pw == 0 && lane == 0 && tcount < 8) WG_TRACE(tcount);
+      for (int ks = 0; ks < ksteps; ++ks, next_stage()) {
+        if (turn != pw) continue;            // another producer warp's stage
+        const int ksr = ks + rot < ksteps ? ks + rot : ks + rot - ksteps;
         // empty[s] is committed by the MMAs of the stage's previous use, which also implies that the
         // splitter warps are done with raw slot s
         int w_ok = 1;
-        if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(2 * gpass);
-        if (active && gl == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
+        if (pw == 0 && lane == 0 && my_pass - TR0 < 12u) WG_TRACE2(2 * (my_pass - TR0));
+        if (lane == 0) w_ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
         if (!__all_sync(0xFFFFFFFFu, w_ok)) { ok = false; fail_code = ST_WAIT_TIMEOUT_PRODUCER; break; }
-        if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(2 * gpass + 1);
+        if (pw == 0 && lane == 0 && my_pass - TR0 < 12u) WG_TRACE2(2 * (my_pass - TR0) + 1);
         uint8_t *stage = smem + s * stage_bytes;
-        if (active && gl == 0) mbar_arrive_expect_tx(&full[s], (live && !ABL(8) ? a_gbytes : 0u) + (ABL(16) ? 0u : b_stage_bytes));
+        // (the kmul K stages of a step lie one after the other in both operand images)
+        if (lane == 0) mbar_arrive_expect_tx(&full[s], (live && !ABL(8) ? a_gbytes * kmul : 0u) + (ABL(16) ? 0u : b_stage_bytes * kmul));
         __syncwarp();
-        if (active) {
-          if (gl == 0) {
-            if (live && !ABL(8))
-              tma_bulk_g2s(stage, a_src + static_cast<size_t>(ksr) * a_gbytes, a_gbytes, &full[s]);
-          } else if (!ABL(16)) {
-            tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_pitch, b_stage_bytes, &full[s]);
-          }
+        if (lane == 0) {
+          if (live && !ABL(8)) tma_bulk_g2s(stage, a_src + static_cast<size_t>(ksr) * a_gbytes * kmul, a_gbytes * kmul, &full[s]);
+        } else if (lane == 1 && !ABL(16)) {
+          tma_bulk_g2s(stage + b_off, b_src + static_cast<size_t>(ksr) * b_pitch * kmul, b_stage_bytes * kmul, &full[s]);
         }
         __syncwarp();
-        if (pw == 0 && lane == 0 && gpass < 12) WG_TRACE2(24 + gpass / 2);
+        if (pw == 0 && lane == 0 && my_pass - TR0 < 6u) WG_TRACE2(24 + (my_pass - TR0));
+        ++my_pass;
       }
-      if (spp == 2 && (p.k_stages & 1)) { --it; back1(); }        // the last pass of an odd K loop served one stage only
-    }
-  } else if (warp == GEMM_PREFETCH_WARP) {
-    // -------- optional L2 prefetch of the A operand, one tile ahead of the producers (an experiment:
-    // it does not change the rate at which stages land).  The warp itself stays: with sixteen warps
-    // instead of fifteen the kernel measured 3 % faster on the same GPU (VGG-16 fp32 stack 5.00 ->
-    // 4.85 ms, its 3 -> 64 channel layer 0.72 -> 0.61 ms), whether or not this role does anything.
-    if (lane == 0 && p.prefetch && !p.flat && !CTA2) {
-      const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
-      int j = 0;
-      for (int tile = first; tile < total_tiles; tile += step, ++j) {
-        const long long t0 = clock64();
-        while (*tile_started < j - 1 && !*abort_flag && clock64() - t0 < WAIT_LIMIT_CYCLES) {
-        }
-        const int a = tile / tiles_per_a;
-        const int r = tile - a * tiles_per_a;
-        const int mt = r % m_units;
-        const uint8_t *a_src = p.a_img + (static_cast<size_t>(a) * p.m_pitch + mt) * p.k_stages * a_gbytes;
-        for (int ks = 0; ks < p.k_stages; ++ks) tma_prefetch_l2(a_src + static_cast<size_t>(ks) * a_gbytes, a_gbytes);
-      }
+      r += step;
+      while (r >= tiles_per_a) { r -= tiles_per_a; ++a; }
     }
   } else if (warp == 1) {
     // -------- MMA issuer (pairs: in the leader CTA only; the peer's lane forwards stage readiness)
@@ -770,26 +762,33 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const uint32_t idesc2 = umma_idesc(1, 2, 2, MM, 2 * BN);
       const uint32_t smem_base = smem_u32(smem);
       bool ok = true;
+      bool staged = false;        // the first stage of this tile was already waited for (behind the previous tile's MMAs)
       for (int tile = first; tile < total_tiles && ok; tile += step, ++tcount) {
         const uint32_t b = acc_bufs == 1 ? 0u : (tcount & 1u), tph = acc_bufs == 1 ? (tcount & 1u) : ((tcount >> 1) & 1u);
-        if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-        tc_fence_after_sync();
-        if (tcount < 8) WG_TRACE(8 + tcount);
         const uint32_t d_tmem = tmem_base + b * acc_stride;
         // The waits for stage ks + 1 are issued BETWEEN the two K steps of stage ks: a wait costs this
         // thread ~300 cycles of latency even when the barrier has completed, and behind the first K
         // step's three MMAs (queued in the tensor pipe) that latency is hidden; done between the
         // stages it left the pipe idle a third of the time (measured timeline, 256-channel layer).
+        // fp32 on single CTAs: the splitter warps arrive on cfull only after they have seen full (the
+        // weights of the stage come with the same transaction count), so cfull alone orders this
+        // thread behind both copies -- one barrier round trip less per stage.
         auto wait_stage = [&](int st, uint32_t phase) -> bool {
-          if (!mbar_wait(&full[st], phase, abort_flag)) return false;
+          if ((CTA2 || p.kind != KIND_F32) && !mbar_wait(&full[st], phase, abort_flag)) return false;
           if (p.kind == KIND_F32 && !mbar_wait(&cfull[st], phase, abort_flag)) return false;
           if (CTA2 && !mbar_wait(&pfull[st], phase, abort_flag)) return false;
           tc_fence_after_sync();
           return true;
         };
-        if (!wait_stage(s, ph)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          if (it < 6) WG_TRACE2(33 + 3 * it);
+        // first the operands (long there unless `staged` already), then the accumulator buffer: the
+        // wait that really blocks comes last
+        if (!staged && !wait_stage(s, ph)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        staged = false;
+        if (!mbar_wait(&tempty[b], tph ^ 1u, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+        tc_fence_after_sync();
+        if (tcount < 8) WG_TRACE(8 + tcount);
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          if (it - TR0 < 6u) WG_TRACE2(33 + 3 * (it - TR0));
           if (ks == 0 && tcount < 8) WG_TRACE(16 + tcount);
           const uint32_t a_addr = smem_base + s * stage_bytes;
           const uint32_t b_addr = a_addr + b_off;
@@ -797,39 +796,59 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           int s_next = s + 1;
           uint32_t ph_next = ph;
           if (s_next == nstages) { s_next = 0; ph_next ^= 1u; }
-          const bool more = ks + 1 < p.k_stages;
+          // (the look-ahead crosses into the next tile: its first stage follows in the ring)
+          const bool last_ks = ks + 1 == ksteps;
+          const bool more = !last_ks || tile + step < total_tiles;
+          if (last_ks && more) staged = true;
           if (ABL(2)) {
             if (more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           } else if (stack) {
             // hi * [hi; lo] in one MMA of 2*BN columns, lo * hi in one of BN columns (same descriptor:
             // the first BN rows of a chunk are the hi rows)
-            const uint64_t st_desc = st_desc_hi | (b_addr >> 4);
+            // (j: the K stages of this pipeline step; more than one only with A in tensor memory)
+#pragma unroll
+            for (int j = 0; j < kmul; ++j) {
+            const uint64_t st_desc = st_desc_hi | ((b_addr + j * 128 * BN) >> 4);
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2) {
               const uint64_t bst = st_desc + ((k2 * 2 * st_lbo) >> 4);
               if (a_in_tmem) {
-                const uint32_t t_hi = tmem_base + A_TMEM_COL0 + s * 32 + k2 * 8, t_lo = t_hi + 16;
-                umma_tf32_ts(d_tmem, t_hi, bst, idesc2, (ks | k2) != 0 ? 1u : 0u);
+                const uint32_t t_hi = tmem_base + A_TMEM_COL0 + (s * kmul + j) * 32 + k2 * 8, t_lo = t_hi + 16;
+#ifdef ELB_TUNING
+                // timing experiments (wrong results): 32 = the lo MMA accumulates elsewhere, 64 = the two K steps do
+                const uint32_t d_hi = (ABL(64) && k2) ? (d_tmem ^ 256u) : d_tmem;
+                const uint32_t d_lo = ABL(32) ? (d_hi ^ 128u) : d_hi;
+                if (it == TR0 + 2) WG_TRACE2(52 + (j * 2 + k2) * 3);
+                umma_tf32_ts(d_hi, t_hi, bst, idesc2, (ks | j | k2) != 0 ? 1u : 0u);
+                if (it == TR0 + 2) WG_TRACE2(53 + (j * 2 + k2) * 3);
+                umma_tf32_ts(d_lo, t_lo, bst, idesc, 1u);
+                if (it == TR0 + 2) WG_TRACE2(54 + (j * 2 + k2) * 3);
+#else
+                umma_tf32_ts(d_tmem, t_hi, bst, idesc2, (ks | j | k2) != 0 ? 1u : 0u);
                 umma_tf32_ts(d_tmem, t_lo, bst, idesc, 1u);
+#endif
               } else {
                 umma_tf32(d_tmem, a_desc + ((k2 * 4096) >> 4), bst, idesc2, (ks | k2) != 0 ? 1u : 0u);
                 umma_tf32(d_tmem, a_desc + ((8192 + k2 * 4096) >> 4), bst, idesc, 1u);
               }
-              if (k2 == 0 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
+              if (j == 0 && k2 == 0 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
+            }
             }
             if (!ok) break;
           } else if (p.kind == KIND_F32) {
             // planes: A hi at +0, lo at +8 KB; B hi at +0, lo at +4 chunks.  K step = 2 chunks.
 #pragma unroll
+            for (int j = 0; j < kmul; ++j) {
+#pragma unroll
             for (int k2 = 0; k2 < 2; ++k2) {
               const uint64_t ahi = a_desc + ((k2 * 4096) >> 4);
               const uint64_t alo = a_desc + ((8192 + k2 * 4096) >> 4);
-              const uint64_t bhi = b_desc + ((k2 * 2 * b_lbo) >> 4);
-              const uint64_t blo = b_desc + ((4 * b_lbo + k2 * 2 * b_lbo) >> 4);
+              const uint64_t bhi = b_desc + ((j * 128 * BN + k2 * 2 * b_lbo) >> 4);
+              const uint64_t blo = b_desc + ((j * 128 * BN + 4 * b_lbo + k2 * 2 * b_lbo) >> 4);
               if (a_in_tmem) {
                 // A planes in tensor memory: hi at columns [0,16) of the stage's slot, lo at [16,32)
-                const uint32_t t_hi = tmem_base + A_TMEM_COL0 + s * 32 + k2 * 8, t_lo = t_hi + 16;
-                umma_tf32_ts(d_tmem, t_lo, bhi, idesc, (ks | k2) != 0 ? 1u : 0u);
+                const uint32_t t_hi = tmem_base + A_TMEM_COL0 + (s * kmul + j) * 32 + k2 * 8, t_lo = t_hi + 16;
+                umma_tf32_ts(d_tmem, t_lo, bhi, idesc, (ks | j | k2) != 0 ? 1u : 0u);
                 umma_tf32_ts(d_tmem, t_hi, blo, idesc, 1u);
                 umma_tf32_ts(d_tmem, t_hi, bhi, idesc, 1u);
               } else if (CTA2) {
@@ -841,7 +860,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
                 umma_tf32(d_tmem, ahi, blo, idesc, 1u);
                 umma_tf32(d_tmem, ahi, bhi, idesc, 1u);
               }
-              if (k2 == 0 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
+              if (j == 0 && k2 == 0 && more && !wait_stage(s_next, ph_next)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; }
+            }
             }
             if (!ok) break;
           } else {
@@ -857,7 +877,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           }
           if (CTA2) umma_commit_2cta(&empty[s]);
           else umma_commit(&empty[s]);
-          if (it < 6) WG_TRACE2(34 + 3 * it);
+          if (it - TR0 < 6u) WG_TRACE2(34 + 3 * (it - TR0));
           s = s_next;
           ph = ph_next;
         }
@@ -869,23 +889,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       }
     }
     __syncwarp();
-  } else if (warp >= 2 + GEMM_EPI_WARPS) {      // (the second producer warp took the first branch)
+  }
+  } else if (warp >= GEMM_SPLIT_WARP0) {
+    reg_dealloc<GEMM_OTHER_REGS>();
     // -------- splitter (fp32 only): raw fp32 stage -> tf32 hi plane + residual lo plane, the
     // operands of the 3xTF32 product.  hi = round-to-nearest tf32(x), lo = x - hi (exact).
     if (p.kind == KIND_F32) {
-      const int cgrp = (warp - 2 - GEMM_EPI_WARPS) / GEMM_CONV_WARPS;       // this warp's group
-      const int tid_c = ((warp - 2 - GEMM_EPI_WARPS) % GEMM_CONV_WARPS) * 32 + lane;
+      const int cgrp = (warp - GEMM_SPLIT_WARP0) / GEMM_CONV_WARPS;       // this warp's group
+      const int tid_c = ((warp - GEMM_SPLIT_WARP0) % GEMM_CONV_WARPS) * 32 + lane;
       uint32_t it = 0;
       int s = 0;
       uint32_t ph = 0;
       auto next_slot = [&]() { if (++s == nstages) { s = 0; ph ^= 1u; } };      // (no divisions: see the MMA loop)
       bool ok = true;
       for (int tile = first; tile < total_tiles && ok; tile += step) {
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it, next_slot()) {
+        for (int ks = 0; ks < ksteps; ++ks, ++it, next_slot()) {
           if (GEMM_CONV_GROUPS > 1 && static_cast<int>(it % GEMM_CONV_GROUPS) != cgrp) continue;       // the other group's stage
-          if (tid_c == 0 && it < 6) WG_TRACE2(50 + it);
+          if (tid_c == 0 && it - TR0 < 2u) WG_TRACE2(50 + (it - TR0));
           if (!mbar_wait_warp(&full[s], ph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
-          if (tid_c == 0 && it < 8) WG_TRACE(48 + 2 * it);
+          if (tid_c == 0 && it - TR0 < 8u) WG_TRACE(48 + 2 * (it - TR0));
           if (ABL(1)) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&cfull[s]);
@@ -897,28 +919,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
             // shared memory, next to the incoming copies, saturated its port).  Warp w may only
             // address lanes 32*(w%4)..: the four splitter warps cover the four quarters.
             const int quarter = warp & 3, srow = quarter * 32 + lane;
-            const float4 *raw4 = reinterpret_cast<const float4 *>(smem + s * stage_bytes);
-            uint32_t h[16], l[16];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float4 v = raw4[j * BM + srow];
-              const float x[4] = {v.x, v.y, v.z, v.w};
+            for (int q = 0; q < kmul; ++q) {        // the K stages of this pipeline step
+              const float4 *raw4 = reinterpret_cast<const float4 *>(smem + s * stage_bytes + q * A_RAW_BYTES);
+              uint32_t h[16], l[16];
 #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                uint32_t hb;
-                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[c]));
-                h[4 * j + c] = hb;
-                l[4 * j + c] = __float_as_uint(__fsub_rn(x[c], __uint_as_float(hb)));
+              for (int j = 0; j < 4; ++j) {
+                const float4 v = raw4[j * BM + srow];
+                const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  uint32_t hb;
+                  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[c]));
+                  h[4 * j + c] = hb;
+                  l[4 * j + c] = __float_as_uint(__fsub_rn(x[c], __uint_as_float(hb)));
+                }
               }
+              const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + A_TMEM_COL0 + (s * kmul + q) * 32;
+              tmem_st16(t_slot, h);
+              tmem_st16(t_slot + 16, l);
             }
-            const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + A_TMEM_COL0 + s * 32;
-            tmem_st16(t_slot, h);
-            tmem_st16(t_slot + 16, l);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&cfull[s]);
-            if (tid_c == 0 && it < 8) WG_TRACE(49 + 2 * it);
+            if (tid_c == 0 && it - TR0 < 8u) WG_TRACE(49 + 2 * (it - TR0));
             continue;
           }
           float4 *hi = reinterpret_cast<float4 *>(smem + s * stage_bytes);     // holds the raw fp32 values on arrival
@@ -949,12 +974,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     }
   } else {
     // -------- epilogue: one tile row (= one Winograd tile) per thread, 16 channels at a time
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    reg_alloc<GEMM_EPI_REGS>();
+    const int quarter = warp & 3, half = (warp - GEMM_EPI_WARP0) >> 2;
     const int row = quarter * 32 + lane;
     const int OCP = p.OCB * 16;
     uint32_t tcount = 0;
     bool ok = true;
     const uint32_t tempty_leader0 = CTA2 ? mapa_u32(&tempty[0], 0) : 0u, tempty_leader1 = CTA2 ? mapa_u32(&tempty[1], 0) : 0u;
+    // The tile loop exists twice (EARLY = one accumulator buffer, whose contents go to registers
+    // first): compiled as one loop with both bodies the register allocator kept both sets of
+    // accumulator registers alive and spilled.
+    auto tile_loop = [&](auto early_tag) {
+    constexpr bool EARLY = decltype(early_tag)::value;
     for (int tile = first; tile < total_tiles && ok; tile += step, ++tcount) {
       const int a = tile / tiles_per_a;
       const int r = tile - a * tiles_per_a;
@@ -965,12 +996,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       const int t = mt * BM + row;
       if (!mbar_wait_warp(&tfull[b], tph, abort_flag)) { ok = false; fail_code = ST_WAIT_TIMEOUT_EPILOGUE; break; }
       tc_fence_after_sync();
-      if (threadIdx.x == 64 && tcount < 8) WG_TRACE(32 + tcount);
+      if (threadIdx.x == GEMM_EPI_WARP0 * 32 && tcount < 8) WG_TRACE(32 + tcount);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * acc_stride;
       // int8: this warp's slice of the per-(position, channel) constants goes to a warp-private
       // piece of shared memory first (one 16-byte load per lane and array), so that the loop below
       // reads them with broadcast shared-memory loads instead of waiting on global memory
-      float *w_sc = epi_consts + (warp - 2) * 2 * MAX_BN, *w_sh = w_sc + MAX_BN;
+      float *w_sc = epi_consts + (warp - GEMM_EPI_WARP0) * 2 * MAX_BN, *w_sh = w_sc + MAX_BN;
       if (p.kind == KIND_I8) {
         __syncwarp();
 #pragma unroll
@@ -987,10 +1018,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       // flat mode: this thread's row is pixel flat_pix of image flat_n
       const int flat_n = p.flat ? mt / p.tiles_img : 0;
       const int flat_pix = p.flat ? (mt - flat_n * p.tiles_img) * BM + row : 0;
-      auto emit = [&](int k, uint32_t (&rr)[16]) {      // k-th 16-column block of this warp
+      auto emit = [&](int k, uint32_t (&rr)[16], bool partner_added) {      // k-th 16-column block of this warp
         const int blk = half + 2 * k;
         const int ocb = nt * (BN / 16) + blk;
-        if (stack) {
+        if (stack && !partner_added) {
           // columns [BN, 2*BN) hold the hi*lo part of the same outputs
           uint32_t r2[16];
           tmem_ld16(t_addr + BN + blk * 16, r2);
@@ -1057,6 +1088,37 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       // pair is already on its way (wait::ld covers every load issued so far).
       const int nblk = (BN / 16 - half + 1) / 2;      // blocks of this warp (may be 0)
       const uint32_t w_addr = t_addr + half * 16;     // k-th block at +32*k columns
+      if constexpr (EARLY) {
+        // One accumulator buffer: the next tile's MMAs wait for this epilogue.  The whole share of the
+        // warp (up to 8 blocks = 128 values per thread, stacked partners included) is read into
+        // registers, tensor memory is handed back, and only then are the results converted and stored:
+        // the MMAs stand still for the ~600 cycles of the loads instead of the ~9000 of the stores.
+        uint32_t acc[8][16];
+        const int nmain = stack ? min(nblk, 4) : nblk;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (!stack) { if (k < nblk) tmem_ld16(w_addr + k * 32, acc[k]); }
+          else if (k < 4) { if (k < nblk) tmem_ld16(w_addr + k * 32, acc[k]); }
+          else if (k - 4 < nblk) tmem_ld16(w_addr + BN + (k - 4) * 32, acc[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tmem_ld_wait16(acc[k]);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[b]);
+        if (threadIdx.x == GEMM_EPI_WARP0 * 32 && tcount < 8) WG_TRACE(40 + tcount);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k < nmain) {
+            if (stack) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                acc[k][i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[k][i]), __uint_as_float(acc[(k + 4) & 7][i])));
+            }
+            emit(k, acc[k], true);
+          }
+        }
+      } else {
       uint32_t r0[16], r1[16], r2[16], r3[16];
       if (0 < nblk) tmem_ld16(w_addr, r0);
       if (1 < nblk) tmem_ld16(w_addr + 32, r1);
@@ -1066,14 +1128,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         tmem_ld_wait16(r1);
         if (k + 2 < nblk) tmem_ld16(w_addr + (k + 2) * 32, r2);
         if (k + 3 < nblk) tmem_ld16(w_addr + (k + 3) * 32, r3);
-        emit(k, r0);
-        if (k + 1 < nblk) emit(k + 1, r1);
+        emit(k, r0, false);
+        if (k + 1 < nblk) emit(k + 1, r1, false);
         tmem_ld_wait16(r2);
         tmem_ld_wait16(r3);
         if (k + 4 < nblk) tmem_ld16(w_addr + (k + 4) * 32, r0);
         if (k + 5 < nblk) tmem_ld16(w_addr + (k + 5) * 32, r1);
-        if (k + 2 < nblk) emit(k + 2, r2);
-        if (k + 3 < nblk) emit(k + 3, r3);
+        if (k + 2 < nblk) emit(k + 2, r2, false);
+        if (k + 3 < nblk) emit(k + 3, r3, false);
       }
       tc_fence_before_sync();
       // one arrival per warp (pairs: on the LEADER's barrier, the accumulator is reused by MMAs that
@@ -1083,8 +1145,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         if (CTA2) mbar_arrive_cluster(b ? tempty_leader1 : tempty_leader0);
         else mbar_arrive(&tempty[b]);
       }
-      if (threadIdx.x == 64 && tcount < 8) WG_TRACE(40 + tcount);
+      if (threadIdx.x == GEMM_EPI_WARP0 * 32 && tcount < 8) WG_TRACE(40 + tcount);
+      }
     }
+    };
+    if (acc_bufs == 1) tile_loop(std::true_type{});
+    else tile_loop(std::false_type{});
   }
 
   if (fail_code != 0) atomicCAS(p.status, 0, fail_code);
@@ -1436,8 +1502,13 @@ std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, in
 // 0.108 -> 0.097 ms) and whenever a CTA runs a single tile (1x1 benchmark layer 68.9 -> 55.9 us).
 // With stacked weights of at most 64 output channels the accumulator is 128 columns wide, two of
 // them fit beside the A slots, and A in tensor memory costs nothing: always on there.
-inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms, int acc_width = 256) {
-  const int dflt = kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms || acc_width <= 128) ? 1 : 0;
+// Since the epilogue of a one-accumulator tile releases tensor memory before it stores (and steps of
+// two K stages need A in tensor memory, see tune_kmul), tiles of at most 128 output channels take
+// it from 8 K stages up: VGG conv2_2 (128 -> 128 channels) GEMM 0.306 -> 0.256 ms with steps of
+// two stages, even at 4 stages (conv2_1 0.180 vs 0.182 ms).
+inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms, int acc_width = 256, int BN = 256) {
+  const int dflt = kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms || acc_width <= 128 ||
+                                        (BN <= 128 && k_stages >= 8 && k_stages % 2 == 0)) ? 1 : 0;
   return tune_env("ELB_F32_A_TMEM", dflt) > 0 ? 1 : 0;
 }
 // K rotation spreads the weight reads of CTAs running side by side over L2; measured without effect
@@ -1445,12 +1516,21 @@ inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sm
 inline int tune_rotate_k() {
   return tune_env("ELB_WINO_ROTATE_K", 0) > 0 ? 1 : 0;
 }
-// Stages per producer pass.  One stage per pass refills a slot as soon as it is free (a pass of two
-// waits for both); two per pass doubles the issue rate.  fp32 needs a stage every ~800 cycles at
-// best and gains from the shorter wait on every layer of the VGG-16 stack (conv3_2 0.368 -> 0.351 ms),
-// int8 Winograd does not care.
-inline int tune_spp(int kind) {
-  return tune_env("ELB_WINO_SPP", kind == KIND_F32 ? 1 : 2) == 1 ? 1 : 2;
+// K stages per pipeline step (WinoGemmParams::kmul).  Tiles of at most 128 output channels spend
+// more time handing a stage from role to role than multiplying it, so they move two stages at a
+// time (VGG conv1_2, 64 -> 64 channels: GEMM 0.610 -> 0.447 ms); 256-wide tiles are bound by their
+// MMAs and keep the deeper ring of single stages.
+inline int tune_kmul(int kind, int a_tmem, int k_stages, int BN) {
+  int v = tune_env("ELB_WINO_KMUL", (kind == KIND_F32 && a_tmem && BN <= 128) ? 2 : 1);
+  if (kind != KIND_F32 || !a_tmem || v != 2) return 1;
+  const int ring_bytes = GEMM_STAGES_1 * (A_STAGE_BYTES + B_STAGE_MAX) + EPI_CONST_BYTES;
+  while (v > 1 && (k_stages % v != 0 || ring_bytes / (v * (A_RAW_BYTES + 128 * BN)) < 2)) v /= 2;
+  return v;
+}
+// Producer warps taking turns on the stages (1..GEMM_PRODUCERS).
+inline int tune_producers() {
+  const int n = tune_env("ELB_WINO_PRODUCERS", GEMM_PRODUCERS_DEFAULT);
+  return n < 1 ? 1 : n > GEMM_PRODUCERS ? GEMM_PRODUCERS : n;
 }
 
 }  // namespace
@@ -1547,6 +1627,8 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
     w->mrepS = d.input_scale * rep;                                      // src/elx_conv_wino_trans_input.cpp:617
   }
   cudaError_t e = cudaFuncSetAttribute(wino_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(wino_gemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(wino_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return ELB_GENERAL_ERROR; }
@@ -1757,11 +1839,12 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.OCB = g.OCB; gp.Tpad = 0; gp.T = count * HW; gp.kind = KIND_F32;
     gp.positions = 1;
     gp.flat = 1; gp.HW = HW; gp.tiles_img = tiles_img; gp.CB = g.CB;
-    gp.spp = tune_spp(KIND_F32);
+    gp.producers = tune_producers();
     gp.rotate_k = tune_rotate_k();
     gp.stack = w->stack ? 1 : 0;
     gp.a_tmem = tune_a_tmem(KIND_F32, gp.k_stages, static_cast<long long>(gp.m_tiles) * gp.n_tiles, num_sms,
                             w->stack ? 2 * w->BN : w->BN);
+    gp.kmul = 1;
     gp.bias = static_cast<const float *>(w->d_bias);
     gp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
     gp.with_bias = w->with_bias; gp.with_relu = w->with_relu; gp.with_sum = w->with_sum;
@@ -1826,14 +1909,13 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.n_tiles = w->n_tiles; gp.k_stages = g.k_stages; gp.BN = w->BN;
     gp.OCB = g.OCB; gp.Tpad = w->g.Tpad; gp.T = g.T; gp.kind = w->kind;
     gp.positions = g.A * g.A;
-    gp.spp = tune_spp(w->kind);
+    gp.producers = tune_producers();
     gp.rotate_k = tune_rotate_k();
-    // opt-in: measured without effect (VGG conv1_2 GEMM 0.786 vs 0.788 ms, conv3_2 0.427 vs 0.433 ms)
-    gp.prefetch = tune_env("ELB_WINO_PREFETCH", 0) > 0 ? 1 : 0;
     gp.ablate = tune_env("ELB_ABL", 0);
     gp.stack = w->stack ? 1 : 0;
     gp.a_tmem = tune_a_tmem(w->kind, gp.k_stages, static_cast<long long>(gp.positions) * gp.m_tiles * gp.n_tiles, num_sms,
-                            w->stack ? 2 * w->BN : w->BN);
+                            w->stack ? 2 * w->BN : w->BN, w->BN);
+    gp.kmul = tune_kmul(w->kind, gp.a_tmem, gp.k_stages, w->BN);
     if (w->cta2) {
       const int pairs = gp.positions * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
       cudaLaunchConfig_t cfg{};
@@ -1849,7 +1931,8 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
       W_TRY(cudaLaunchKernelEx(&cfg, wino_gemm_kernel<true>, gp));
     } else {
       const int total = gp.positions * gp.m_tiles * gp.n_tiles;
-      wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+      if (gp.kmul == 2) wino_gemm_kernel<false, 2><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+      else wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
       W_TRY(cudaGetLastError());
     }
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[2], s));
@@ -2017,6 +2100,8 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
     e = cudaFuncSetAttribute(wino_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(wino_gemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
     if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
   }
@@ -2071,11 +2156,14 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   gp.m_tiles = g.m_tiles; gp.m_pitch = g.m_tiles; gp.n_tiles = n_tiles; gp.k_stages = g.k_stages; gp.BN = BN;
   gp.OCB = g.OCB; gp.Tpad = g.Tpad; gp.T = g.T; gp.kind = KIND_F32;
   gp.positions = 36;
-  gp.spp = 1;
+  gp.producers = GEMM_PRODUCERS_DEFAULT;
   const int total = 36 * gp.m_tiles * gp.n_tiles;
   gp.stack = stack;
-  gp.a_tmem = (gp.k_stages >= 16 || total <= num_sms || (stack ? 2 * BN : BN) <= 128) ? 1 : 0;
-  wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  gp.a_tmem = (gp.k_stages >= 16 || total <= num_sms || (stack ? 2 * BN : BN) <= 128 ||
+               (BN <= 128 && gp.k_stages >= 8 && gp.k_stages % 2 == 0)) ? 1 : 0;
+  gp.kmul = tune_kmul(KIND_F32, gp.a_tmem, gp.k_stages, BN);
+  if (gp.kmul == 2) wino_gemm_kernel<false, 2><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  else wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
   WinoOutParams op{};
   op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;
   op.out_type = OUT_F32; op.with_bias = d.with_bias; op.with_relu = d.with_relu; op.with_sum = d.with_ip_sum;
