@@ -148,6 +148,7 @@ struct elb_conv {
   // device workspace
   void *d_wpack = nullptr, *d_wplain = nullptr, *d_scale = nullptr, *d_shift = nullptr;
   void *d_shift_tbl = nullptr, *d_tap_cls = nullptr;     // int8 direct, zero point with padding: per-class shifts
+  void *d_tap_tbl = nullptr;                             // int8 direct, BOX mode: I8ConvParams::tap_tbl
   int *d_status = nullptr;
   int *h_status = nullptr;              // pinned: the status word travels back on the stream, behind the kernels
   std::string name = "ioi";             // eld_conv_t::name, printed in the euler-perf line
@@ -180,7 +181,7 @@ struct elb_conv {
 
   ~elb_conv() {
     cudaSetDevice(device);
-    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, d_shift_tbl, d_tap_cls, (void *)d_status, d_in_stage, d_out_stage,
+    for (void *p : {d_wpack, d_wplain, d_scale, d_shift, d_shift_tbl, d_tap_cls, d_tap_tbl, (void *)d_status, d_in_stage, d_out_stage,
                     d_cvt_in, d_cvt_out})
       if (p) cudaFree(p);
     wino_release(wino);
@@ -413,10 +414,34 @@ int setup_i8_direct(elb_conv &pl) {
     {
       const char *on2 = getenv("ELB_I8_CTA2");
       const bool zp_classes = d.input_z != 0.0f && (d.pad_t || d.pad_l || d.pad_b || d.pad_r);   // (single CTAs only)
-      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && on2 && atoi(on2) > 0 && !zp_classes) ? 1 : 0;
+      pl.i8cfg.cta2 = (mode == I8_MODE_BOX && p.m_tiles >= 4 && on2 && atoi(on2) > 0 && !zp_classes && pl.i8cfg.KC == 8) ? 1 : 0;
     }
     if (pl.i8cfg.cta2) CUDA_TRY(init_i8_umma2(pl.i8cfg, pl.num_sms));
     CUDA_TRY(init_i8_umma(pl.i8cfg));
+    // BOX mode: the copy table (where each tiled copy of each K stage reads)
+    p.tap_tbl = nullptr; p.tap_n = 0; p.ncopy = pl.i8cfg.KC / p.box_c;
+    if (mode == I8_MODE_BOX && !pl.i8cfg.cta2 && p.k_stages * p.ncopy <= I8_TAP_TBL_MAX && p.CB < 4096 &&
+        p.KH - p.pad_t <= 7 && p.KW - p.pad_l <= 7 && p.pad_t <= 8 && p.pad_l <= 8) {
+      std::vector<uint32_t> tbl(static_cast<size_t>(p.k_stages) * p.ncopy, 0u);
+      auto fdiv = [](int e, int s) { return e >= 0 ? e / s : -((-e + s - 1) / s); };
+      for (int ks = 0; ks < p.k_stages; ++ks)
+        for (int c = 0; c < p.ncopy; ++c) {
+          const int q = ks * pl.i8cfg.KC + c * p.box_c;
+          if (q >= p.Q) continue;
+          const int tap = q / p.CB, cb0 = q - tap * p.CB;
+          // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
+          const int kh = tap / p.KW, kw = tap - kh * p.KW;
+          const int eh = kh - p.pad_t, ew = kw - p.pad_l;
+          const int dh = fdiv(eh, p.stride), dw = fdiv(ew, p.stride);
+          const int map = (eh - dh * p.stride) * p.stride + (ew - dw * p.stride);
+          tbl[static_cast<size_t>(ks) * p.ncopy + c] = static_cast<uint32_t>(cb0) | static_cast<uint32_t>(dh + 8) << 12 |
+                                                      static_cast<uint32_t>(dw + 8) << 16 | static_cast<uint32_t>(map) << 20;
+        }
+      CUDA_TRY(cudaMalloc(&pl.d_tap_tbl, tbl.size() * 4));
+      CUDA_TRY(cudaMemcpy(pl.d_tap_tbl, tbl.data(), tbl.size() * 4, cudaMemcpyHostToDevice));
+      p.tap_tbl = static_cast<const uint32_t *>(pl.d_tap_tbl);
+      p.tap_n = static_cast<int>(tbl.size());
+    }
   }
   pl.info.launches_per_call = 1;
   return ELB_OK;

@@ -157,7 +157,13 @@ struct I8ConvParams {
   int spp;                           // BOX mode: pipeline stages a producer warp fills per pass (1 or 2)
   int nprod;                         // BOX mode: producer warps taking turns on the passes (1, 2 or 4)
   int rotate_k;                      // tiles start their K loop at different stages (spreads the weight reads over L2)
+  // BOX mode: where each tiled copy of a K stage reads, worked out once on the host instead of with four
+  // integer divisions per copy in the one-warp producer loop.  Entry [stage * ncopy + copy] =
+  // channel block | (row shift + 8) << 12 | (column shift + 8) << 16 | tensor map << 20; null: compute.
+  const uint32_t *tap_tbl;
+  int tap_n, ncopy;                  // entries in all; tiled copies per full stage (KC / box_c)
 };
+constexpr int I8_TAP_TBL_MAX = 1024;   // entries the kernels keep in shared memory
 
 enum : int { I8_MODE_FLAT = 0, I8_MODE_BOX = 1 };
 

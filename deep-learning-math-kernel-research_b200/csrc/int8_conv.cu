@@ -64,7 +64,8 @@ struct SmemLayout {
   static constexpr int BAR_OFF = RING_BYTES;                       // full[S], empty[S], tfull[2], tempty[2]
   static constexpr int MISC_OFF = BAR_OFF + (2 * STAGES + 4) * 8;  // tmem slot, abort flag
   static constexpr int CONST_OFF = (MISC_OFF + 16 + 15) / 16 * 16; // scale[MAX_OC_SMEM], shift[MAX_OC_SMEM]
-  static constexpr int TOTAL = CONST_OFF + 2 * MAX_OC_SMEM * 4 + 128;   // +128: manual alignment slack
+  static constexpr int TAP_OFF = CONST_OFF + 2 * MAX_OC_SMEM * 4;  // the copy table (I8ConvParams::tap_tbl)
+  static constexpr int TOTAL = TAP_OFF + I8_TAP_TBL_MAX * 4 + 128; // +128: manual alignment slack
 };
 
 // optional per-CTA timeline (SM cycle counter), 64 slots per CTA; used by the profiling notes
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFF + 4);
   float *s_scale = reinterpret_cast<float *>(smem + L::CONST_OFF);
   float *s_shift = s_scale + MAX_OC_SMEM;
+  uint32_t *s_tap = reinterpret_cast<uint32_t *>(smem + L::TAP_OFF);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,6 +121,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
       fence_proxy_async_smem();
     }
     __syncwarp();
+  }
+  if (MODE == I8_MODE_BOX && is_producer && p.tap_tbl) {
+    const int ptid = (warp == 0 ? 0 : warp - PRODUCER2_WARP + 1) * 32 + lane;
+    for (int i = ptid; i < p.tap_n; i += 32 * MAX_PRODUCERS) s_tap[i] = __ldg(p.tap_tbl + i);
   }
   if (is_producer || warp == 1) named_bar_sync(1, 32 * (MAX_PRODUCERS + 1));
   if (!is_producer) {
@@ -201,6 +207,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
         // Chunks past the end of K are not fetched: their weights are zero, whatever the slot holds.
         const int grp = lane >> 4, gl = lane & 15;
         const int spp = p.spp == 1 ? 1 : 2;          // stages per pass
+        // (KC = 16: the host picks box_c >= 2, so at most 8 lanes fetch pixels and lane 15 is free)
+        constexpr int B_LANE = KC < 16 ? KC : 15;
         for (int ki0 = 0; ki0 < p.k_stages; ki0 += spp, it += spp, ++gpass) {
           if ((gpass & (nprod - 1u)) != pw) continue;          // another producer warp's pass
           const int ki = ki0 + grp;
@@ -226,19 +234,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
             uint8_t *a_dst = smem + s * L::STAGE_BYTES;
             const int q0 = ks * KC;
             const int valid = min(KC, p.Q - q0);
-            if (gl == KC) {
+            if (gl == B_LANE) {
               tma_bulk_g2s(a_dst + L::A_BYTES, p.wpack + (static_cast<size_t>(nt) * p.k_stages + ks) * L::B_BYTES,
                            L::B_BYTES, &full[s]);
-            } else if (gl < KC && gl * p.box_c < valid) {
-              const int q = q0 + gl * p.box_c;
-              const int tap = q / p.CB, cb0 = q - tap * p.CB;
-              // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
-              const int kh = tap / p.KW, kw = tap - kh * p.KW;
-              const int eh = kh - p.pad_t, ew = kw - p.pad_l;
-              const int dh = (eh >= 0) ? eh / p.stride : -((-eh + p.stride - 1) / p.stride);
-              const int dw = (ew >= 0) ? ew / p.stride : -((-ew + p.stride - 1) / p.stride);
-              const int par_h = eh - dh * p.stride, par_w = ew - dw * p.stride;
-              const CUtensorMap *tm = &p.tmap[par_h * p.stride + par_w];
+            } else if (gl < B_LANE && gl * p.box_c < valid) {
+              int cb0, dh, dw, map;
+              if (p.tap_tbl) {
+                const uint32_t e = s_tap[ks * p.ncopy + gl];
+                cb0 = static_cast<int>(e & 0xFFFu);
+                dh = static_cast<int>((e >> 12) & 15u) - 8;
+                dw = static_cast<int>((e >> 16) & 15u) - 8;
+                map = static_cast<int>(e >> 20);
+              } else {
+                const int q = q0 + gl * p.box_c;
+                const int tap = q / p.CB;
+                cb0 = q - tap * p.CB;
+                // input row = stride*(oh + dh) + parity_h with dh = floor((kh - pad)/stride)
+                const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                const int eh = kh - p.pad_t, ew = kw - p.pad_l;
+                dh = (eh >= 0) ? eh / p.stride : -((-eh + p.stride - 1) / p.stride);
+                dw = (ew >= 0) ? ew / p.stride : -((-ew + p.stride - 1) / p.stride);
+                map = (eh - dh * p.stride) * p.stride + (ew - dw * p.stride);
+              }
+              const CUtensorMap *tm = &p.tmap[map];
               uint8_t *dst = a_dst + gl * p.box_c * (BM * 16);
               // stride 1: rows of the box are contiguous in memory, so the map describes them as runs of
               // 8-byte elements (2 per pixel) and the TMA unit moves whole rows instead of 16-byte items
@@ -499,9 +517,19 @@ I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
     const int v = tune_env("ELB_I8_BN", c.BN);
     if (v == 64 || v == 128 || v == 256) c.BN = v;
   }
+  // K chunks (of 16 channels) per stage.  Handing a stage from role to role costs the single-thread
+  // role loops about a thousand cycles whatever its size, and the MMAs of a stage of 8 chunks take
+  // less than that below 256 output channels: those tiles move 16 chunks per stage (BOX mode needs
+  // at most 15 copies per stage for that, i.e. an even number of channel blocks).
   c.KC = 8;
+  const bool kc16_ok = c.BN <= 128 && cb * taps >= 32 && (mode == I8_MODE_FLAT || cb % 2 == 0);
+  if (tune_env("ELB_I8_KC", kc16_ok ? 16 : 8) == 16 && kc16_ok) c.KC = 16;
+  if (c.KC == 16) {
+    c.STAGES = c.BN == 128 ? 3 : 4;
+    c.smem_bytes = c.BN == 128 ? SmemLayout<128, 16, 3>::TOTAL : SmemLayout<64, 16, 4>::TOTAL;
+    return c;
+  }
   c.STAGES = c.BN == 256 ? 4 : c.BN == 128 ? 6 : 8;     // as many as shared memory holds: the ring is latency-bound
-  (void)cb; (void)taps;
   c.smem_bytes = c.BN == 256 ? SmemLayout<256, 8, 4>::TOTAL
                : c.BN == 128 ? SmemLayout<128, 8, 6>::TOTAL : SmemLayout<64, 8, 8>::TOTAL;
   return c;
@@ -509,6 +537,14 @@ I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
 
 static cudaError_t dispatch_i8_umma(const I8ConvParams &p, const I8UmmaConfig &cfg, int num_sms, cudaStream_t s,
                                     bool attr_only) {
+  if (cfg.KC == 16) {
+    if (cfg.mode == I8_MODE_FLAT) {
+      if (cfg.BN == 128) return launch_cfg<128, 16, 3, I8_MODE_FLAT>(p, num_sms, s, attr_only);
+      return launch_cfg<64, 16, 4, I8_MODE_FLAT>(p, num_sms, s, attr_only);
+    }
+    if (cfg.BN == 128) return launch_cfg<128, 16, 3, I8_MODE_BOX>(p, num_sms, s, attr_only);
+    return launch_cfg<64, 16, 4, I8_MODE_BOX>(p, num_sms, s, attr_only);
+  }
   if (cfg.mode == I8_MODE_FLAT) {
     if (cfg.BN == 256) return launch_cfg<256, 8, 4, I8_MODE_FLAT>(p, num_sms, s, attr_only);
     if (cfg.BN == 128) return launch_cfg<128, 8, 6, I8_MODE_FLAT>(p, num_sms, s, attr_only);

@@ -76,7 +76,7 @@ constexpr int GEMM_THREADS = (GEMM_SPLIT_WARP0 + GEMM_CONV_GROUPS * GEMM_CONV_WA
 static_assert(GEMM_EPI_WARP0 % 4 == 0 && GEMM_EPI_WARPS % 4 == 0 && GEMM_CONV_WARPS == 4, "roles must fill whole warpgroups");
 // Registers per thread after the set-up: the epilogue warpgroups hold a whole 128 x 256 accumulator
 // (128 values per thread) so that tensor memory is released before the global stores; the other
-// warpgroups give theirs up.  (2 x 128 x 176 + 2 x 128 x 80 = the 64 K registers the launch owns.)
+// warpgroups give theirs up.  (2 x 128 x 184 + 2 x 128 x 72 = the 64 K registers the launch owns.)
 constexpr int GEMM_EPI_REGS = 184, GEMM_OTHER_REGS = 72;
 static_assert(GEMM_CONV_GROUPS == 1, "the register split assumes four warpgroups");
 constexpr size_t WORKSPACE_BUDGET = size_t(6) << 30;   // transform-domain buffers per chunk
@@ -539,7 +539,7 @@ struct WinoGemmParams {
 #define ABL(bit) false
 #endif
 #ifdef ELB_TUNING
-#define WG_TRACE2(slot) do { if (p.trace && (slot) < 64) p.trace[(gridDim.x + blockIdx.x) * 64 + (slot)] = clock64(); } while (0)
+#define WG_TRACE2(slot) do { if (tracing && (slot) < 64) p.trace[(gridDim.x + blockIdx.x) * 64 + (slot)] = clock64(); } while (0)
 #else
 #define WG_TRACE2(slot) do { } while (0)
 #endif
@@ -548,12 +548,19 @@ struct WinoGemmParams {
 #else
 #define TR0 0u
 #endif
-#define WG_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
+#define WG_TRACE(slot) do { if (tracing && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
 // KMUL: K stages per pipeline step (WinoGemmParams::kmul); a template argument because the role
 // loops are single threads bound by instruction latency -- as a run-time loop count the same code
 // measured 10-20 % slower at kmul = 1.
-template <bool CTA2, int KMUL = 1>
+// SPEC: 0 = every mode decided at run time from the parameters; 1 / 2 = fp32 with A in tensor memory
+// and stacked / plain weight rows, 3 = int8; none of them flat: the modes of the long launches,
+// compiled with their flags as constants (every instruction the one-thread role loops do not
+// execute is ~6 cycles; measured against the generic kernel on the same GPU: c1 GEMM 0.333 -> 0.265
+// ms, VGG conv1_2 0.45 -> 0.35 ms, conv4_2 0.19 -> 0.14 ms).
+// TBN: the tile's output channels as a constant (0 = p.BN): descriptors, ring geometry and the
+// epilogue's block loop then fold at compile time.
+template <bool CTA2, int KMUL = 1, int SPEC = 0, int TBN = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid_constant__ WinoGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -574,7 +581,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   float *epi_consts = reinterpret_cast<float *>(consts_area);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int BN = p.BN;
+  const int BN = TBN != 0 ? TBN : p.BN;
+  const int kind = SPEC == 3 ? static_cast<int>(KIND_I8) : SPEC != 0 ? static_cast<int>(KIND_F32) : p.kind;
+  const bool flat = SPEC != 0 ? false : p.flat != 0;
+  const bool tracing = SPEC != 0 ? false : p.trace != nullptr;      // (timelines are taken from the generic kernel)
   const uint32_t rank = CTA2 ? cluster_ctarank() : 0u;
   const bool leader = rank == 0;
   const int BNL = CTA2 ? BN / 2 : BN;                      // weight rows this CTA stages
@@ -587,10 +597,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // fp32 on single CTAs: ONE accumulator buffer (columns 0..255) and, behind it, a ring of A-operand
   // slots in tensor memory, one per shared-memory stage: 16 columns of tf32 hi + 16 of lo
   constexpr uint32_t A_TMEM_COL0 = MAX_BN;
-  const bool a_in_tmem = !CTA2 && p.kind == KIND_F32 && p.a_tmem != 0;
+  const bool a_in_tmem = SPEC == 3 ? false : SPEC != 0 ? true : (!CTA2 && kind == KIND_F32 && p.a_tmem != 0);
   // Stacked weights (see WinoGemmParams::stack): the accumulator is 2*BN columns wide, columns
   // [BN, 2*BN) collect hi*lo and are added to [0, BN) by the epilogue.
-  const bool stack = !CTA2 && p.kind == KIND_F32 && p.stack != 0;
+  const bool stack = SPEC == 1 ? true : SPEC != 0 ? false : (!CTA2 && kind == KIND_F32 && p.stack != 0);
   const int acc_width = stack ? 2 * BN : BN;
   // Accumulator buffers: two (the epilogue of a tile overlaps the next tile's MMAs) unless the A
   // slots in tensor memory leave room for one only: columns [0,256) hold the accumulators (two of at
@@ -612,7 +622,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
   // GEMM 0.367 -> 0.429 ms.  The kernel is bound by shared-memory bandwidth -- per stage 48 KB of B
   // reads by the MMAs, 40 KB of incoming copies and 8 KB of splitter reads against 128 B/clk -- and
   // the detour adds 256 KB of shared-memory traffic per tile.)
-  const int ring_bytes = GEMM_STAGES * STAGE_BYTES + (p.kind == KIND_F32 ? EPI_CONST_BYTES : 0);
+  const int ring_bytes = GEMM_STAGES * STAGE_BYTES + (kind == KIND_F32 ? EPI_CONST_BYTES : 0);
   const int nstages = CTA2 ? GEMM_STAGES : min(GEMM_MAX_STAGES / kmul, ring_bytes / stage_bytes);     // (8 A slots of 16 channels in tensor memory)
 
   if (threadIdx.x == 0) {
@@ -649,7 +659,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     // this loop about a thousand, all of it latency of a single warp -- so the warps take turns on
     // the stages: stage i belongs to producer i mod p.producers.
     const int pw = warp == 0 ? 0 : warp - 1;
-    const int np = p.producers;
+    const int np = SPEC != 0 ? GEMM_PRODUCERS_DEFAULT : p.producers;
     int turn = 0;               // whose stage the current one is
     // ring slot / phase of the current stage, kept as counters (an integer division costs this
     // one-warp loop more than the copy instructions it issues)
@@ -661,7 +671,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       if (++turn == np) turn = 0;
     };
     bool ok = pw < np;
-    if (p.flat) {
+    if (flat) {
       // flat mode: lanes 0..3 fetch the four 16-byte channel chunks of a stage (boxes of 4 floats x
       // 128 pixels, rows past the end of the plane arrive as zeros), lane 4 the weights
       if (lane == 0) tma_prefetch_desc(&p.tmap_a);
@@ -688,12 +698,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       }
     }
     // fp32: A arrives as plain fp32 (8 KB per stage) in the raw ring; int8: straight into the stage
-    const uint32_t a_gbytes = p.kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
+    const uint32_t a_gbytes = kind == KIND_F32 ? A_RAW_BYTES : A_STAGE_BYTES;
     const size_t b_pitch = static_cast<size_t>(CTA2 ? 2 : 1) * b_stage_bytes;
     // position a and index r within it of the current tile, carried along instead of divided out
     int a = first / tiles_per_a, r = first - a * tiles_per_a;
     uint32_t tcount = 0;
-    for (int tile = first; tile < total_tiles && ok && !p.flat; tile += step, ++tcount) {
+    for (int tile = first; tile < total_tiles && ok && !flat; tile += step, ++tcount) {
       int nt = 0, mu = r;
       while (mu >= m_units) { mu -= m_units; ++nt; }        // (one or two n tiles)
       const int mt = CTA2 ? 2 * mu + static_cast<int>(rank) : mu;
@@ -702,7 +712,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       // pairs: the weight image holds the two halves of every stage one after the other
       const uint8_t *b_src = p.b_img + (static_cast<size_t>(a) * p.n_tiles + nt) * p.k_stages * b_pitch +
                              (CTA2 ? rank * b_stage_bytes : 0);
-      const int rot = p.rotate_k ? tile % ksteps : 0;      // see the flat-mode loop above
+      const int rot = (SPEC == 0 && p.rotate_k) ? tile % ksteps : 0;      // see the flat-mode loop above
       if (pw == 0 && lane == 0 && tcount < 8) WG_TRACE(tcount);
       for (int ks = 0; ks < ksteps; ++ks, next_stage()) {
         if (turn != pw) continue;            // another producer warp's stage
@@ -740,13 +750,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
           const int s = static_cast<int>(it % static_cast<uint32_t>(nstages));
           const uint32_t ph = (it / static_cast<uint32_t>(nstages)) & 1u;
           if (!mbar_wait(&full[s], ph, abort_flag) ||
-              (p.kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag))) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
+              (kind == KIND_F32 && !mbar_wait(&cfull[s], ph, abort_flag))) { ok = false; fail_code = ST_WAIT_TIMEOUT_MMA; break; }
           mbar_arrive_cluster(mapa_u32(&pfull[s], 0));
         }
       }
     } else if (lane == 0) {
       const int MM = CTA2 ? 2 * BM : BM;
-      const uint32_t idesc = p.kind == KIND_F32 ? umma_idesc(1, 2, 2, MM, BN) : umma_idesc(2, 0, 1, MM, BN);
+      const uint32_t idesc = kind == KIND_F32 ? umma_idesc(1, 2, 2, MM, BN) : umma_idesc(2, 0, 1, MM, BN);
       const uint32_t b_lbo = 16u * BNL;
       uint32_t it = 0, tcount = 0;
       // This loop is ONE thread: every instruction in it costs its full latency (measured ~330 cycles
@@ -774,8 +784,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         // weights of the stage come with the same transaction count), so cfull alone orders this
         // thread behind both copies -- one barrier round trip less per stage.
         auto wait_stage = [&](int st, uint32_t phase) -> bool {
-          if ((CTA2 || p.kind != KIND_F32) && !mbar_wait(&full[st], phase, abort_flag)) return false;
-          if (p.kind == KIND_F32 && !mbar_wait(&cfull[st], phase, abort_flag)) return false;
+          if ((CTA2 || kind != KIND_F32) && !mbar_wait(&full[st], phase, abort_flag)) return false;
+          if (kind == KIND_F32 && !mbar_wait(&cfull[st], phase, abort_flag)) return false;
           if (CTA2 && !mbar_wait(&pfull[st], phase, abort_flag)) return false;
           tc_fence_after_sync();
           return true;
@@ -835,7 +845,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
             }
             }
             if (!ok) break;
-          } else if (p.kind == KIND_F32) {
+          } else if (kind == KIND_F32) {
             // planes: A hi at +0, lo at +8 KB; B hi at +0, lo at +4 chunks.  K step = 2 chunks.
 #pragma unroll
             for (int j = 0; j < kmul; ++j) {
@@ -894,7 +904,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
     reg_dealloc<GEMM_OTHER_REGS>();
     // -------- splitter (fp32 only): raw fp32 stage -> tf32 hi plane + residual lo plane, the
     // operands of the 3xTF32 product.  hi = round-to-nearest tf32(x), lo = x - hi (exact).
-    if (p.kind == KIND_F32) {
+    if (kind == KIND_F32) {
       const int cgrp = (warp - GEMM_SPLIT_WARP0) / GEMM_CONV_WARPS;       // this warp's group
       const int tid_c = ((warp - GEMM_SPLIT_WARP0) % GEMM_CONV_WARPS) * 32 + lane;
       uint32_t it = 0;
@@ -1002,7 +1012,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
       // piece of shared memory first (one 16-byte load per lane and array), so that the loop below
       // reads them with broadcast shared-memory loads instead of waiting on global memory
       float *w_sc = epi_consts + (warp - GEMM_EPI_WARP0) * 2 * MAX_BN, *w_sh = w_sc + MAX_BN;
-      if (p.kind == KIND_I8) {
+      if (kind == KIND_I8) {
         __syncwarp();
 #pragma unroll
         for (int c = lane * 4; c < MAX_BN; c += 128) {
@@ -1016,8 +1026,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         __syncwarp();
       }
       // flat mode: this thread's row is pixel flat_pix of image flat_n
-      const int flat_n = p.flat ? mt / p.tiles_img : 0;
-      const int flat_pix = p.flat ? (mt - flat_n * p.tiles_img) * BM + row : 0;
+      const int flat_n = flat ? mt / p.tiles_img : 0;
+      const int flat_pix = flat ? (mt - flat_n * p.tiles_img) * BM + row : 0;
       auto emit = [&](int k, uint32_t (&rr)[16], bool partner_added) {      // k-th 16-column block of this warp
         const int blk = half + 2 * k;
         const int ocb = nt * (BN / 16) + blk;
@@ -1029,7 +1039,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
 #pragma unroll
           for (int i = 0; i < 16; ++i) rr[i] = __float_as_uint(__fadd_rn(__uint_as_float(rr[i]), __uint_as_float(r2[i])));
         }
-        if (p.flat) {
+        if (flat) {
           if (flat_pix < p.HW && ocb < p.OCB) {
             float4 *o = reinterpret_cast<float4 *>(p.out + ((static_cast<size_t>(flat_n) * p.OCB + ocb) * p.HW + flat_pix) * 16);
 #pragma unroll
@@ -1055,7 +1065,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
         }
         if (live && ocb < p.OCB && !ABL(4)) {
           float f[16];
-          if (p.kind == KIND_F32) {
+          if (kind == KIND_F32) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(rr[i]);
           } else {
@@ -1068,7 +1078,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) wino_gemm_kernel(const __grid
               f[4 * i + 2] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[4 * i + 2])), c.z, h.z);
               f[4 * i + 3] = __fmaf_rn(__int2float_rn(static_cast<int>(rr[4 * i + 3])), c.w, h.w);
             }
-            if (p.acc_dump && t < p.T) {
+            if (SPEC == 0 && p.acc_dump && t < p.T) {
               int32_t *d = p.acc_dump + (static_cast<size_t>(a) * p.T + t) * OCP + ocb * 16;
 #pragma unroll
               for (int i = 0; i < 16; ++i) d[i] = static_cast<int>(rr[i]);
@@ -1170,6 +1180,48 @@ constexpr int GEMM_SMEM_BYTES_2 = GEMM_STAGES_2 * (A_STAGE_BYTES + B_STAGE_MAX /
 constexpr int GEMM_SMEM_BYTES = GEMM_SMEM_BYTES_1 > GEMM_SMEM_BYTES_2 ? GEMM_SMEM_BYTES_1 : GEMM_SMEM_BYTES_2;
 static_assert(GEMM_SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 static_assert(GEMM_EPI_WARPS * 2 * MAX_BN * 4 <= EPI_CONST_BYTES, "epilogue constants must fit their area");
+
+// The single-CTA instantiations of the GEMM kernel: the generic one, the two K stages per step one,
+// and the ones specialised for fp32 with A in tensor memory (see SPEC).
+inline cudaError_t gemm_set_attributes() {
+  cudaError_t e = cudaSuccess;
+  auto set = [&](const void *f) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  };
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 1, 0>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 1, 1>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 1, 2>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 2, 0>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 2, 1>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 2, 1, 64>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 2, 1, 128>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 1, 2, 256>));
+  set(reinterpret_cast<const void *>(wino_gemm_kernel<false, 1, 3, 256>));
+  return e;
+}
+inline void gemm_launch(const WinoGemmParams &gp, int ctas, cudaStream_t s) {
+  // specialised kernels: fp32, A in tensor memory, not flat, no timeline requested
+  const bool plain = !gp.flat && !gp.trace && !gp.ablate && !gp.rotate_k && gp.producers == GEMM_PRODUCERS_DEFAULT;
+  if (plain && gp.kind == KIND_I8 && gp.BN == 256 && !gp.acc_dump) {
+    wino_gemm_kernel<false, 1, 3, 256><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    return;
+  }
+  const int spec = (plain && gp.kind == KIND_F32 && gp.a_tmem) ? (gp.stack ? 1 : 2) : 0;
+  if (gp.kmul == 2) {
+    if (spec == 1 && gp.BN == 64) wino_gemm_kernel<false, 2, 1, 64><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    else if (spec == 1 && gp.BN == 128) wino_gemm_kernel<false, 2, 1, 128><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    else if (spec == 1) wino_gemm_kernel<false, 2, 1><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    else wino_gemm_kernel<false, 2, 0><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  } else if (spec == 1) {
+    wino_gemm_kernel<false, 1, 1><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  } else if (spec == 2 && gp.BN == 256) {
+    wino_gemm_kernel<false, 1, 2, 256><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  } else if (spec == 2) {
+    wino_gemm_kernel<false, 1, 2><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  } else {
+    wino_gemm_kernel<false, 1, 0><<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  }
+}
 
 // ------------------------------------------------------------------------------ output transform
 struct WinoOutParams {
@@ -1494,21 +1546,16 @@ std::vector<float> transform_weights(const float *w, int oc, int ic, int OCP, in
 }
 
 // Tuning switches of the GEMM kernel (tune_env: overridable only in -DELB_TUNING builds).
-// fp32: A in tensor memory costs the second accumulator buffer (the epilogue no longer overlaps the
-// next tile's MMAs) but relieves the shared-memory port and deepens the ring.  Measured on B200,
-// per layer of the VGG-16 stack (32 images): it loses where the K loop is short and the epilogue
-// therefore weighs most (64 / 128 input channels: 1.29 -> 1.52 ms, 0.42 -> 0.49 ms), is even at 128
-// channels x 8 stages, and wins from 256 input channels up (conv4_2 0.308 -> 0.283 ms, conv5_x
-// 0.108 -> 0.097 ms) and whenever a CTA runs a single tile (1x1 benchmark layer 68.9 -> 55.9 us).
-// With stacked weights of at most 64 output channels the accumulator is 128 columns wide, two of
-// them fit beside the A slots, and A in tensor memory costs nothing: always on there.
-// Since the epilogue of a one-accumulator tile releases tensor memory before it stores (and steps of
-// two K stages need A in tensor memory, see tune_kmul), tiles of at most 128 output channels take
-// it from 8 K stages up: VGG conv2_2 (128 -> 128 channels) GEMM 0.306 -> 0.256 ms with steps of
-// two stages, even at 4 stages (conv2_1 0.180 vs 0.182 ms).
-inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms, int acc_width = 256, int BN = 256) {
-  const int dflt = kind == KIND_F32 && (k_stages >= 16 || total_tiles <= num_sms || acc_width <= 128 ||
-                                        (BN <= 128 && k_stages >= 8 && k_stages % 2 == 0)) ? 1 : 0;
+// fp32: A in tensor memory relieves the shared-memory port and deepens the ring; with an accumulator
+// wider than 128 columns it leaves room for one accumulator buffer only, whose epilogue therefore
+// hands tensor memory back before it stores (see the kernel).  The Winograd / direct GEMMs (not flat)
+// always use it: they then run the kernels specialised for it, which beat the generic kernel with A
+// in shared memory on every layer of the VGG-16 stack (same GPU, 32 images: conv2_1 GEMM 0.176 ->
+// 0.126 ms, conv3_1 0.116 -> 0.087 ms; the layers from 256 input channels up had it before).  The
+// flat 1x1 kernel keeps the rule it was measured with: long K loops, or a CTA that runs a single tile
+// (1x1 benchmark layer 68.9 -> 55.9 us), or accumulators of at most 128 columns.
+inline int tune_a_tmem(int kind, int k_stages, long long total_tiles, int num_sms, int acc_width, bool flat) {
+  const int dflt = kind != KIND_F32 ? 0 : !flat ? 1 : (k_stages >= 16 || total_tiles <= num_sms || acc_width <= 128) ? 1 : 0;
   return tune_env("ELB_F32_A_TMEM", dflt) > 0 ? 1 : 0;
 }
 // K rotation spreads the weight reads of CTAs running side by side over L2; measured without effect
@@ -1626,9 +1673,7 @@ int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, st
     volatile float rep = 1.0f / d.tinput_scale;
     w->mrepS = d.input_scale * rep;                                      // src/elx_conv_wino_trans_input.cpp:617
   }
-  cudaError_t e = cudaFuncSetAttribute(wino_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(wino_gemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  cudaError_t e = gemm_set_attributes();
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(wino_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return ELB_GENERAL_ERROR; }
@@ -1843,7 +1888,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.rotate_k = tune_rotate_k();
     gp.stack = w->stack ? 1 : 0;
     gp.a_tmem = tune_a_tmem(KIND_F32, gp.k_stages, static_cast<long long>(gp.m_tiles) * gp.n_tiles, num_sms,
-                            w->stack ? 2 * w->BN : w->BN);
+                            w->stack ? 2 * w->BN : w->BN, true);
     gp.kmul = 1;
     gp.bias = static_cast<const float *>(w->d_bias);
     gp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
@@ -1852,7 +1897,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     const bool timed = pl.stage_ev[0] != nullptr;
     if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[0], s)); W_TRY(cudaEventRecord(pl.stage_ev[1], s)); }
     const int total = gp.m_tiles * gp.n_tiles;
-    wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+    gemm_launch(gp, total < num_sms ? total : num_sms, s);
     W_TRY(cudaGetLastError());
     if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[2], s)); W_TRY(cudaEventRecord(pl.stage_ev[3], s)); }
     launches = 1;
@@ -1914,7 +1959,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     gp.ablate = tune_env("ELB_ABL", 0);
     gp.stack = w->stack ? 1 : 0;
     gp.a_tmem = tune_a_tmem(w->kind, gp.k_stages, static_cast<long long>(gp.positions) * gp.m_tiles * gp.n_tiles, num_sms,
-                            w->stack ? 2 * w->BN : w->BN, w->BN);
+                            w->stack ? 2 * w->BN : w->BN, false);
     gp.kmul = tune_kmul(w->kind, gp.a_tmem, gp.k_stages, w->BN);
     if (w->cta2) {
       const int pairs = gp.positions * ((gp.m_tiles + 1) / 2) * gp.n_tiles;
@@ -1931,8 +1976,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
       W_TRY(cudaLaunchKernelEx(&cfg, wino_gemm_kernel<true>, gp));
     } else {
       const int total = gp.positions * gp.m_tiles * gp.n_tiles;
-      if (gp.kmul == 2) wino_gemm_kernel<false, 2><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
-      else wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+      gemm_launch(gp, total < num_sms ? total : num_sms, s);
       W_TRY(cudaGetLastError());
     }
     if (timed) W_TRY(cudaEventRecord(pl.stage_ev[2], s));
@@ -2099,9 +2143,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
     void *p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(wino_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(wino_gemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    e = gemm_set_attributes();
     if (e != cudaSuccess) return fail(ELB_GENERAL_ERROR, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
   }
@@ -2159,11 +2201,9 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
   gp.producers = GEMM_PRODUCERS_DEFAULT;
   const int total = 36 * gp.m_tiles * gp.n_tiles;
   gp.stack = stack;
-  gp.a_tmem = (gp.k_stages >= 16 || total <= num_sms || (stack ? 2 * BN : BN) <= 128 ||
-               (BN <= 128 && gp.k_stages >= 8 && gp.k_stages % 2 == 0)) ? 1 : 0;
+  gp.a_tmem = 1;
   gp.kmul = tune_kmul(KIND_F32, gp.a_tmem, gp.k_stages, BN);
-  if (gp.kmul == 2) wino_gemm_kernel<false, 2><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
-  else wino_gemm_kernel<false><<<total < num_sms ? total : num_sms, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(gp);
+  gemm_launch(gp, total < num_sms ? total : num_sms, s);
   WinoOutParams op{};
   op.m_in = m_buf; op.bias = static_cast<const float *>(bias); op.out = output; op.g = g;
   op.out_type = OUT_F32; op.with_bias = d.with_bias; op.with_relu = d.with_relu; op.with_sum = d.with_ip_sum;
