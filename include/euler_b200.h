@@ -176,7 +176,10 @@ ELB_API int elb_conv_device_status(elb_conv_t *plan);
 ELB_API int elb_conv_set_stage_events(elb_conv_t *plan, void **cuda_events4);
 
 /* Debug hook, no counterpart in the reference: per-CTA timeline of the tcgen05 kernels (SM cycle
- * counter), 64 int64 slots per CTA in caller DEVICE memory; NULL switches it off. */
+ * counter), 64 int64 slots per CTA in caller DEVICE memory; NULL switches it off.  While it is on,
+ * the Winograd / fp32 GEMM runs its generic kernel instead of the one compiled for its mode (the
+ * stamps would slow the specialised role loops down for everybody), so timings taken with a
+ * timeline are not the timings of a normal call. */
 ELB_API int elb_conv_set_trace(elb_conv_t *plan, void *device_int64);
 
 /* Self test of the bounded waits, no counterpart in the reference: a one-CTA kernel waits on a
