@@ -69,11 +69,18 @@ struct SmemLayout {
 };
 
 // optional per-CTA timeline (SM cycle counter), 64 slots per CTA; used by the profiling notes
-#define ELB_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
+#define ELB_TRACE(slot) do { if (tracing && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
-template <int BN, int KC, int STAGES, int MODE>
+// SPEC: 0 = everything decided at run time; 1 / 2 = BOX mode with the copy table, every K stage
+// full (K a multiple of the stage), no timeline, rows of a box merged (stride 1) / not merged: the
+// long launches, compiled with those flags as constants.  The producer and issuer loops are single
+// warps / threads whose every instruction and branch costs its latency.
+template <int BN, int KC, int STAGES, int MODE, int SPEC = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_constant__ I8ConvParams p) {
   using L = SmemLayout<BN, KC, STAGES>;
+  const bool tracing = SPEC != 0 ? false : p.trace != nullptr;
+  const bool merged_rows = SPEC == 1 ? true : SPEC == 2 ? false : p.merged_rows != 0;
+  const bool use_tbl = SPEC != 0 ? true : p.tap_tbl != nullptr;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
@@ -122,7 +129,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
     }
     __syncwarp();
   }
-  if (MODE == I8_MODE_BOX && is_producer && p.tap_tbl) {
+  if (MODE == I8_MODE_BOX && is_producer && use_tbl) {
     const int ptid = (warp == 0 ? 0 : warp - PRODUCER2_WARP + 1) * 32 + lane;
     for (int i = ptid; i < p.tap_n; i += 32 * MAX_PRODUCERS) s_tap[i] = __ldg(p.tap_tbl + i);
   }
@@ -239,7 +246,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
                            L::B_BYTES, &full[s]);
             } else if (gl < B_LANE && gl * p.box_c < valid) {
               int cb0, dh, dw, map;
-              if (p.tap_tbl) {
+              if (use_tbl) {
                 const uint32_t e = s_tap[ks * p.ncopy + gl];
                 cb0 = static_cast<int>(e & 0xFFFu);
                 dh = static_cast<int>((e >> 12) & 15u) - 8;
@@ -260,7 +267,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
               uint8_t *dst = a_dst + gl * p.box_c * (BM * 16);
               // stride 1: rows of the box are contiguous in memory, so the map describes them as runs of
               // 8-byte elements (2 per pixel) and the TMA unit moves whole rows instead of 16-byte items
-              if (p.merged_rows) tma_tile_4d(dst, tm, (ow0 + dw) * 2, oh0 + dh, cb0, n0, &full[s]);
+              if (merged_rows) tma_tile_4d(dst, tm, (ow0 + dw) * 2, oh0 + dh, cb0, n0, &full[s]);
               else tma_tile_5d(dst, tm, 0, ow0 + dw, oh0 + dh, cb0, n0, &full[s]);
             }
           }
@@ -303,10 +310,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
           const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
           const uint64_t ad0 = A_DESC_HI | (a_addr >> 4), bd0 = B_DESC_HI | ((a_addr + L::A_BYTES) >> 4);
           // K = 32 bytes = two chunks per instruction; the last stage may hold fewer than KC chunks
-          const int pairs = (min(KC, p.Q - ks * KC) + 1) >> 1;
+          const int pairs = SPEC != 0 ? KC / 2 : (min(KC, p.Q - ks * KC) + 1) >> 1;
 #pragma unroll
           for (int k2 = 0; k2 < KC / 2; ++k2) {
-            if (k2 < pairs)
+            if (SPEC != 0 || k2 < pairs)
               umma_i8(d_tmem, ad0 + ((k2 * 2 * (BM * 16)) >> 4), bd0 + ((k2 * 2 * (BN * 16)) >> 4), IDESC, (ki | k2) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
@@ -489,15 +496,27 @@ template <int BN, int KC, int STAGES, int MODE>
 cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool attr_only) {
   using L = SmemLayout<BN, KC, STAGES>;
   auto kern = i8_umma_kernel<BN, KC, STAGES, MODE>;
-  if (attr_only)   // once per plan and device, outside any stream capture
-    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  if (attr_only) {   // once per plan and device, outside any stream capture
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (MODE == I8_MODE_BOX) {
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(i8_umma_kernel<BN, KC, STAGES, MODE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(i8_umma_kernel<BN, KC, STAGES, MODE, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    }
+    return e;
+  }
   const int tiles = p.m_tiles * p.n_tiles;
   int grid = tiles < num_sms ? tiles : num_sms;
   {
     const int v = tune_env("ELB_MAX_CTAS", grid);
     if (v > 0 && v < grid) grid = v;
   }
-  kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
+  // the kernels compiled for the plain case (see SPEC)
+  const bool plain = MODE == I8_MODE_BOX && p.tap_tbl && !p.trace && p.Q % KC == 0;
+  if (MODE == I8_MODE_BOX && plain && p.merged_rows) i8_umma_kernel<BN, KC, STAGES, MODE, 1><<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
+  else if (MODE == I8_MODE_BOX && plain) i8_umma_kernel<BN, KC, STAGES, MODE, 2><<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
+  else kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
   return cudaGetLastError();
 }
 
