@@ -71,10 +71,12 @@ struct SmemLayout {
 // optional per-CTA timeline (SM cycle counter), 64 slots per CTA; used by the profiling notes
 #define ELB_TRACE(slot) do { if (tracing && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
 
-// SPEC: 0 = everything decided at run time; 1 / 2 = BOX mode with the copy table, every K stage
-// full (K a multiple of the stage), no timeline, rows of a box merged (stride 1) / not merged: the
-// long launches, compiled with those flags as constants.  The producer and issuer loops are single
-// warps / threads whose every instruction and branch costs its latency.
+// SPEC: 0 = everything decided at run time; 1 / 2 = BOX mode with the copy table, no timeline, rows
+// of a box merged (stride 1) / not merged: the long launches, compiled with those flags as
+// constants.  The producer and issuer loops are single warps / threads whose every instruction and
+// branch costs its latency.  These kernels also issue ALL the MMAs of a last, partly filled K stage:
+// the packed weights of the chunks past the end of K are zero, so whatever bytes the unfetched part
+// of the slot holds contribute nothing, and the issuer loop needs no per-MMA guard.
 template <int BN, int KC, int STAGES, int MODE, int SPEC = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_constant__ I8ConvParams p) {
   using L = SmemLayout<BN, KC, STAGES>;
@@ -513,7 +515,7 @@ cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool 
     if (v > 0 && v < grid) grid = v;
   }
   // the kernels compiled for the plain case (see SPEC)
-  const bool plain = MODE == I8_MODE_BOX && p.tap_tbl && !p.trace && p.Q % KC == 0;
+  const bool plain = MODE == I8_MODE_BOX && p.tap_tbl && !p.trace;
   if (MODE == I8_MODE_BOX && plain && p.merged_rows) i8_umma_kernel<BN, KC, STAGES, MODE, 1><<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
   else if (MODE == I8_MODE_BOX && plain) i8_umma_kernel<BN, KC, STAGES, MODE, 2><<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
   else kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
