@@ -76,6 +76,8 @@ def _load():
         "elb_conv_info": (i32, [vp, C.POINTER(ElbConvInfo)]),
         "elb_conv_execute": (i32, [vp, vp, vp, vp, vp]),
         "elb_conv_enqueue": (i32, [vp, vp, vp, vp, vp, vp]),
+        "elb_conv_input_step_supported": (i32, [vp]),
+        "elb_conv_enqueue_strided": (i32, [vp, vp, vp, i32, i32, i32, vp]),
         "elb_conv_prepare": (i32, [vp, vp, vp]),
         "elb_conv_set_accumulator_dump": (i32, [vp, vp]),
         "elb_conv_device_status": (i32, [vp]),
@@ -125,7 +127,8 @@ EXPORTED_SYMBOLS = ["elb_conv_sizes", "elb_conv_create", "elb_conv_info", "elb_c
                     "elb_selftest_bounded_wait", "elb_stack_create", "elb_stack_prepare", "elb_stack_enqueue",
                     "elb_stack_execute", "elb_stack_layer", "elb_stack_sizes", "elb_stack_launch_count",
                     "elb_stack_layer_output", "elb_stack_set_layer_events", "elb_stack_destroy", "elb_conv_multi_create", "elb_conv_multi_execute", "elb_conv_multi_parts",
-                    "elb_conv_multi_destroy", "elb_wino_f32_conv_noalloc", "elb_wino_f32_noalloc_status"]
+                    "elb_conv_multi_destroy", "elb_wino_f32_conv_noalloc", "elb_wino_f32_noalloc_status",
+                    "elb_conv_input_step_supported", "elb_conv_enqueue_strided"]
 
 
 def last_error() -> str:
@@ -233,6 +236,14 @@ class eld_conv_t:
     def enqueue(self, output, input, weights=None, bias=None, stream=None) -> int:
         """Device pointers only; returns after the kernels are enqueued on ``stream``."""
         return lib.elb_conv_enqueue(self.xc, _ptr(output), _ptr(input), _ptr(weights), _ptr(bias), stream)
+
+    def input_step_supported(self) -> bool:
+        return bool(lib.elb_conv_input_step_supported(self.xc))
+
+    def enqueue_strided(self, output, input, src_h: int, src_w: int, step: int, stream=None) -> int:
+        """As enqueue on a prepared plan, but ``input`` holds src_h x src_w pixels per plane of which every
+        ``step``-th row and column is read (a subsample folded into the kernel's loads)."""
+        return lib.elb_conv_enqueue_strided(self.xc, _ptr(output), _ptr(input), src_h, src_w, step, stream)
 
     def set_accumulator_dump(self, dev_int32) -> int:
         return lib.elb_conv_set_accumulator_dump(self.xc, _ptr(dev_int32))

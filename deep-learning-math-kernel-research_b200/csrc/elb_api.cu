@@ -1030,6 +1030,29 @@ int elb_conv_enqueue(elb_conv_t *plan, void *output, const void *input, const vo
   return do_enqueue(*plan, output, input, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int elb_conv_input_step_supported(elb_conv_t *plan) {
+  if (!plan) return 0;
+  const int k = plan->info.kernel;
+  return (k == ELB_KERNEL_WINO_F32_UMMA && !plan->cvt_in && wino_input_step_supported(plan->wino)) ? 1 : 0;
+}
+
+int elb_conv_enqueue_strided(elb_conv_t *plan, void *output, const void *input, int src_h, int src_w, int step,
+                             void *cuda_stream) {
+  if (!plan || !output || !input) return fail(ELB_GENERAL_ERROR, "null argument");
+  if (step < 1 || src_h < 1 || src_w < 1 || (src_h + step - 1) / step != plan->d.ih || (src_w + step - 1) / step != plan->d.iw)
+    return fail(ELB_GENERAL_ERROR, "strided input: %d x %d read with step %d is not the %d x %d input of this plan", src_h,
+                src_w, step, plan->d.ih, plan->d.iw);
+  if (step == 1) return elb_conv_enqueue(plan, output, input, nullptr, nullptr, cuda_stream);
+  DeviceGuard guard(plan->device);
+  int rc = do_prepare(*plan, nullptr, nullptr);
+  if (rc != ELB_OK) return rc;
+  if (!elb_conv_input_step_supported(plan)) return fail(ELB_UNIMPLEMENTED, "this plan's kernel cannot read its input with a step");
+  plan->wino.in_step = step; plan->wino.src_h = src_h; plan->wino.src_w = src_w;
+  rc = do_enqueue(*plan, output, input, static_cast<cudaStream_t>(cuda_stream));
+  plan->wino.in_step = 1;
+  return rc;
+}
+
 int elb_conv_execute(elb_conv_t *plan, void *output, const void *input, const void *weights, const void *bias) {
   if (!plan || !output || !input) return fail(ELB_GENERAL_ERROR, "null argument");
   return execute_common(*plan, output, input, weights, bias, true);

@@ -76,6 +76,7 @@ struct elb_stack {
     elb_conv_desc_t d{};
     elb_conv_info_t info{};
     int step = 1;               // subsample behind this layer (1 = none)
+    bool fused = false;         // ... which the NEXT layer folds into its input loads (no kernel, no d_sub)
     void *d_out = nullptr;      // this layer's output (null for the last layer without a subsample: the caller's tensor)
     void *d_sub = nullptr;      // the subsampled tensor (null when step == 1, or when it is the caller's tensor)
     bool prepared = false;
@@ -123,10 +124,12 @@ int stack_enqueue(elb_stack &st, void *output, const void *input, cudaStream_t s
     const bool last = k + 1 == L;
     void *y = (last && l.step == 1) ? output : l.d_out;
     if (!st.layer_ev.empty() && cudaEventRecord(st.layer_ev[k], s) != cudaSuccess) return mfail(ELB_GENERAL_ERROR, "event record failed");
-    int rc = elb_conv_enqueue(l.plan, y, x, nullptr, nullptr, s);
+    int rc = (k > 0 && st.layers[k - 1].fused)
+                 ? elb_conv_enqueue_strided(l.plan, y, x, st.layers[k - 1].d.oh, st.layers[k - 1].d.ow, st.layers[k - 1].step, s)
+                 : elb_conv_enqueue(l.plan, y, x, nullptr, nullptr, s);
     if (rc != ELB_OK) return rc;
     x = y;
-    if (l.step > 1) {
+    if (l.step > 1 && !l.fused) {
       void *z = last ? output : l.d_sub;
       rc = elb_subsample_nChw16c(z, y, l.d.n, l.d.oc, l.d.oh, l.d.ow, l.step, l.step, (int)elem_bytes(l.d.dt_output), s);
       if (rc != ELB_OK) return rc;
@@ -194,8 +197,10 @@ int elb_stack_create(const elb_conv_desc_t *descs, const int32_t *subsample_afte
     const size_t sh = (l.d.oh + l.step - 1) / l.step, sw = (l.d.ow + l.step - 1) / l.step;
     const size_t sub_bytes = (size_t)l.d.n * ocp * sh * sw * eb;
     cudaError_t e = cudaSuccess;
+    // a subsample in front of a layer that can read its input with a step costs nothing
+    l.fused = l.step > 1 && !last && elb_conv_input_step_supported(st->layers[k + 1].plan) != 0;
     if (!last || l.step > 1) e = cudaMalloc(&l.d_out, l.info.bytes_output);
-    if (e == cudaSuccess && l.step > 1 && !last) e = cudaMalloc(&l.d_sub, sub_bytes);
+    if (e == cudaSuccess && l.step > 1 && !last && !l.fused) e = cudaMalloc(&l.d_sub, sub_bytes);
     if (e != cudaSuccess) { delete st; return mfail(ELB_GENERAL_ERROR, "device allocation failed: %s", cudaGetErrorString(e)); }
     if (last) st->out_bytes = l.step > 1 ? sub_bytes : l.info.bytes_output;
   }

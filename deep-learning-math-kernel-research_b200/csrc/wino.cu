@@ -134,6 +134,7 @@ struct WinoInParams {
   void *a_img;         // operand image
   WinoGeom g;
   float mrepS, tz;     // int8: u8 = sat(rne(fma(V, mrepS, tz)))
+  int step, SH, SW;    // fp32 F(4x4,3x3): the input is a plane of SH x SW pixels read with this step (1: SH = IH, SW = IW)
 };
 
 template <bool IN_U8>
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
       for (int w = 0; w < 6; ++w) {
         const int ih = ih0 + h, iw = iw0 + w;
         const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
-        const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
+        const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * p.SH + (ok ? ih * p.step : 0)) * p.SW + (ok ? iw * p.step : 0);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (ok) v = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16) + quad);
         m[h][w][0] = v.x; m[h][w][1] = v.y; m[h][w][2] = v.z; m[h][w][3] = v.w;
@@ -1842,6 +1843,8 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     return ELB_GENERAL_ERROR;
   }
   if (first < 0 || count <= 0 || first + count > w->N) { err = "image range outside the batch"; return ELB_GENERAL_ERROR; }
+  const bool stepped = pl.in_step > 1;
+  if (stepped && !wino_input_step_supported(pl)) { err = "this kernel cannot read its input with a step"; return ELB_UNIMPLEMENTED; }
   if (w->small_ic) {
     const WinoGeom &g = w->g;
     SmallIcParams sp{};
@@ -1914,9 +1917,10 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     g.m_tiles = w->g.m_tiles;             // operand image pitch
     // 1. input transform (covers every row of the m-tiles that will be multiplied)
     WinoInParams ip{};
-    ip.in = static_cast<const uint8_t *>(in) + static_cast<size_t>(n0) * w->in_img_bytes;
+    ip.in = static_cast<const uint8_t *>(in) + static_cast<size_t>(n0) * (stepped ? static_cast<size_t>(g.CB) * pl.src_h * pl.src_w * 64 : w->in_img_bytes);
     ip.a_img = w->d_a;
     ip.g = g;
+    ip.step = stepped ? pl.in_step : 1; ip.SH = stepped ? pl.src_h : g.IH; ip.SW = stepped ? pl.src_w : g.IW;
     ip.g.Tpad = m_tiles_run * BM;
     ip.mrepS = w->mrepS; ip.tz = w->tz;
     dim3 gi((m_tiles_run * BM + TRANS_TILES - 1) / TRANS_TILES, g.CB);
@@ -1999,6 +2003,11 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     launches += 3;
   }
   return ELB_OK;
+}
+
+bool wino_input_step_supported(const WinoPlan &pl) {
+  const WinoImpl *w = pl.impl;
+  return w && w->kind == KIND_F32 && !w->small_ic && !w->flat && !w->direct && w->g.A == 6;
 }
 
 void wino_release(WinoPlan &pl) {
@@ -2191,6 +2200,7 @@ extern "C" ELB_API int elb_wino_f32_conv_noalloc(const elb_conv_desc_t *desc, vo
                                                                          d.ic, OCP, ICP, BN, n_tiles, stack);
   WinoInParams ip{};
   ip.in = input; ip.a_img = a_img; ip.g = g;
+  ip.step = 1; ip.SH = g.IH; ip.SW = g.IW;
   wino_input_kernel<false><<<dim3((g.Tpad + TRANS_TILES - 1) / TRANS_TILES, g.CB), TRANS_THREADS, 0, s>>>(ip);
   WinoGemmParams gp{};
   gp.a_img = a_img; gp.b_img = reinterpret_cast<const uint8_t *>(b_img); gp.m_out = m_buf;

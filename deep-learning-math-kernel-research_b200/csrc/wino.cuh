@@ -11,7 +11,12 @@ struct WinoPlan {
   WinoImpl *impl = nullptr;
   void *trace = nullptr;     // optional debug timeline of the GEMM kernel (64 int64 slots per CTA)
   cudaEvent_t stage_ev[4] = {nullptr, nullptr, nullptr, nullptr};   // optional: recorded before / between / after the three kernels
+  // next call only: the input tensor is a plane of src_h x src_w pixels of which the convolution reads
+  // every in_step-th row and column (a subsample folded into the input transform); 1 = plain
+  int in_step = 1, src_h = 0, src_w = 0;
 };
+// Can this plan read its input with a step (fp32 Winograd F(4x4,3x3) through the transform kernels)?
+bool wino_input_step_supported(const WinoPlan &pl);
 
 // Build the launch geometry for pl from the descriptor (no device work).
 int wino_setup(WinoPlan &pl, const elb_conv_desc_t &d, elb_conv_info_t &info, std::string &err);

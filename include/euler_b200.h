@@ -165,6 +165,17 @@ ELB_API int elb_conv_prepare(elb_conv_t *plan, const void *weights, const void *
  * off.  The reference keeps the same values in its `toutput` scratch (src/kernel/elk_u8s8_gemm.hxx:146-166). */
 ELB_API int elb_conv_set_accumulator_dump(elb_conv_t *plan, void *device_int32);
 
+/* No counterpart in the reference (its harness feeds a layer's output to the next call,
+ * tests/elt_conv.cpp:399-410, and networks subsample between stages): enqueue as elb_conv_enqueue
+ * on an already prepared plan, but `input` is a device tensor of src_h x src_w pixels per plane of
+ * which the convolution reads every step-th row and column (ceil(src_h / step) == ih, same for w) --
+ * a subsample folded into the kernel's own loads instead of a kernel and a tensor of its own.
+ * elb_conv_input_step_supported() says whether the plan's kernel can do it (fp32 Winograd
+ * F(4x4,3x3) today); otherwise ELB_UNIMPLEMENTED, and elb_subsample_nChw16c does the job. */
+ELB_API int elb_conv_input_step_supported(elb_conv_t *plan);
+ELB_API int elb_conv_enqueue_strided(elb_conv_t *plan, void *output, const void *input, int src_h, int src_w, int step,
+                                     void *cuda_stream);
+
 /* Device-side status word of the last launch: 0 = ok, otherwise the code of the bounded wait that
  * gave up (see csrc/elb_common.cuh).  Also returned as ELB_GENERAL_ERROR by execute. */
 ELB_API int elb_conv_device_status(elb_conv_t *plan);

@@ -131,3 +131,53 @@ def test_int8_winograd_matches_oracle(pkg, case):
                 assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
     finally:
         d.close()
+
+
+@pytest.mark.parametrize("src_hw,step", [((28, 28), 2), ((13, 15), 2), ((24, 24), 3)])
+def test_fp32_winograd_reads_its_input_with_a_step(pkg, src_hw, step):
+    """elb_conv_enqueue_strided: the convolution of every step-th row and column of a larger plane is
+    bit-identical to subsampling first (elb_subsample_nChw16c) and convolving the small tensor."""
+    import torch
+    import gpuutil as G
+    E = G.package()
+    sh, sw = src_hw
+    ih, iw = (sh + step - 1) // step, (sw + step - 1) // step
+    case = _f32(f"wino_step{step}_{sh}x{sw}", 2, 32, 48, ih, iw)
+    t = R.make_tensors(case)
+    d = G.make_desc(case)
+    assert d.setup() == E.ELD_OK, E.last_error()
+    try:
+        assert d.kernel == "wino_f32_umma" and d.input_step_supported()
+        rng = np.random.default_rng(R.seed_for(case.name, "big"))
+        big = torch.from_numpy(rng.standard_normal((case.n, 2, sh, sw, 16)).astype(np.float32)).cuda()
+        small = torch.empty((case.n, 2, ih, iw, 16), dtype=torch.float32, device="cuda")
+        assert E.subsample(small, big, case.n, 32, sh, sw, step, step) == E.ELD_OK
+        torch.cuda.synchronize()
+        assert torch.equal(small, big[:, :, ::step, ::step, :])
+        w = torch.from_numpy(t["weights"]).cuda()
+        b = torch.from_numpy(t["bias"]).cuda()
+        assert d.prepare(w, b) == E.ELD_OK
+        out_a = torch.zeros(int(np.prod(R.out_shape(case))), dtype=torch.float32, device="cuda")
+        out_b = torch.zeros_like(out_a)
+        s = torch.cuda.current_stream().cuda_stream
+        assert d.enqueue(out_a, small, None, None, s) == E.ELD_OK
+        assert d.enqueue_strided(out_b, big, sh, sw, step, s) == E.ELD_OK
+        torch.cuda.synchronize()
+        assert d.device_status() == 0
+        assert torch.equal(out_a, out_b)
+        # a plane that does not subsample to this plan's input is refused
+        assert d.enqueue_strided(out_b, big, sh + step, sw, step, s) != E.ELD_OK
+    finally:
+        d.close()
+
+
+def test_strided_input_is_refused_where_the_kernel_cannot_do_it(pkg):
+    import gpuutil as G
+    E = G.package()
+    case = _f32("wino4_step", 1, 32, 32, 8, 8, tile=4)
+    d = G.make_desc(case)
+    assert d.setup() == E.ELD_OK, E.last_error()
+    try:
+        assert not d.input_step_supported()
+    finally:
+        d.close()
