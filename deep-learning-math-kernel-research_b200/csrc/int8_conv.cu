@@ -541,9 +541,11 @@ I8UmmaConfig i8_umma_config(int ocb, int cb, int taps, int mode) {
   // K chunks (of 16 channels) per stage.  Handing a stage from role to role costs the single-thread
   // role loops about a thousand cycles whatever its size, and the MMAs of a stage of 8 chunks take
   // less than that below 256 output channels: those tiles move 16 chunks per stage (BOX mode needs
-  // at most 15 copies per stage for that, i.e. an even number of channel blocks).
+  // at most 15 copies per stage for that, i.e. an even number of channel blocks).  A K of 9..16
+  // chunks (the 3-channel first layer of an image network) becomes a single stage.
   c.KC = 8;
-  const bool kc16_ok = c.BN <= 128 && cb * taps >= 32 && (mode == I8_MODE_FLAT || cb % 2 == 0);
+  // (an odd number of channel blocks is fetched block by block: fine while K has at most 15 of them)
+  const bool kc16_ok = c.BN <= 128 && cb * taps > 8 && (mode == I8_MODE_FLAT || cb % 2 == 0 || cb * taps <= 15);
   if (tune_env("ELB_I8_KC", kc16_ok ? 16 : 8) == 16 && kc16_ok) c.KC = 16;
   if (c.KC == 16) {
     c.STAGES = c.BN == 128 ? 3 : 4;
