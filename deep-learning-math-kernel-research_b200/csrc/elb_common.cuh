@@ -67,10 +67,17 @@ __device__ __forceinline__ void requant_store16(const int (&acc)[16], const floa
     f[4 * i + 2] = requant_one(acc[4 * i + 2], c.z, h.z);
     f[4 * i + 3] = requant_one(acc[4 * i + 3], c.w, h.w);
   }
+  // (an upper bound of +inf -- plain ReLU -- needs no min; the test is uniform)
+  const bool clamp_hi = rq.relu_hi < 3.0e38f;
   if (rq.out_type == OUT_F32) {
     if (rq.relu) {
+      if (clamp_hi) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
+        for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) f[i] = fmaxf(f[i], rq.relu_lo);
+      }
     }
     float4 *o = reinterpret_cast<float4 *>(out);
 #pragma unroll
@@ -89,8 +96,13 @@ __device__ __forceinline__ void requant_store16(const int (&acc)[16], const floa
     }
   }
   if (rq.relu) {
+    if (clamp_hi) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
+      for (int i = 0; i < 16; ++i) f[i] = fminf(fmaxf(f[i], rq.relu_lo), rq.relu_hi);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = fmaxf(f[i], rq.relu_lo);
+    }
   }
   uint32_t w[4];
   // Packing with saturation.  s8: signed saturation is what the reference does.  u8: the reference
