@@ -115,6 +115,54 @@ __device__ __forceinline__ void at6(const float (&f)[6], float (&p)[4]) {
   p[3] = __fadd_rn(__fmaf_rn(t2, z5, __fmul_rn(t3, z2)), f[5]);
 }
 
+// Two-lane fp32 arithmetic (add / mul / fma .f32x2: each lane rounds exactly as the scalar
+// instruction does).  The output transform runs few warps per SM and the four channels of a thread go
+// through identical arithmetic: as two channel pairs the same work is half the instructions and,
+// as compiled, 136 registers instead of 181 (c1's output transform 0.147 -> 0.137 ms, VGG conv1_2's
+// 0.282 -> 0.259 ms).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+// at6 on two channels at once, operation for operation
+__device__ __forceinline__ void at6x2(const f32x2 (&f)[6], f32x2 (&p)[4]) {
+  const f32x2 z0 = pack2(1.5f, 1.5f), z1 = pack2(2.25f, 2.25f), z2 = pack2(3.375f, 3.375f), z3 = pack2(0.625f, 0.625f),
+              z4 = pack2(0.390625f, 0.390625f), z5 = pack2(0.244140625f, 0.244140625f);
+  const f32x2 t0 = add2(f[1], f[2]);
+  const f32x2 t1 = add2(f[3], f[4]);
+  const f32x2 t2 = sub2(f[1], f[2]);
+  const f32x2 t3 = sub2(f[3], f[4]);
+  p[0] = add2(add2(t0, t1), f[0]);
+  p[1] = fma2(t2, z3, mul2(t3, z0));
+  p[2] = fma2(t0, z4, mul2(t1, z1));
+  p[3] = add2(fma2(t2, z5, mul2(t3, z2)), f[5]);
+}
+
 struct WinoGeom {
   int A;          // input tile edge: 6 = F(4x4,3x3), 4 = F(2x2,3x3); output tile edge A - 2.
                   // 1 = fp32 direct convolution: one "position", a GEMM row per output pixel
@@ -194,7 +242,9 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
         m[h][w][0] = v.x; m[h][w][1] = v.y; m[h][w][2] = v.z; m[h][w][3] = v.w;
       }
   }
-  // pass along h, in place
+  // pass along h, in place.  (Two channels per instruction, as in the output transform, measured
+  // SLOWER here: c1's input transform 0.127 -> 0.137 ms, VGG conv1_2's 0.245 -> 0.264 ms; and without
+  // effect in the u8 kernel below: c4's 0.084 ms either way.)
 #pragma unroll
   for (int w = 0; w < 6; ++w)
 #pragma unroll
@@ -1253,19 +1303,15 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid
     for (int j = 0; j < 6; ++j)
       raw[i][j] = __ldg(reinterpret_cast<const float4 *>(
           p.m_in + (((static_cast<size_t>(i * 6 + j) * g.OCB + ocb) * 4 + quad) * g.Tpad + t) * 4));
-  float m[4][6][4];   // after the pass along h: m[i][j][channel]
+  f32x2 m[4][6][2];   // after the pass along h: m[i][j][channel pair]
 #pragma unroll
   for (int j = 0; j < 6; ++j) {
-    float col[6][4];
 #pragma unroll
-    for (int i = 0; i < 6; ++i) {
-      col[i][0] = raw[i][j].x; col[i][1] = raw[i][j].y; col[i][2] = raw[i][j].z; col[i][3] = raw[i][j].w;
-    }
+    for (int c = 0; c < 2; ++c) {
+      f32x2 f[6], q[4];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float f[6] = {col[0][c], col[1][c], col[2][c], col[3][c], col[4][c], col[5][c]};
-      float q[4];
-      at6(f, q);
+      for (int i = 0; i < 6; ++i) f[i] = c == 0 ? pack2(raw[i][j].x, raw[i][j].y) : pack2(raw[i][j].z, raw[i][j].w);
+      at6x2(f, q);
 #pragma unroll
       for (int i = 0; i < 4; ++i) m[i][j][c] = q[i];
     }
@@ -1279,12 +1325,12 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid
     const int oh = 4 * th + i;
     float y[4][4];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float f[6] = {m[i][0][c], m[i][1][c], m[i][2][c], m[i][3][c], m[i][4][c], m[i][5][c]};
-      float q[4];
-      at6(f, q);
+    for (int c = 0; c < 2; ++c) {
+      const f32x2 f[6] = {m[i][0][c], m[i][1][c], m[i][2][c], m[i][3][c], m[i][4][c], m[i][5][c]};
+      f32x2 q[4];
+      at6x2(f, q);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) y[j][c] = q[j];
+      for (int j = 0; j < 4; ++j) unpack2(q[j], y[j][2 * c], y[j][2 * c + 1]);
     }
     if (oh >= g.OH) continue;
 #pragma unroll
