@@ -136,6 +136,33 @@ __device__ __forceinline__ void mac_row(const RowWin<S> &w, const FilterRow &f, 
   }
 }
 
+// Two-lane fp32 arithmetic (each lane rounds exactly as the scalar instruction with the same
+// rounding mode does): the epilogue below is bound by instruction issue.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2_rm(f32x2 a, f32x2 b) {      // round toward minus infinity
+  f32x2 d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 #ifndef DW_MIN_BLOCKS
 #define DW_MIN_BLOCKS 3      // resident 256-thread blocks per SM the register allocation must allow
 #endif
@@ -241,29 +268,47 @@ __global__ void __launch_bounds__(256, DW_MIN_BLOCKS) dw_kernel(const __grid_con
               make_int4(acc[k][0] - ACC0, acc[k][1] - ACC0, acc[k][2] - ACC0, acc[k][3] - ACC0);
     }
     float f[4][4];
+    if (FAST) {
+      // channel pairs: (acc - magic) * scale + shift in two packed instructions per pair
+      const f32x2 magic2 = pack2(MAGIC, MAGIC);
+      const f32x2 sc2[2] = {pack2(sc[0], sc[1]), pack2(sc[2], sc[3])}, sh2[2] = {pack2(sh[0], sh[1]), pack2(sh[2], sh[3])};
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+      for (int k = 0; k < 4; ++k)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float a = FAST ? __fsub_rn(__int_as_float(acc[k][c]), MAGIC) : __int2float_rn(acc[k][c]);
-        float v = __fmaf_rn(a, sc[c], sh[c]);
-        if (p.relu) {
-          v = fmaxf(v, p.relu_lo);
-          if (clamp_hi) v = fminf(v, p.relu_hi);
+        for (int c = 0; c < 2; ++c) {
+          const f32x2 a = sub2(pack2(__int_as_float(acc[k][2 * c]), __int_as_float(acc[k][2 * c + 1])), magic2);
+          unpack2(fma2(a, sc2[c], sh2[c]), f[k][2 * c], f[k][2 * c + 1]);
         }
-        f[k][c] = v;
-      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) f[k][c] = __fmaf_rn(__int2float_rn(acc[k][c]), sc[c], sh[c]);
+    }
+    if (p.relu) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          f[k][c] = fmaxf(f[k][c], p.relu_lo);
+          if (clamp_hi) f[k][c] = fminf(f[k][c], p.relu_hi);
+        }
+    }
     uint32_t cw[4] = {0u, 0u, 0u, 0u};       // per channel: bytes = pixels 0..3
     bool packed = false;
     if (FAST) {
       if (floored) {
         uint32_t any = 0u, bits[4][4];
+        const f32x2 magic2 = pack2(MAGIC, MAGIC);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            bits[k][c] = __float_as_uint(__fadd_rd(f[k][c], MAGIC));     // MAGIC_BITS + floor(f)
-            any |= bits[k][c];
+          for (int c = 0; c < 2; ++c) {
+            float b0, b1;
+            unpack2(add2_rm(pack2(f[k][2 * c], f[k][2 * c + 1]), magic2), b0, b1);     // MAGIC_BITS + floor(f)
+            bits[k][2 * c] = __float_as_uint(b0);
+            bits[k][2 * c + 1] = __float_as_uint(b1);
+            any |= bits[k][2 * c] | bits[k][2 * c + 1];
           }
         if ((any & 0x003FFF00u) == 0u) {      // all sixteen floored values fit a byte: no carries anywhere
 #pragma unroll

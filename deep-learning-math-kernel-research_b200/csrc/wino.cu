@@ -1319,20 +1319,41 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid
   float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
   if (p.with_bias && p.bias) bias4 = *reinterpret_cast<const float4 *>(p.bias + ocb * 16 + quad * 4);
   const float bb[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
+  const f32x2 bias_lo = pack2(bias4.x, bias4.y), bias_hi = pack2(bias4.z, bias4.w);
   const int elt = p.out_type == OUT_F32 ? 4 : 1;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int oh = 4 * th + i;
     float y[4][4];
+    f32x2 yp[4][2];
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       const f32x2 f[6] = {m[i][0][c], m[i][1][c], m[i][2][c], m[i][3][c], m[i][4][c], m[i][5][c]};
       f32x2 q[4];
       at6x2(f, q);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) unpack2(q[j], y[j][2 * c], y[j][2 * c + 1]);
+      for (int j = 0; j < 4; ++j) { yp[j][c] = q[j]; unpack2(q[j], y[j][2 * c], y[j][2 * c + 1]); }
     }
     if (oh >= g.OH) continue;
+    if (p.out_type == OUT_F32 && !p.with_sum) {
+      // the common case (fp32 result, no residual): bias on channel pairs, one address per row
+      float *row0 = static_cast<float *>(p.out) +
+                    ((((static_cast<size_t>(n) * g.OCB + ocb) * g.OH + oh) * g.OW + 4 * tw) * 16 + quad * 4);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (4 * tw + j >= g.OW) continue;
+        float4 v;
+        if (p.with_bias) {
+          unpack2(add2(yp[j][0], bias_lo), v.x, v.y);
+          unpack2(add2(yp[j][1], bias_hi), v.z, v.w);
+        } else {
+          v = make_float4(y[j][0], y[j][1], y[j][2], y[j][3]);
+        }
+        if (p.with_relu) { v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f); }
+        *reinterpret_cast<float4 *>(row0 + j * 16) = v;
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int ow = 4 * tw + j;
