@@ -230,17 +230,33 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
         for (int c = 0; c < 4; ++c)
           m[h][w][c] = __fsub_rn(__uint_as_float(__byte_perm(raw[h][w], 0x4B000000u, 0x7650 + c)), 8388608.0f);
   } else {
+    // one base pointer per thread, row and column offsets added to it; tiles that do not touch the
+    // image border load without any bounds test (the address arithmetic and the predicates of 36
+    // separately addressed loads cost this kernel more than its transform)
+    const float4 *plane = reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) +
+                                                           (static_cast<size_t>(n) * g.CB + cb) * p.SH * p.SW * 16) + quad;
+    const int row_pitch = p.SW * p.step * 4, col_pitch = p.step * 4;      // in float4 units
+    if (live && ih0 >= 0 && iw0 >= 0 && ih0 + 5 < g.IH && iw0 + 5 < g.IW) {
+      const float4 *p0 = plane + static_cast<size_t>(ih0) * row_pitch + iw0 * col_pitch;
 #pragma unroll
-    for (int h = 0; h < 6; ++h)
+      for (int h = 0; h < 6; ++h)
 #pragma unroll
-      for (int w = 0; w < 6; ++w) {
-        const int ih = ih0 + h, iw = iw0 + w;
-        const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
-        const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * p.SH + (ok ? ih * p.step : 0)) * p.SW + (ok ? iw * p.step : 0);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ok) v = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(p.in) + pix * 16) + quad);
-        m[h][w][0] = v.x; m[h][w][1] = v.y; m[h][w][2] = v.z; m[h][w][3] = v.w;
-      }
+        for (int w = 0; w < 6; ++w) {
+          const float4 v = __ldg(p0 + h * row_pitch + w * col_pitch);
+          m[h][w][0] = v.x; m[h][w][1] = v.y; m[h][w][2] = v.z; m[h][w][3] = v.w;
+        }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 6; ++h)
+#pragma unroll
+        for (int w = 0; w < 6; ++w) {
+          const int ih = ih0 + h, iw = iw0 + w;
+          const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (ok) v = __ldg(plane + static_cast<size_t>(ih) * row_pitch + iw * col_pitch);
+          m[h][w][0] = v.x; m[h][w][1] = v.y; m[h][w][2] = v.z; m[h][w][3] = v.w;
+        }
+    }
   }
   // pass along h, in place.  (Two channels per instruction, as in the output transform, measured
   // SLOWER here: c1's input transform 0.127 -> 0.137 ms, VGG conv1_2's 0.245 -> 0.264 ms; and without
@@ -256,6 +272,9 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
       for (int i = 0; i < 6; ++i) m[i][w][c] = o[i];
     }
   // pass along w, one transformed row at a time, stored as soon as it is ready
+  float *v_base = static_cast<float *>(p.a_img) +
+                  ((static_cast<size_t>(mt) * g.k_stages + cb) * (A_RAW_BYTES / 4) + (quad * BM + row) * 4);   // fp32: position 0
+  const size_t v_step = static_cast<size_t>(g.m_tiles) * g.k_stages * (A_RAW_BYTES / 4);                        // ... to the next position
 #pragma unroll
   for (int i = 0; i < 6; ++i) {
     float v[6][4];
@@ -302,9 +321,8 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_input_kernel(const __grid_
       } else {
         // stage = this channel block, chunk = quad; plain fp32 (the GEMM kernel splits it into its
         // tf32 hi / lo planes in shared memory, so V crosses HBM once, not twice)
-        const size_t stage = (static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + cb;
-        float *base = static_cast<float *>(p.a_img) + stage * (A_RAW_BYTES / 4);
-        *reinterpret_cast<float4 *>(base + (quad * BM + row) * 4) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+        // (one base address per thread + a constant step per position)
+        *reinterpret_cast<float4 *>(v_base + static_cast<size_t>(a) * v_step) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
       }
     }
   }
@@ -336,15 +354,25 @@ __global__ void __launch_bounds__(TRANS_THREADS, 512 / TRANS_THREADS) wino_input
   const int ih0 = 4 * th - g.pad_t, iw0 = 4 * tw - g.pad_l;
   const bool border = th == 0 || tw == 0 || th == g.ht - 1 || tw == g.wt - 1;   // src/elx_conv_wino_trans_input.hpp:247-249
   uint32_t raw[6][6], outw[36];
+  // one base pointer per thread; tiles inside the image load without bounds tests (see the fp32 kernel)
+  const uint32_t *plane = reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(p.in) +
+                                                             (static_cast<size_t>(n) * g.CB + cb) * g.IH * g.IW * 16) + quad;
+  if (live && ih0 >= 0 && iw0 >= 0 && ih0 + 5 < g.IH && iw0 + 5 < g.IW) {
+    const uint32_t *p0 = plane + (static_cast<size_t>(ih0) * g.IW + iw0) * 4;
 #pragma unroll
-  for (int h = 0; h < 6; ++h)
+    for (int h = 0; h < 6; ++h)
 #pragma unroll
-    for (int w = 0; w < 6; ++w) {
-      const int ih = ih0 + h, iw = iw0 + w;
-      const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
-      const size_t pix = ((static_cast<size_t>(n) * g.CB + cb) * g.IH + (ok ? ih : 0)) * g.IW + (ok ? iw : 0);
-      raw[h][w] = ok ? __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(p.in) + pix * 16) + quad) : 0u;
-    }
+      for (int w = 0; w < 6; ++w) raw[h][w] = __ldg(p0 + (h * g.IW + w) * 4);
+  } else {
+#pragma unroll
+    for (int h = 0; h < 6; ++h)
+#pragma unroll
+      for (int w = 0; w < 6; ++w) {
+        const int ih = ih0 + h, iw = iw0 + w;
+        const bool ok = live && ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW;
+        raw[h][w] = ok ? __ldg(plane + (static_cast<size_t>(ih) * g.IW + iw) * 4) : 0u;
+      }
+  }
 #pragma unroll
   for (int a = 0; a < 36; ++a) outw[a] = 0u;
 #pragma unroll 1
@@ -397,11 +425,11 @@ __global__ void __launch_bounds__(TRANS_THREADS, 512 / TRANS_THREADS) wino_input
     }
   }
   // stage = 8 channel blocks; chunk = cb % 8; 4 bytes per thread, 128 contiguous bytes per warp
+  uint32_t *v_base = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) +
+                     (((static_cast<size_t>(mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4);   // position 0
+  const size_t v_step = static_cast<size_t>(g.m_tiles) * g.k_stages * 8 * BM * 4;                                        // words to the next one
 #pragma unroll
-  for (int a = 0; a < 36; ++a) {
-    const size_t off = ((((static_cast<size_t>(a) * g.m_tiles + mt) * g.k_stages + (cb >> 3)) * 8 + (cb & 7)) * BM + row) * 16 + quad * 4;
-    *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.a_img) + off) = live ? outw[a] : 0u;
-  }
+  for (int a = 0; a < 36; ++a) v_base[a * v_step] = live ? outw[a] : 0u;
 }
 
 
@@ -1297,6 +1325,7 @@ __global__ void __launch_bounds__(TRANS_THREADS) wino_output_kernel(const __grid
 
   // all 36 loads first (bytes in flight, see the input transform), then the pass along h
   float4 raw[6][6];
+  // (a hand-made "base + position * step" for these addresses measured slower: 0.107 -> 0.113 ms on c1)
 #pragma unroll
   for (int i = 0; i < 6; ++i)
 #pragma unroll
