@@ -117,3 +117,42 @@ def test_stack_rejects_mismatched_layers(pkg):
     b = G.make_desc(R.ConvCase("b", 2, 48, 32, 8, 8, types="u8f32u8f32", algo="direct", relu=True, bias=True))
     with pytest.raises(RuntimeError):
         E.ConvStack([a, b])
+
+
+@pytest.mark.parametrize("int8", [False, True], ids=["fp32_folds_the_subsample", "int8_keeps_the_kernel"])
+def test_stack_subsample_between_layers(pkg, int8):
+    """Two layers with a stride-2 subsample between them.  fp32 Winograd: the second layer reads every
+    second row and column of the first layer's full output itself (3 + 3 launches, no subsample
+    kernel); INT8 direct: one kernel per layer plus the subsample kernel.  Either way the chain equals
+    the CPU chain with an explicit subsample."""
+    import torch
+    E = G.package()
+    n = 2
+    if int8:
+        cases = [R.ConvCase("sub_a", n, 32, 32, 24, 24, types="u8f32u8f32", algo="direct", relu=True, bias=True, iscale=0.02, oscale=0.05),
+                 R.ConvCase("sub_b", n, 32, 48, 12, 12, types="u8f32u8f32", algo="direct", relu=True, bias=True, iscale=0.05, oscale=0.1)]
+    else:
+        cases = [R.ConvCase("sub_a", n, 32, 32, 24, 24, types="fp32", algo="wino", tile=6, relu=True, bias=True),
+                 R.ConvCase("sub_b", n, 32, 48, 12, 12, types="fp32", algo="wino", tile=6, relu=True, bias=True)]
+    st = E.ConvStack([G.make_desc(c) for c in cases], [2, 1])
+    tens = [R.make_tensors(c) for c in cases]
+    for k, t in enumerate(tens):
+        assert st.prepare(k, torch.from_numpy(t["weights"]).cuda(), torch.from_numpy(t["bias"]).cuda()) == 0
+    x_np = tens[0]["input"]
+    x = torch.from_numpy(x_np).cuda()
+    dt = torch.uint8 if int8 else torch.float32
+    y = torch.zeros((n, 3, 12, 12, 16), dtype=dt, device="cuda")
+    before = st.launch_count()
+    assert st.enqueue(y, x, torch.cuda.current_stream().cuda_stream) == 0, E.last_error()
+    torch.cuda.synchronize()
+    assert st.launch_count() - before == (3 if int8 else 6)
+    oracle = R.oracle_int8_conv if int8 else R.oracle_wino_f32
+    mid = oracle(cases[0], {"input": x_np, "weights": tens[0]["weights"], "bias": tens[0]["bias"]})
+    want = oracle(cases[1], {"input": np.ascontiguousarray(mid[:, :, ::2, ::2, :]), "weights": tens[1]["weights"],
+                             "bias": tens[1]["bias"]})
+    got = y.cpu().numpy()
+    if int8:
+        assert np.array_equal(got, want)
+    else:
+        assert R.rel_l2(got, want) <= 2e-5      # two chained fp32 layers
+    st.close()
