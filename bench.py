@@ -110,6 +110,27 @@ NCU_TRAFFIC = {"c1": 2139.6e6, "c2": 13.15e6, "c3": 26.03e6, "c3s": 38.88e6, "c4
 
 
 # ------------------------------------------------------------------------------------ helpers
+def bind_to_gpu_cpus(index: int):
+    """Several ranks on one box: keep this process (and therefore the pages of the pinned host buffers
+    it is about to allocate, and the threads that feed its copies) on the CPU cores NVML lists as
+    local to its GPU.  Process affinity only -- nothing about the GPU changes.  Returns the number of
+    cores bound to, or None when NVML or the affinity call is unavailable."""
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = nv.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
+
+
 class ClockSampler(threading.Thread):
     """Polls SM clock and throttle reasons through NVML (read-only) while the GPU is under load."""
 
@@ -780,6 +801,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device -- this library has no CPU path")
     torch.cuda.set_device(local_rank)
+    numa = bind_to_gpu_cpus(local_rank) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
