@@ -102,19 +102,6 @@ __device__ __forceinline__ void bt6(const float (&f)[6], float (&o)[6]) {
   o[5] = __fmaf_rn(f[3], z3, t5);
 }
 
-// A^T (src/kernel/elk_conv_wino_4x4_3x3_output.hxx:115-157)
-__device__ __forceinline__ void at6(const float (&f)[6], float (&p)[4]) {
-  const float z0 = 1.5f, z1 = 2.25f, z2 = 3.375f, z3 = 0.625f, z4 = 0.390625f, z5 = 0.244140625f;
-  const float t0 = __fadd_rn(f[1], f[2]);
-  const float t1 = __fadd_rn(f[3], f[4]);
-  const float t2 = __fsub_rn(f[1], f[2]);
-  const float t3 = __fsub_rn(f[3], f[4]);
-  p[0] = __fadd_rn(__fadd_rn(t0, t1), f[0]);
-  p[1] = __fmaf_rn(t2, z3, __fmul_rn(t3, z0));
-  p[2] = __fmaf_rn(t0, z4, __fmul_rn(t1, z1));
-  p[3] = __fadd_rn(__fmaf_rn(t2, z5, __fmul_rn(t3, z2)), f[5]);
-}
-
 // Two-lane fp32 arithmetic (add / mul / fma .f32x2: each lane rounds exactly as the scalar
 // instruction does).  The output transform runs few warps per SM and the four channels of a thread go
 // through identical arithmetic: as two channel pairs the same work is half the instructions and,
@@ -149,7 +136,8 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
-// at6 on two channels at once, operation for operation
+// A^T with the reference's constants and evaluation order (src/kernel/elk_conv_wino_4x4_3x3_output.hxx:115-157),
+// on two channels at once, operation for operation
 __device__ __forceinline__ void at6x2(const f32x2 (&f)[6], f32x2 (&p)[4]) {
   const f32x2 z0 = pack2(1.5f, 1.5f), z1 = pack2(2.25f, 2.25f), z2 = pack2(3.375f, 3.375f), z3 = pack2(0.625f, 0.625f),
               z4 = pack2(0.390625f, 0.390625f), z5 = pack2(0.244140625f, 0.244140625f);
