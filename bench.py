@@ -91,7 +91,8 @@ WORKLOADS = {
                desc="INT8 depthwise 3x3 MobileNet-v1 Conv2d_3 N=64 C=128 56x56 s1 p1 bias+ReLU u8 out nChw16c T=14"),
     "c5": dict(metric="effective_conv_tflops_fp32_winograd_vgg16_stack", unit="TFLOP/s", dtype="tf32x3(fp32)", batch=256,
                desc="VGG-16 conv stack, 13 layers 3x3 p1, 224x224 input, fp32 Winograd F(4x4,3x3), global batch 256 in "
-                    "chunks of 32 images, stride-2 subsample between stages, bias+ReLU, nChw16c"),
+                    "chunks of 32 images, stride-2 subsample between stages, bias+ReLU; the network input is the "
+                    "nchw image (3 planes), activations and weights nChw16c / OIhw16i16o"),
     "c5i8": dict(metric="effective_conv_tops_int8_vgg16_stack", unit="TOP/s", dtype="u8", batch=256,
                  desc="VGG-16 conv stack, 13 layers 3x3 p1, 224x224 input, INT8 u8s8 direct, u8 between layers, global "
                       "batch 256 in chunks of 32 images, stride-2 subsample between stages, bias+ReLU, nChw16c"),
@@ -558,10 +559,13 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
     chunks = chunks_g // ctx.world                  # per GPU
     c_first = ctx.rank * chunks
     scales = vgg_calibrate(ctx.local_rank) if int8 else None
-    st, cases = build_stack(n, int8, ctx.local_rank, scales)
+    # the fp32 stack's first layer reads the caller's nchw image (three planes); the INT8 stack takes
+    # the blocked u8 tensor
+    plain = not int8
+    st, cases = build_stack(n, int8, ctx.local_rank, scales, plain_image=plain)
     ops_chunk = sum(c.cal_ops() for c in cases)
     ops_g = ops_chunk * chunks_g
-    x_np = np.concatenate([vgg_input(c_first + c, n, int8) for c in range(chunks)])
+    x_np = np.concatenate([vgg_input(c_first + c, n, int8, plain) for c in range(chunks)])
     x = torch.from_numpy(x_np).cuda()
     xin = [x[c * n:(c + 1) * n] for c in range(chunks)]
     last = cases[-1]
@@ -670,7 +674,8 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
     eb = 1 if int8 else 4
     for k, c in enumerate(cases):
         w_b = 9 * c.ic * c.oc * 4
-        b = c.n * (16 * ((c.ic + 15) // 16) * c.ih * c.iw + c.oc * c.oh * c.ow) * eb + w_b
+        cin = c.ic if c.ifmt == "nchw" else 16 * ((c.ic + 15) // 16)      # (the plain image has its real channels only)
+        b = c.n * (cin * c.ih * c.iw + c.oc * c.oh * c.ow) * eb + w_b
         if vgg_layers()[k][3] == 2:
             b += 2 * c.n * c.oc * (c.oh // 2) * (c.ow // 2) * eb
         alg_bytes += b

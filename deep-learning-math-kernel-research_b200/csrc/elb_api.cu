@@ -995,6 +995,12 @@ int elb_conv_create(const elb_conv_desc_t *desc, elb_conv_t **plan) {
     }
   }
   if (rc != ELB_OK) { delete pl; return rc; }
+  // the direct kernel for at most four input channels reads an nchw tensor itself: no conversion,
+  // no 16-channel copy of an image of which three channels are real
+  if (cvt_in && ud.fmt_input == ELB_NCHW && pl->info.kernel == ELB_KERNEL_F32_SMALL_IC) {
+    pl->wino.in_planar = true;
+    pl->cvt_in = cvt_in = false;
+  }
   // what the caller sees: the sizes of ITS formats, everything else from the internal plan
   uinfo.algorithm = pl->info.algorithm; uinfo.tile_size = pl->info.tile_size; uinfo.kernel = pl->info.kernel;
   uinfo.device = pl->info.device; uinfo.launches_per_call = pl->info.launches_per_call + (cvt_in ? 1 : 0) + (cvt_out ? 1 : 0);

@@ -170,7 +170,10 @@ int elb_stack_create(const elb_conv_desc_t *descs, const int32_t *subsample_afte
     if (l.step < 1) { delete st; return mfail(ELB_GENERAL_ERROR, "layer %d: subsample step must be >= 1", k); }
     if (l.d.fmt_input == ELB_FMT_UNDEF) l.d.fmt_input = ELB_NCHW16C;
     if (l.d.fmt_output == ELB_FMT_UNDEF) l.d.fmt_output = ELB_NCHW16C;
-    if (l.d.fmt_input != ELB_NCHW16C || l.d.fmt_output != ELB_NCHW16C) {
+    // (the first layer may take the caller's plain image, nchw or nhwc, as the reference's own
+    // first-layer runs do; everything between the layers is blocked)
+    const bool plain_image = k == 0 && (l.d.fmt_input == ELB_NCHW || l.d.fmt_input == ELB_NHWC);
+    if ((l.d.fmt_input != ELB_NCHW16C && !plain_image) || l.d.fmt_output != ELB_NCHW16C) {
       delete st;
       return mfail(ELB_UNIMPLEMENTED, "layer %d: a stack runs on nChw16c activations", k);
     }

@@ -60,7 +60,16 @@ __device__ __forceinline__ void st_global_v8(void *ptr, const float (&v)[8]) {
 // IC = 3 compiles the kernel for three input channels (an RGB image, the case that matters): the 27
 // (tap, channel) steps then form one straight-line block whose weight loads the compiler can issue
 // ahead of the arithmetic; IC = 0 tests the channel count at run time.
-template <int IC>
+//
+// PLANAR reads the caller's nchw tensor (how the reference's own first-layer runs pass an image,
+// --input-format=nchw): three planes of floats instead of 16-channel blocks of which three channels
+// are real, i.e. less than a fifth of the input bytes over PCIe and from HBM, and loads that
+// neighbouring lanes share lines of (a lane's strip is 16 contiguous bytes of each plane row).
+__device__ __forceinline__ void set_channel(float4 &v, int ch, float x) {
+  if (ch == 0) v.x = x; else if (ch == 1) v.y = x; else if (ch == 2) v.z = x; else v.w = x;
+}
+
+template <int IC, bool PLANAR>
 __global__ void __launch_bounds__(SI_THREADS, 3) f32_small_ic_kernel(const SmallIcParams p) {
   extern __shared__ float4 s_w4[];                 // [9 taps][4 channels][OCP] floats, then [OCP] bias
   float *s_w = reinterpret_cast<float *>(s_w4);
@@ -79,17 +88,46 @@ __global__ void __launch_bounds__(SI_THREADS, 3) f32_small_ic_kernel(const Small
 
   // the four real channels of the 3 x 6 input pixels around the strip (zero outside the image)
   float4 win[3][6];
-  const float *in_n = p.in + static_cast<size_t>(n) * p.CB * p.H * p.W * 16;      // channel block 0 holds every real channel
+  if (PLANAR) {
+    const float *in_n = p.in + static_cast<size_t>(n) * p.ic * p.H * p.W;
+    const bool vec = (p.W & 3) == 0;               // rows start on 16-byte boundaries: one float4 for the strip itself
 #pragma unroll
-  for (int r = 0; r < 3; ++r) {
-    const int ih = oh - 1 + r;
+    for (int r = 0; r < 3; ++r) {
+      const int ih = oh - 1 + r;
+      const bool row_ok = ih >= 0 && ih < p.H;
 #pragma unroll
-    for (int c = 0; c < 6; ++c) {
-      const int iw = ow0 - 1 + c;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
-        v = __ldg(reinterpret_cast<const float4 *>(in_n + (static_cast<size_t>(ih) * p.W + iw) * 16));
-      win[r][c] = v;
+      for (int c = 0; c < 6; ++c) win[r][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        if ((IC != 0 ? ch < IC : ch < p.ic) && row_ok) {
+          const float *row = in_n + (static_cast<size_t>(ch) * p.H + ih) * p.W;
+          if (vec) {
+            const float4 m = __ldg(reinterpret_cast<const float4 *>(row + ow0));
+            set_channel(win[r][1], ch, m.x); set_channel(win[r][2], ch, m.y);
+            set_channel(win[r][3], ch, m.z); set_channel(win[r][4], ch, m.w);
+          } else {
+#pragma unroll
+            for (int c = 1; c < 5; ++c)
+              if (ow0 + c - 1 < p.W) set_channel(win[r][c], ch, __ldg(row + ow0 + c - 1));
+          }
+          if (ow0 > 0) set_channel(win[r][0], ch, __ldg(row + ow0 - 1));
+          if (ow0 + 4 < p.W) set_channel(win[r][5], ch, __ldg(row + ow0 + 4));
+        }
+      }
+    }
+  } else {
+    const float *in_n = p.in + static_cast<size_t>(n) * p.CB * p.H * p.W * 16;    // channel block 0 holds every real channel
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int ih = oh - 1 + r;
+#pragma unroll
+      for (int c = 0; c < 6; ++c) {
+        const int iw = ow0 - 1 + c;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
+          v = __ldg(reinterpret_cast<const float4 *>(in_n + (static_cast<size_t>(ih) * p.W + iw) * 16));
+        win[r][c] = v;
+      }
     }
   }
 
@@ -166,16 +204,24 @@ size_t f32_small_ic_smem_bytes(int OCB) { return (static_cast<size_t>(9) * 4 + 1
 
 cudaError_t init_f32_small_ic(int OCB) {
   const int bytes = static_cast<int>(f32_small_ic_smem_bytes(OCB));
-  cudaError_t e = cudaFuncSetAttribute(f32_small_ic_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(f32_small_ic_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  cudaError_t e = cudaFuncSetAttribute(f32_small_ic_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(f32_small_ic_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(f32_small_ic_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(f32_small_ic_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   return e;
 }
 
 cudaError_t launch_f32_small_ic(const SmallIcParams &p, cudaStream_t s) {
   const long long threads = static_cast<long long>(p.N) * p.H * ((p.W + 3) / 4);
   const unsigned blocks = static_cast<unsigned>((threads + SI_THREADS - 1) / SI_THREADS);
-  if (p.ic == 3) f32_small_ic_kernel<3><<<blocks, SI_THREADS, f32_small_ic_smem_bytes(p.OCB), s>>>(p);
-  else f32_small_ic_kernel<0><<<blocks, SI_THREADS, f32_small_ic_smem_bytes(p.OCB), s>>>(p);
+  const size_t smem = f32_small_ic_smem_bytes(p.OCB);
+  if (p.planar) {
+    if (p.ic == 3) f32_small_ic_kernel<3, true><<<blocks, SI_THREADS, smem, s>>>(p);
+    else f32_small_ic_kernel<0, true><<<blocks, SI_THREADS, smem, s>>>(p);
+  } else {
+    if (p.ic == 3) f32_small_ic_kernel<3, false><<<blocks, SI_THREADS, smem, s>>>(p);
+    else f32_small_ic_kernel<0, false><<<blocks, SI_THREADS, smem, s>>>(p);
+  }
   return cudaGetLastError();
 }
 

@@ -1932,7 +1932,9 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
   if (w->small_ic) {
     const WinoGeom &g = w->g;
     SmallIcParams sp{};
-    sp.in = static_cast<const float *>(in) + static_cast<size_t>(first) * (w->in_img_bytes / 4);
+    sp.planar = pl.in_planar ? 1 : 0;
+    sp.in = static_cast<const float *>(in) +
+            static_cast<size_t>(first) * (pl.in_planar ? static_cast<size_t>(w->ic_real) * g.IH * g.IW : w->in_img_bytes / 4);
     sp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
     sp.w = static_cast<const float *>(w->d_w_small);
     sp.bias = static_cast<const float *>(w->d_bias);

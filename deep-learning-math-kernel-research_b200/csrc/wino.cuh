@@ -14,6 +14,9 @@ struct WinoPlan {
   // next call only: the input tensor is a plane of src_h x src_w pixels of which the convolution reads
   // every in_step-th row and column (a subsample folded into the input transform); 1 = plain
   int in_step = 1, src_h = 0, src_w = 0;
+  // the input tensor is the caller's nchw tensor (only the direct kernel for at most four input
+  // channels reads one; set by the C-ABI layer after wino_setup)
+  bool in_planar = false;
 };
 // Can this plan read its input with a step (fp32 Winograd F(4x4,3x3) through the transform kernels)?
 bool wino_input_step_supported(const WinoPlan &pl);
@@ -31,12 +34,13 @@ void wino_release(WinoPlan &pl);
 
 // fp32 3x3 stride-1 pad-1 convolution with at most four input channels (f32_small_ic.cu)
 struct SmallIcParams {
-  const float *in;      // nChw16c fp32, first image of the range
+  const float *in;      // nChw16c fp32 (planar: nchw), first image of the range
   const float *w;       // [9 taps][4 channels][OCP] fp32
   const float *bias;    // [OCP]
   float *out;           // nChw16c fp32
   int N, H, W, CB, OCB, ic;
   int with_bias, with_relu, with_sum;
+  int planar;           // the input is the caller's nchw tensor
 };
 size_t f32_small_ic_smem_bytes(int OCB);
 cudaError_t init_f32_small_ic(int OCB);        // once per plan and device (kernel attribute)

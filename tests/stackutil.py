@@ -54,8 +54,13 @@ VGG_F32_KNOBS = {
 }
 
 
-def vgg_layer_case(idx, ic, oc, hw, n, int8, iscale=1.0, oscale=1.0):
+def vgg_layer_case(idx, ic, oc, hw, n, int8, iscale=1.0, oscale=1.0, plain_image=False):
+    """plain_image: the first layer takes the caller's nchw image (three planes) instead of a blocked
+    tensor of 16 channels of which three are real, as the reference's own first-layer runs do
+    (scripts/regression-fp32.sh: --input-format=nchw)."""
     import refutil as R
+    if plain_image and idx == 0:
+        return dataclasses.replace(vgg_layer_case(idx, ic, oc, hw, n, int8, iscale, oscale), ifmt="nchw")
     if int8:
         # blocking in the style of the reference's tuned int8 direct scripts (e.g.
         # scripts/best_configs/resnet-n64-8180-1s-direct-int8.sh): 1.5 - 2 x faster on the CPU than one
@@ -79,8 +84,9 @@ def vgg_weights(idx, ic, oc):
     return R.weights_buffer(R.to_OIhw16i16o(w)), b
 
 
-def vgg_input(chunk: int, n: int, int8: bool):
-    """Blocked network input of chunk `chunk` (n images): 3 channels zero-padded to 16 (fp32 U[-1,1] / u8 U[0,255])."""
+def vgg_input(chunk: int, n: int, int8: bool, plain: bool = False):
+    """Network input of chunk `chunk` (n images), fp32 U[-1,1] / u8 U[0,255]: blocked (3 channels
+    zero-padded to 16), or the same values as an nchw image when plain."""
     import numpy as np
     import refutil as R
     g = np.random.Generator(np.random.Philox(R.seed_for("vgg16", f"input{chunk}")))
@@ -88,10 +94,10 @@ def vgg_input(chunk: int, n: int, int8: bool):
         x = g.integers(0, 256, (n, 3, 224, 224), dtype=np.uint8)
     else:
         x = g.uniform(-1.0, 1.0, (n, 3, 224, 224)).astype(np.float32)
-    return R.to_nChw16c(x)
+    return x if plain else R.to_nChw16c(x)
 
 
-def build_stack(n, int8, device, scales=None):
+def build_stack(n, int8, device, scales=None, plain_image=False):
     """The 13 convolutions as ONE stack object of the library (elb_stack_*), weights prepared."""
     import torch
     import gpuutil as G
@@ -100,7 +106,7 @@ def build_stack(n, int8, device, scales=None):
     descs, cases = [], []
     for k, (ic, oc, hw, _) in enumerate(layers):
         isc, osc = (scales[k], scales[k + 1]) if int8 else (1.0, 1.0)
-        case = vgg_layer_case(k, ic, oc, hw, n, int8, isc, osc)
+        case = vgg_layer_case(k, ic, oc, hw, n, int8, isc, osc, plain_image)
         descs.append(G.make_desc(case, device=device))
         cases.append(case)
     st = E.ConvStack(descs, [l[3] for l in layers])
@@ -152,11 +158,11 @@ def stack_reference_chain(cases, x_np, int8, keep=None):
     keep: optional list that receives every layer's output (before the subsample)."""
     import numpy as np
     import refutil as R
-    x = x_np
+    x = R.to_nChw16c(x_np) if x_np.ndim == 4 else x_np        # (an nchw image: the CPU side takes it blocked)
     layers = vgg_layers()
     kind = "reference" if R.reference_available() else "port"
     for k, case in enumerate(cases):
-        c = dataclasses.replace(case, n=x.shape[0])
+        c = dataclasses.replace(case, n=x.shape[0], ifmt="")
         w, b = vgg_weights(k, c.ic, c.oc)
         t = {"input": np.ascontiguousarray(x), "weights": w, "bias": b}
         if kind == "reference":
@@ -198,9 +204,9 @@ def per_layer_parity(cases, x_np, gpu_outs, int8):
     layers = vgg_layers()
     kind = "reference" if R.reference_available() else "port"
     figures = []
-    x = x_np
+    x = R.to_nChw16c(x_np) if x_np.ndim == 4 else x_np
     for k, case in enumerate(cases):
-        c = dataclasses.replace(case, n=x.shape[0])
+        c = dataclasses.replace(case, n=x.shape[0], ifmt="")
         w, b = vgg_weights(k, c.ic, c.oc)
         t = {"input": np.ascontiguousarray(x), "weights": w, "bias": b}
         want = R.run_reference(c, t)[0] if kind == "reference" else oracle_fn(c)(c, t)

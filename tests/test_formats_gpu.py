@@ -30,6 +30,13 @@ CASES = [
         ifmt="nhwc", ofmt="nhwc", wfmt="hwio"),
     R.ConvCase("fmt_f32_wino_rgb_nchw", 2, 3, 64, 16, 16, types="fp32", algo="wino", tile=6, relu=True, bias=True,
                ifmt="nchw", wfmt="oihw"),
+    # the direct kernel for at most four input channels reads an nchw image itself (no conversion)
+    R.ConvCase("fmt_f32_wino_rgb_nchw_ragged", 2, 3, 32, 21, 30, types="fp32", algo="wino", tile=6, relu=True, bias=True,
+               ifmt="nchw"),
+    R.ConvCase("fmt_f32_wino_gray_nchw_both", 1, 1, 16, 9, 13, types="fp32", algo="wino", tile=6, relu=False, bias=True,
+               ifmt="nchw", ofmt="nchw", wfmt="oihw"),
+    R.ConvCase("fmt_f32_wino_4ch_nchw_sum", 1, 4, 40, 12, 12, types="fp32", algo="wino", tile=6, relu=True, bias=True,
+               sum=True, ifmt="nchw"),
     R.ConvCase("fmt_f32_wino_nhwc", 1, 32, 48, 9, 11, types="fp32", algo="wino", tile=4, relu=True, bias=True,
                ifmt="nhwc", ofmt="nhwc", wfmt="hwio"),
     R.ConvCase("fmt_f32_1x1_nhwc_sum", 2, 64, 40, 8, 8, kh=1, kw=1, pad=0, types="fp32", algo="1x1", relu=True, bias=True,

@@ -49,6 +49,28 @@ def test_vgg16_chain_fp32_every_layer(pkg):
     st.close()
 
 
+def test_vgg16_chain_fp32_takes_the_plain_image(pkg):
+    """The first layer given the caller's nchw image (three planes, how the reference's own first-layer
+    runs pass it) produces the bytes of the chain fed the blocked tensor, on the device and through
+    elb_stack_execute from the host; the image is less than a fifth of the bytes."""
+    import torch
+    n = 2
+    st_b, cases_b = S.build_stack(n, False, 0)
+    st_p, cases_p = S.build_stack(n, False, 0, plain_image=True)
+    assert cases_p[0].ifmt == "nchw"
+    x_b, x_p = S.vgg_input(0, n, False), S.vgg_input(0, n, False, plain=True)
+    assert x_p.shape == (n, 3, 224, 224) and x_p.nbytes * 5 < x_b.nbytes
+    got_b, _ = _gpu_chain(st_b, cases_b, x_b, torch.float32)
+    got_p, y_p = _gpu_chain(st_p, cases_p, x_p, torch.float32)
+    for k, c in enumerate(cases_b):
+        assert np.array_equal(got_b[k], got_p[k]), f"{c.name}: the plain image gives other bytes"
+    hy = np.zeros(tuple(y_p.shape), np.float32)
+    assert st_p.execute(hy, x_p, n) == 0, G.package().last_error()
+    assert np.array_equal(hy, got_b[-1])
+    st_b.close()
+    st_p.close()
+
+
 def test_vgg16_chain_int8_every_layer_bit_exact(pkg):
     import torch
     n = 2
