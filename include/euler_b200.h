@@ -245,7 +245,11 @@ ELB_API int elb_subsample_nChw16c(void *dst, const void *src, int n, int c, int 
  * buffer sets): layer k's output is layer k+1's input, u8 between int8 layers, fp32 between fp32
  * layers; subsample_after[k] = s > 1 keeps every s-th row and column of layer k's output (the
  * stride-2 stand-in for pooling between the stages of VGG-16).  All descriptors name the same batch
- * n, nChw16c activations and one device (descs[0].device). */
+ * n, nChw16c activations and one device (descs[0].device); the FIRST layer's input may instead be
+ * the caller's plain image (ELB_NCHW or ELB_NHWC, as the reference's first-layer runs pass it,
+ * scripts/regression-fp32.sh: --input-format=nchw).  An fp32 3x3 stride-1 layer with at most four
+ * input channels reads an nchw image directly (three planes instead of a 16-channel block of which
+ * three channels are real); other plain inputs are converted on the device first. */
 typedef struct elb_stack elb_stack_t;
 ELB_API int elb_stack_create(const elb_conv_desc_t *descs, const int32_t *subsample_after, int n_layers,
                              elb_stack_t **stack);
