@@ -11,7 +11,7 @@ c5i8 the stack with INT8 direct kernels, dw INT8 depthwise), each with its own v
 e2e, roofline and parity.  `--workload X` runs one workload alone (profiling, experiments).
 
 Partitioning: the minibatch is split.  With N GPUs rank r owns images [r*B/N, (r+1)*B/N) of every
-configuration's global batch B (c5: 256 images = 8/N chunks of 32 per GPU), weights are replicated,
+configuration's global batch B (c5: 256/N images per GPU in chunks of 64, of 32 at 8 GPUs), weights are replicated,
 nothing is exchanged on the data path, so `scaling` is "strong" (total work fixed).
 
 What the numbers are:
@@ -91,17 +91,23 @@ WORKLOADS = {
                desc="INT8 depthwise 3x3 MobileNet-v1 Conv2d_3 N=64 C=128 56x56 s1 p1 bias+ReLU u8 out nChw16c T=14"),
     "c5": dict(metric="effective_conv_tflops_fp32_winograd_vgg16_stack", unit="TFLOP/s", dtype="tf32x3(fp32)", batch=256,
                desc="VGG-16 conv stack, 13 layers 3x3 p1, 224x224 input, fp32 Winograd F(4x4,3x3), global batch 256 in "
-                    "chunks of 32 images, stride-2 subsample between stages, bias+ReLU; the network input is the "
+                    "chunks (see chunk_images), stride-2 subsample between stages, bias+ReLU; the network input is the "
                     "nchw image (3 planes), activations and weights nChw16c / OIhw16i16o"),
     "c5i8": dict(metric="effective_conv_tops_int8_vgg16_stack", unit="TOP/s", dtype="u8", batch=256,
                  desc="VGG-16 conv stack, 13 layers 3x3 p1, 224x224 input, INT8 u8s8 direct, u8 between layers, global "
-                      "batch 256 in chunks of 32 images, stride-2 subsample between stages, bias+ReLU, nChw16c"),
+                      "batch 256 in chunks (see chunk_images), stride-2 subsample between stages, bias+ReLU; the network input is "
+                      "the nchw u8 image (3 planes), activations and weights nChw16c / OIhw16i16o"),
 }
 HEADLINE = "c5"
 PER_CONFIG = ["c1", "c2", "c3", "c4", "c5i8", "dw"]
 # published number for exactly this metric/config (2 x Xeon 8180, the reference's tuned script comment)
 PUBLISHED = {"c1": 11.2}
-STACK_CHUNK = 32
+# Images per chunk of a stack (one chunk = one pass of the chain over that many images): 64 where a
+# GPU's share of the global batch allows it, i.e. up to 4 GPUs for 256 images, 32 at 8 GPUs.  Measured
+# on one B200 (fp32 stack, 256 images): 25.7 ms per step with chunks of 32, 25.0 ms with 64 (the
+# 14x14 and 28x28 layers fill their last wave better and there are half the launches); 24.7 ms with
+# 128, whose first copy in is too long to hide end to end (25.96 against 25.3 ms).
+STACK_CHUNK = 64
 
 # DRAM bytes (read + written) per step from the ncu captures summarised under profiles/ (sum over
 # the kernels of a step, full-size workloads; c5: captured at 8 images and scaled to the 256 of a
@@ -552,16 +558,19 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
     args = ctx.args
     int8 = wid == "c5i8"
     gbatch = args.batch or wl["batch"]
-    n = min(STACK_CHUNK, gbatch)
+    n = min(STACK_CHUNK, max(1, gbatch // ctx.world))
+    while n > 1 and (gbatch // ctx.world) % n:
+        n //= 2
     chunks_g = gbatch // n
     if chunks_g * n != gbatch or chunks_g % ctx.world:
         raise RuntimeError(f"{wid}: global batch {gbatch} is not {ctx.world} x a whole number of {n}-image chunks")
     chunks = chunks_g // ctx.world                  # per GPU
     c_first = ctx.rank * chunks
     scales = vgg_calibrate(ctx.local_rank) if int8 else None
-    # the fp32 stack's first layer reads the caller's nchw image (three planes); the INT8 stack takes
-    # the blocked u8 tensor
-    plain = not int8
+    # the network input is the caller's nchw image (three planes): the fp32 stack's first kernel reads
+    # it directly, the INT8 stack converts it to a blocked tensor on the device (one small kernel,
+    # counted in the timed region) -- a fifth of the bytes over PCIe either way
+    plain = True
     st, cases = build_stack(n, int8, ctx.local_rank, scales, plain_image=plain)
     ops_chunk = sum(c.cal_ops() for c in cases)
     ops_g = ops_chunk * chunks_g

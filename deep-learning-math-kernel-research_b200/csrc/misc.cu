@@ -44,9 +44,49 @@ __global__ void __launch_bounds__(256) reorder_kernel(T *__restrict__ dst, const
   }
 }
 
+// u8 nchw -> nChw16c when a plane is a whole number of 4-pixel groups: one thread = 4 pixels of one
+// channel block.  It reads one 32-bit word per real channel (a warp: 128 contiguous bytes of a plane)
+// and writes the four pixels' 16-byte blocks, padding lanes zero.  (The byte-wise kernel above moves
+// one byte per access: measured 43 us for 32 RGB images of 224x224 against a few us of traffic.)
+__global__ void __launch_bounds__(256) reorder_u8_planes_kernel(uint4 *__restrict__ dst, const uint8_t *__restrict__ src,
+                                                                int c, int hw4, long long total) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int C2 = (c + 15) / 16;
+  const int q = static_cast<int>(idx % hw4);
+  const int cb = static_cast<int>((idx / hw4) % C2);
+  const long long n = idx / (static_cast<long long>(hw4) * C2);
+  uint32_t pl[16];
+#pragma unroll
+  for (int ch = 0; ch < 16; ++ch) {
+    const int cc = cb * 16 + ch;
+    pl[ch] = cc < c ? __ldg(reinterpret_cast<const uint32_t *>(src) + (n * c + cc) * hw4 + q) : 0u;
+  }
+  uint4 *o = dst + ((n * C2 + cb) * hw4 + q) * 4;
+#pragma unroll
+  for (int px = 0; px < 4; ++px) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // byte px of the four planes 4j .. 4j+3, in channel order
+      const uint32_t lo = __byte_perm(pl[4 * j], pl[4 * j + 1], 0x0040 + px * 0x0011);
+      const uint32_t hi = __byte_perm(pl[4 * j + 2], pl[4 * j + 3], 0x0040 + px * 0x0011);
+      w[j] = __byte_perm(lo, hi, 0x5410);
+    }
+    o[px] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 template <bool TO_BLOCKED>
 cudaError_t launch(void *dst, const void *src, int n, int c, int h, int w, int eb, cudaStream_t s) {
   const int hw = h * w;
+  if (TO_BLOCKED && eb == 1 && hw % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) & 3) == 0) &&
+      ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+    const long long total = static_cast<long long>(n) * ((c + 15) / 16) * (hw / 4);
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    reorder_u8_planes_kernel<<<blocks, 256, 0, s>>>((uint4 *)dst, (const uint8_t *)src, c, hw / 4, total);
+    return cudaGetLastError();
+  }
   dim3 grid((hw + 127) / 128, (c + 15) / 16, n);
   if (eb == 1)
     reorder_kernel<uint8_t, TO_BLOCKED><<<grid, 256, 0, s>>>((uint8_t *)dst, (const uint8_t *)src, c, hw);

@@ -26,6 +26,9 @@ CASES = [
     _i8("fmt_i8_3x3_nhwc_in_blocked_out", 2, 32, 64, 12, algo="direct", ifmt="nhwc", wfmt="oihw"),
     _i8("fmt_i8_3x3s2_nchw_s8", 1, 48, 32, 15, stride=2, algo="direct", types="u8f32s8f32", relu=False, oscale=8.0,
         ifmt="nchw", ofmt="nchw", wfmt="oihw"),
+    # u8 planes whose size is a multiple of four pixels: the word-wise nchw -> nChw16c converter
+    _i8("fmt_i8_3x3_rgb_nchw", 2, 3, 32, 16, algo="direct", ifmt="nchw"),
+    _i8("fmt_i8_3x3_40ch_nchw", 1, 40, 24, 12, algo="direct", ifmt="nchw", wfmt="oihw"),
     _i8("fmt_i8_wino_nhwc_f32", 2, 32, 32, 12, algo="wino", tile=6, types="u8f32f32f32", relu=False, bias=False,
         ifmt="nhwc", ofmt="nhwc", wfmt="hwio"),
     R.ConvCase("fmt_f32_wino_rgb_nchw", 2, 3, 64, 16, 16, types="fp32", algo="wino", tile=6, relu=True, bias=True,

@@ -39,7 +39,8 @@ def pairs(E):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.uint8])
-@pytest.mark.parametrize("dims", [(1, 2, 19, 5, 7), (3, 35, 16, 3, 3), (1, 4, 64, 14, 14), (2, 17, 3, 1, 1)])
+@pytest.mark.parametrize("dims", [(1, 2, 19, 5, 7), (3, 35, 16, 3, 3), (1, 4, 64, 14, 14), (2, 17, 3, 1, 1),
+                                  (1, 3, 3, 8, 6), (1, 2, 37, 4, 10)])
 def test_every_reorder_pair(dtype, dims):
     import torch
     E = package()
