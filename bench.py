@@ -11,7 +11,7 @@ c5i8 the stack with INT8 direct kernels, dw INT8 depthwise), each with its own v
 e2e, roofline and parity.  `--workload X` runs one workload alone (profiling, experiments).
 
 Partitioning: the minibatch is split.  With N GPUs rank r owns images [r*B/N, (r+1)*B/N) of every
-configuration's global batch B (c5: 256/N images per GPU in chunks of 64, of 32 at 8 GPUs), weights are replicated,
+configuration's global batch B (c5: 256/N images per GPU in chunks of 64, of 32 from 4 GPUs up), weights are replicated,
 nothing is exchanged on the data path, so `scaling` is "strong" (total work fixed).
 
 What the numbers are:
@@ -103,7 +103,8 @@ PER_CONFIG = ["c1", "c2", "c3", "c4", "c5i8", "dw"]
 # published number for exactly this metric/config (2 x Xeon 8180, the reference's tuned script comment)
 PUBLISHED = {"c1": 11.2}
 # Images per chunk of a stack (one chunk = one pass of the chain over that many images): 64 where a
-# GPU's share of the global batch allows it, i.e. up to 4 GPUs for 256 images, 32 at 8 GPUs.  Measured
+# GPU's share of the global batch is at least two such chunks (end to end, the copy in of one chunk
+# hides behind the chain of the previous one), i.e. at 1 and 2 GPUs for 256 images; 32 otherwise.  Measured
 # on one B200 (fp32 stack, 256 images): 25.7 ms per step with chunks of 32, 25.0 ms with 64 (the
 # 14x14 and 28x28 layers fill their last wave better and there are half the launches); 24.7 ms with
 # 128, whose first copy in is too long to hide end to end (25.96 against 25.3 ms).
@@ -558,8 +559,9 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
     args = ctx.args
     int8 = wid == "c5i8"
     gbatch = args.batch or wl["batch"]
-    n = min(STACK_CHUNK, max(1, gbatch // ctx.world))
-    while n > 1 and (gbatch // ctx.world) % n:
+    per_gpu = max(1, gbatch // ctx.world)
+    n = STACK_CHUNK if per_gpu >= 2 * STACK_CHUNK else min(STACK_CHUNK // 2, per_gpu)
+    while n > 1 and per_gpu % n:
         n //= 2
     chunks_g = gbatch // n
     if chunks_g * n != gbatch or chunks_g % ctx.world:
