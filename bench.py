@@ -114,7 +114,7 @@ STACK_CHUNK = 64
 # the kernels of a step, full-size workloads; c5: captured at 8 images and scaled to the 256 of a
 # step -- the traffic of every kernel of the stack grows in proportion to the images).
 NCU_TRAFFIC = {"c1": 2139.6e6, "c2": 13.15e6, "c3": 26.03e6, "c3s": 38.88e6, "c4": 1268.9e6, "dw": 25.72e6, "c2f": 53.5e6,
-               "c5": 95.1e9}
+               "c5": 94.9e9}
 
 
 # ------------------------------------------------------------------------------------ helpers
