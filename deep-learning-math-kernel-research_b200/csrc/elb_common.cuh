@@ -21,6 +21,25 @@ inline int tune_env(const char *name, int dflt) {
   return dflt;
 }
 
+// Launch a kernel that may overlap its set-up with the tail of the kernel before it in the stream
+// (see griddep_wait in umma.cuh: the kernel must contain the wait).  Captured into a CUDA graph the
+// dependency becomes a programmatic edge.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = tune_env("ELB_NO_OVERLAP", 0) ? 0 : 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // device status word values (0 = ok)
 enum : int {
   ST_OK = 0,

@@ -148,6 +148,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) i8_umma_kernel(const __grid_co
   }
   const uint32_t tmem_base = is_producer ? 0u : *tmem_slot;      // (producers never touch tensor memory)
   if (threadIdx.x == 0) ELB_TRACE(1);
+  // Everything above touched only this plan's constants.  The kernel after this one may set itself up
+  // now; this one reads its input (and later writes its output) only once the kernel before it is done:
+  // the producers wait here, every other role acts on what the producers' copies deliver.
+  if (threadIdx.x == 0) griddep_launch_dependents();
+  if (is_producer) griddep_wait();
   int fail_code = 0;
 
   if (warp == 0 || warp >= PRODUCER2_WARP) {
@@ -516,10 +521,11 @@ cudaError_t launch_cfg(const I8ConvParams &p, int num_sms, cudaStream_t s, bool 
   }
   // the kernels compiled for the plain case (see SPEC)
   const bool plain = MODE == I8_MODE_BOX && p.tap_tbl && !p.trace;
-  if (MODE == I8_MODE_BOX && plain && p.merged_rows) i8_umma_kernel<BN, KC, STAGES, MODE, 1><<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
-  else if (MODE == I8_MODE_BOX && plain) i8_umma_kernel<BN, KC, STAGES, MODE, 2><<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
-  else kern<<<grid, NUM_THREADS, L::TOTAL, s>>>(p);
-  return cudaGetLastError();
+  if (MODE == I8_MODE_BOX && plain && p.merged_rows)
+    return launch_overlapped(i8_umma_kernel<BN, KC, STAGES, MODE, 1>, dim3(grid), dim3(NUM_THREADS), L::TOTAL, s, p);
+  if (MODE == I8_MODE_BOX && plain)
+    return launch_overlapped(i8_umma_kernel<BN, KC, STAGES, MODE, 2>, dim3(grid), dim3(NUM_THREADS), L::TOTAL, s, p);
+  return launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), L::TOTAL, s, p);
 }
 
 }  // namespace
