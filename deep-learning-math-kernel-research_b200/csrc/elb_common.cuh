@@ -21,9 +21,23 @@ inline int tune_env(const char *name, int dflt) {
   return dflt;
 }
 
+// A kernel launched with programmatic stream serialisation (launch_overlapped below) may
+// start while the kernel before it in the stream is still running, once every CTA of that kernel has
+// executed griddep_launch_dependents() or has finished.  Such a kernel must execute griddep_wait()
+// before its first access to global memory that an earlier kernel writes or reads: the wait returns
+// when the earlier kernel has completed and its writes are visible.  What runs before the wait (barrier
+// initialisation, tensor-memory allocation, loading per-plan constants) overlaps the tail of the
+// earlier kernel.  In a kernel launched the plain way both instructions do nothing.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Launch a kernel that may overlap its set-up with the tail of the kernel before it in the stream
-// (see griddep_wait in umma.cuh: the kernel must contain the wait).  Captured into a CUDA graph the
-// dependency becomes a programmatic edge.
+// (the kernel must contain griddep_wait).  Captured into a CUDA graph the
+// dependency becomes a programmatic edge.  Only the INT8 tensor-core kernels are launched this way:
+// their set-up (barriers, tensor memory, per-channel constants, the copy table) is 2-3 us of a launch
+// that may last 10 us.  Measured on the fp32 Winograd path: overlapped launches of the GEMM and the
+// input transform change nothing, and the output transform launched as an early dependent is SLOWER
+// (c1 0.506 -> 0.550 ms, with all three 0.592 ms; the fp32 stack 24.2 -> 28.5 ms), so those stay plain.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
                                      Args &&...args) {

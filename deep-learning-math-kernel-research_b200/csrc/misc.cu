@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(256) reorder_kernel(T *__restrict__ dst, const
 // one byte per access: measured 43 us for 32 RGB images of 224x224 against a few us of traffic.)
 __global__ void __launch_bounds__(256) reorder_u8_planes_kernel(uint4 *__restrict__ dst, const uint8_t *__restrict__ src,
                                                                 int c, int hw4, long long total) {
+  griddep_launch_dependents();      // an INT8 kernel behind this one may set itself up (see launch_overlapped)
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int C2 = (c + 15) / 16;
@@ -161,6 +162,7 @@ __global__ void __launch_bounds__(256) transpose_kernel(T *__restrict__ dst, con
 template <int PIECES>
 __global__ void __launch_bounds__(256) subsample_kernel(int4 *__restrict__ dst, const int4 *__restrict__ src, int planes,
                                                         int h, int w, int oh, int ow, int sh, int sw) {
+  griddep_launch_dependents();      // an INT8 kernel behind this one may set itself up (see launch_overlapped)
   const long long total = (long long)planes * oh * ow * PIECES;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {

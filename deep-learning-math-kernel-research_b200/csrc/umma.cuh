@@ -184,17 +184,6 @@ __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
-// ------------------------------------------------------------------------------------ dependent launches
-// A kernel launched with programmatic stream serialisation (launch_overlapped in elb_common.cuh) may
-// start while the kernel before it in the stream is still running, once every CTA of that kernel has
-// executed griddep_launch_dependents() or has finished.  Such a kernel must execute griddep_wait()
-// before its first access to global memory that an earlier kernel writes or reads: the wait returns
-// when the earlier kernel has completed and its writes are visible.  What runs before the wait (barrier
-// initialisation, tensor-memory allocation, loading per-plan constants) overlaps the tail of the
-// earlier kernel.  In a kernel launched the plain way both instructions do nothing.
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // ------------------------------------------------------------------------------------ TMEM
 // Allocate ncols (power of two, 32..512) columns of tensor memory; the base address is written to
 // *smem_slot.  Must be executed by one full, converged warp.
