@@ -197,6 +197,17 @@ def split_batch(global_batch: int, world: int, rank: int):
     return first, global_batch * (rank + 1) // world - first
 
 
+def stack_chunk_images(global_batch: int, world: int) -> int:
+    """Images per chunk of a stack on one GPU of `world` (see STACK_CHUNK): 64 where the GPU's share
+    holds at least two such chunks, else 32 (or the whole share when that is smaller), halved until it
+    divides the share."""
+    per_gpu = max(1, global_batch // world)
+    n = STACK_CHUNK if per_gpu >= 2 * STACK_CHUNK else min(STACK_CHUNK // 2, per_gpu)
+    while n > 1 and per_gpu % n:
+        n //= 2
+    return n
+
+
 def throughput(ops_global: float, ms_per_step: float) -> float:
     """Whole-job T(FL)OP/s: the op count of the GLOBAL batch over the step time of the slowest rank."""
     return ops_global / (ms_per_step * 1e-3) / 1e12
@@ -559,10 +570,7 @@ def run_stack(wid: str, ctx: Ctx, cpu_baseline: bool, steps: int):
     args = ctx.args
     int8 = wid == "c5i8"
     gbatch = args.batch or wl["batch"]
-    per_gpu = max(1, gbatch // ctx.world)
-    n = STACK_CHUNK if per_gpu >= 2 * STACK_CHUNK else min(STACK_CHUNK // 2, per_gpu)
-    while n > 1 and per_gpu % n:
-        n //= 2
+    n = stack_chunk_images(gbatch, ctx.world)
     chunks_g = gbatch // n
     if chunks_g * n != gbatch or chunks_g % ctx.world:
         raise RuntimeError(f"{wid}: global batch {gbatch} is not {ctx.world} x a whole number of {n}-image chunks")

@@ -55,6 +55,18 @@ def test_max_over_ranks_and_aggregate(tmp_path):
     assert out["chunks0"] == [0, 4]
 
 
+def test_stack_chunks_per_gpu():
+    """The stacks' chunk size: 64 images while a GPU has at least two such chunks of the 256, else 32;
+    a whole number of chunks per GPU at every N the harness runs."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+    assert [bench.stack_chunk_images(256, w) for w in (1, 2, 4, 8)] == [64, 64, 32, 32]
+    assert bench.stack_chunk_images(8, 1) == 8 and bench.stack_chunk_images(96, 1) == 32
+    for w in (1, 2, 4, 8):
+        n = bench.stack_chunk_images(256, w)
+        assert (256 // w) % n == 0 and (256 // n) % w == 0
+
+
 @pytest.mark.skipif(not (ROOT / "oracle" / "_ref" / "ref_driver").exists(), reason="reference build missing")
 def test_reference_arm_runs_on_rank0_only():
     r = _torchrun(["bench.py", "--impl", "reference", "--workload", "c2", "--gpus", "2", "--steps", "3", "--warmup", "1"])
