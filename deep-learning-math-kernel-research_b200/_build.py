@@ -15,7 +15,7 @@ ROOT = PKG_DIR.parent
 LIB_PATH = PKG_DIR / "lib" / "libeuler_b200.so"
 HOST_LIB_PATH = PKG_DIR / "lib" / "libel.so"
 CSRC = PKG_DIR / "csrc"
-CU_SOURCES = ["elb_api.cu", "int8_conv.cu", "int8_conv2.cu", "wino.cu", "depthwise.cu", "misc.cu", "elb_multi.cu", "f32_small_ic.cu"]
+CU_SOURCES = ["elb_api.cu", "int8_conv.cu", "int8_conv2.cu", "wino.cu", "depthwise.cu", "misc.cu", "elb_multi.cu", "f32_small_ic.cu", "f32_rgb_umma.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
 

@@ -1933,6 +1933,7 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     const WinoGeom &g = w->g;
     SmallIcParams sp{};
     sp.planar = pl.in_planar ? 1 : 0;
+    sp.trace = static_cast<long long *>(pl.trace);
     sp.in = static_cast<const float *>(in) +
             static_cast<size_t>(first) * (pl.in_planar ? static_cast<size_t>(w->ic_real) * g.IH * g.IW : w->in_img_bytes / 4);
     sp.out = static_cast<float *>(out) + static_cast<size_t>(first) * (w->out_img_bytes / 4);
@@ -1943,7 +1944,8 @@ int wino_run(WinoPlan &pl, void *out, const void *in, void *acc_dump, int *statu
     sp.with_bias = w->with_bias; sp.with_relu = w->with_relu; sp.with_sum = w->with_sum;
     const bool timed = pl.stage_ev[0] != nullptr;
     if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[0], s)); W_TRY(cudaEventRecord(pl.stage_ev[1], s)); }
-    W_TRY(launch_f32_small_ic(sp, s));
+    if (f32_rgb_umma_supported(sp) && tune_env("ELB_RGB_UMMA", 1) != 0) W_TRY(launch_f32_rgb_umma(sp, num_sms, status, s));
+    else W_TRY(launch_f32_small_ic(sp, s));
     if (timed) { W_TRY(cudaEventRecord(pl.stage_ev[2], s)); W_TRY(cudaEventRecord(pl.stage_ev[3], s)); }
     launches = 1;
     return ELB_OK;

@@ -41,9 +41,14 @@ struct SmallIcParams {
   int N, H, W, CB, OCB, ic;
   int with_bias, with_relu, with_sum;
   int planar;           // the input is the caller's nchw tensor
+  long long *trace;     // optional per-CTA timeline of the tensor-core kernel (64 slots per CTA), else null
 };
 size_t f32_small_ic_smem_bytes(int OCB);
 cudaError_t init_f32_small_ic(int OCB);        // once per plan and device (kernel attribute)
 cudaError_t launch_f32_small_ic(const SmallIcParams &p, cudaStream_t s);
+// the same convolution on the tensor cores for an nchw image and 64 output channels (f32_rgb_umma.cu);
+// status = the plan's device status word (a bounded wait that gives up leaves its code there)
+bool f32_rgb_umma_supported(const SmallIcParams &p);
+cudaError_t launch_f32_rgb_umma(const SmallIcParams &p, int num_sms, int *status, cudaStream_t s);
 
 }  // namespace elb

@@ -40,6 +40,15 @@ CASES = [
                ifmt="nchw", ofmt="nchw", wfmt="oihw"),
     R.ConvCase("fmt_f32_wino_4ch_nchw_sum", 1, 4, 40, 12, 12, types="fp32", algo="wino", tile=6, relu=True, bias=True,
                sum=True, ifmt="nchw"),
+    # ... and with exactly 64 output channels the tensor-core first-layer kernel takes it
+    R.ConvCase("fmt_f32_rgb64_nchw_ragged", 2, 3, 64, 21, 30, types="fp32", algo="wino", tile=6, relu=True, bias=True,
+               ifmt="nchw"),
+    R.ConvCase("fmt_f32_gray64_nchw_plain", 1, 1, 64, 9, 13, types="fp32", algo="wino", tile=6, relu=False, bias=True,
+               ifmt="nchw", ofmt="nchw", wfmt="oihw"),
+    R.ConvCase("fmt_f32_2ch64_nchw", 3, 2, 64, 40, 36, types="fp32", algo="wino", tile=6, relu=True, bias=False,
+               ifmt="nchw"),
+    R.ConvCase("fmt_f32_4ch64_nchw", 1, 4, 56, 12, 12, types="fp32", algo="wino", tile=6, relu=True, bias=True,
+               ifmt="nchw"),
     R.ConvCase("fmt_f32_wino_nhwc", 1, 32, 48, 9, 11, types="fp32", algo="wino", tile=4, relu=True, bias=True,
                ifmt="nhwc", ofmt="nhwc", wfmt="hwio"),
     R.ConvCase("fmt_f32_1x1_nhwc_sum", 2, 64, 40, 8, 8, kh=1, kw=1, pad=0, types="fp32", algo="1x1", relu=True, bias=True,
