@@ -111,7 +111,8 @@ enum {
   ELB_KERNEL_WINO_I8_UMMA = 5,      /* int8 F(4x4,3x3): quantising transforms + tcgen05 kind::i8     */
   ELB_KERNEL_I8_DEPTHWISE = 6,      /* int8 depthwise 3x3: bandwidth-bound dp4a kernel               */
   ELB_KERNEL_F32_DIRECT_UMMA = 7,   /* fp32 1x1 / KxK direct: implicit GEMM on the 3xTF32 tcgen05 kernel */
-  ELB_KERNEL_F32_SMALL_IC = 8       /* fp32 3x3 s1 p1 Winograd request with <= 4 input channels: CUDA-core direct kernel */
+  ELB_KERNEL_F32_SMALL_IC = 8       /* fp32 3x3 s1 p1 Winograd request with <= 4 input channels: direct kernel (tcgen05
+                                       implicit GEMM for an nchw image into 64 channels, CUDA cores otherwise) */
 };
 
 typedef struct elb_conv elb_conv_t;      /* the plan; replaces `elx_conv_t *xc` (include/euler.hpp:186) */
